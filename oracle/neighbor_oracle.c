@@ -1,0 +1,182 @@
+/*
+ * TEST INFRASTRUCTURE — NOT PART OF THE PRODUCT PATH.
+ *
+ * Plain-C restatement, on the CPU, of what the reference's CUDA neighbour
+ * search computes.  It exists to check the sm_100a kernels bit for bit and is
+ * imported only by tests, the smoke check and the CPU-baseline leg of the
+ * benchmark.  Nothing under pytorch_cluster_b200/ may call it.
+ *
+ * What is restated (paths are relative to the reference checkout):
+ *   - segment pointers      torch_cluster/knn.py:74-79 (bucketize, right=False)
+ *   - segment lookup        csrc/cuda/utils.cuh:11-19
+ *   - squared-L2 distance   csrc/cuda/knn_cuda.cu:61-64, radius_cuda.cu:28-31
+ *   - cosine distance       csrc/cuda/knn_cuda.cu:9-28, 55-59
+ *   - k-best insertion      csrc/cuda/knn_cuda.cu:44-50, 67-77 (strict '>')
+ *   - radius scan           csrc/cuda/radius_cuda.cu:26-41 (strict '<', first
+ *                           max_num_neighbors hits in ascending x order)
+ *   - r*r narrowing         csrc/cuda/radius_cuda.cu:90
+ *
+ * Rounding policy.  nvcc contracts `acc += d*d` into one fused multiply-add by
+ * default, so the reference CUDA kernels accumulate acc = fma(d, d, acc) in the
+ * tensor's scalar type, starting from 0, in ascending feature order.  `fused`
+ * = 1 restates exactly that.  `fused` = 0 restates the reference's CPU
+ * arithmetic instead (nanoflann L2_Adaptor, csrc/cpu/utils/nanoflann.hpp:383-408):
+ * separately rounded multiplies and adds, in groups of four features
+ * (d0*d0 + d1*d1 + d2*d2 + d3*d3 added to the running sum) with a sequential
+ * tail.  The file must be compiled with -ffp-contract=off so that only the
+ * explicit fma()/fmaf() calls fuse.
+ *
+ * Parity pin: checked in tests/test_oracle.py against the reference's own
+ * known-answer tests (test/test_knn.py, test/test_radius.py, README examples)
+ * and against outputs of the reference's compiled CPU path (oracle/_ref, and
+ * the fixtures under tests/golden that were generated with it).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#if defined(__x86_64__) && defined(__GNUC__)
+#define HOT __attribute__((target_clones("fma", "default")))
+#else
+#define HOT
+#endif
+
+/* ptr[i] = number of entries of the sorted batch vector that are < i,
+ * i = 0..num_segments (torch.bucketize(arange(B+1), batch), knn.py:77-79). */
+void oracle_segment_ptr(const int64_t *batch, int64_t n, int64_t num_segments,
+                        int64_t *ptr) {
+  int64_t j = 0;
+  for (int64_t i = 0; i <= num_segments; i++) {
+    while (j < n && batch[j] < i)
+      j++;
+    ptr[i] = j;
+  }
+}
+
+/* First i with ptr[i+1] > idx, else num_segments-1 (utils.cuh:11-19). */
+static int64_t segment_of(int64_t idx, const int64_t *ptr, int64_t num_segments) {
+  for (int64_t i = 0; i < num_segments; i++)
+    if (ptr[i + 1] > idx)
+      return i;
+  return num_segments - 1;
+}
+
+#define DEFINE_ORACLE(T, SUFFIX, FMA, SQRT)                                     \
+  static inline T sqdist_##SUFFIX(const T *a, const T *b, int64_t dim,         \
+                                  int fused) {                                  \
+    if (fused) {                                                                \
+      T acc = 0;                                                                \
+      for (int64_t d = 0; d < dim; d++) {                                       \
+        T diff = a[d] - b[d];                                                   \
+        acc = FMA(diff, diff, acc);                                             \
+      }                                                                         \
+      return acc;                                                               \
+    }                                                                           \
+    /* non-fused: a = query side, b = point side, as nanoflann evaluates */     \
+    T result = 0;                                                      \
+    int64_t d = 0;                                                              \
+    for (; d + 3 < dim; d += 4) {                                               \
+      T d0 = a[d] - b[d], d1 = a[d + 1] - b[d + 1];                    \
+      T d2 = a[d + 2] - b[d + 2], d3 = a[d + 3] - b[d + 3];            \
+      T p0 = d0 * d0, p1 = d1 * d1, p2 = d2 * d2, p3 = d3 * d3;        \
+      T s = p0 + p1;                                                   \
+      s = s + p2;                                                               \
+      s = s + p3;                                                               \
+      result = result + s;                                                      \
+    }                                                                           \
+    for (; d < dim; d++) {                                                      \
+      T d0 = a[d] - b[d];                                              \
+      T p0 = d0 * d0;                                                  \
+      result = result + p0;                                                     \
+    }                                                                           \
+    return result;                                                              \
+  }                                                                             \
+                                                                                \
+  static inline T cosdist_##SUFFIX(const T *xr, const T *yr, int64_t dim) {    \
+    T dot = 0, nx = 0, ny = 0;                                                  \
+    for (int64_t d = 0; d < dim; d++)                                           \
+      dot = FMA(xr[d], yr[d], dot);                                             \
+    for (int64_t d = 0; d < dim; d++)                                           \
+      nx = FMA(xr[d], xr[d], nx);                                               \
+    for (int64_t d = 0; d < dim; d++)                                           \
+      ny = FMA(yr[d], yr[d], ny);                                               \
+    T q = dot / (SQRT(nx) * SQRT(ny));                                          \
+    return (T)(1. - (double)q);                                                 \
+  }                                                                             \
+                                                                                \
+  /* out_col / out_dist: [m*k], -1 / 1e10 where fewer than k were found.        \
+   * Returns the number of valid (non -1) slots. */                             \
+  HOT int64_t oracle_knn_##SUFFIX(                                              \
+      const T *x, const T *y, const int64_t *ptr_x, const int64_t *ptr_y,       \
+      int64_t num_segments, int64_t n, int64_t m, int64_t dim, int64_t k,       \
+      int cosine, int fused, int64_t *out_col, T *out_dist) {                   \
+    (void)n;                                                                    \
+    int64_t valid = 0;                                                          \
+    _Pragma("omp parallel for schedule(dynamic, 64) reduction(+ : valid)")      \
+    for (int64_t n_y = 0; n_y < m; n_y++) {                                     \
+      const int64_t b = segment_of(n_y, ptr_y, num_segments);                   \
+      T *best_dist = out_dist + n_y * k;                                        \
+      int64_t *best_idx = out_col + n_y * k;                                    \
+      for (int64_t e = 0; e < k; e++) {                                         \
+        best_dist[e] = (T)1e10;                                                 \
+        best_idx[e] = -1;                                                       \
+      }                                                                         \
+      for (int64_t n_x = ptr_x[b]; n_x < ptr_x[b + 1]; n_x++) {                 \
+        T tmp = cosine ? cosdist_##SUFFIX(x + n_x * dim, y + n_y * dim, dim)    \
+                       : sqdist_##SUFFIX(x + n_x * dim, y + n_y * dim, dim,     \
+                                         fused);                                \
+        /* the list is ascending, so "no slot is > tmp" == "last is not" */     \
+        if (!(best_dist[k - 1] > tmp))                                          \
+          continue;                                                             \
+        int64_t e1 = 0;                                                         \
+        while (!(best_dist[e1] > tmp))                                          \
+          e1++;                                                                 \
+        for (int64_t e2 = k - 1; e2 > e1; e2--) {                               \
+          best_dist[e2] = best_dist[e2 - 1];                                    \
+          best_idx[e2] = best_idx[e2 - 1];                                      \
+        }                                                                       \
+        best_dist[e1] = tmp;                                                    \
+        best_idx[e1] = n_x;                                                     \
+      }                                                                         \
+      for (int64_t e = 0; e < k; e++)                                           \
+        valid += best_idx[e] >= 0;                                              \
+    }                                                                           \
+    return valid;                                                               \
+  }                                                                             \
+                                                                                \
+  /* Pass 1 (out_col == NULL): counts[n_y] = number of edges kept for n_y.      \
+   * Pass 2: out_col[offsets[n_y] + j] = j-th kept x index (ascending).         \
+   * Returns the total number of edges. */                                      \
+  HOT int64_t oracle_radius_##SUFFIX(                                           \
+      const T *x, const T *y, const int64_t *ptr_x, const int64_t *ptr_y,       \
+      int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,        \
+      int64_t max_num_neighbors, int ignore_same_index, int fused,              \
+      int64_t *counts, const int64_t *offsets, int64_t *out_col) {              \
+    (void)n;                                                                    \
+    const T r2 = (T)(r * r);                                                    \
+    int64_t total = 0;                                                          \
+    _Pragma("omp parallel for schedule(dynamic, 64) reduction(+ : total)")      \
+    for (int64_t n_y = 0; n_y < m; n_y++) {                                     \
+      const int64_t b = segment_of(n_y, ptr_y, num_segments);                   \
+      int64_t count = 0;                                                        \
+      for (int64_t n_x = ptr_x[b]; n_x < ptr_x[b + 1]; n_x++) {                 \
+        if (count >= max_num_neighbors)                                         \
+          break;                                                                \
+        T dist = fused ? sqdist_##SUFFIX(x + n_x * dim, y + n_y * dim, dim, 1)  \
+                       : sqdist_##SUFFIX(y + n_y * dim, x + n_x * dim, dim, 0); \
+        if (dist < r2 && !(ignore_same_index && n_y == n_x)) {                  \
+          if (out_col)                                                          \
+            out_col[offsets[n_y] + count] = n_x;                                \
+          count++;                                                              \
+        }                                                                       \
+      }                                                                         \
+      if (counts)                                                               \
+        counts[n_y] = count;                                                    \
+      total += count;                                                           \
+    }                                                                           \
+    return total;                                                               \
+  }
+
+DEFINE_ORACLE(float, f32, fmaf, sqrtf)
+DEFINE_ORACLE(double, f64, fma, sqrt)
