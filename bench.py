@@ -1,0 +1,324 @@
+"""Benchmark of the neighbour-graph path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+Headline workload (``knn_graph_batched``): 32 clouds x 4096 points, 3-D fp32 ~ N(0,1), sorted
+batch vector, k = 20, loop = False — synthetic, seeded.  One step = one ``knn_graph`` call over
+the whole batch.  Printed: ONE JSON line with
+  value       queries/s with inputs resident in HBM (CUDA events, L2 flushed between steps)
+  e2e         the same call from pinned host buffers: H2D of x and batch, knn_graph, D2H of
+              edge_index inside the timed region
+  roofline    of the dominant kernel (knn_lowd_kernel, FP32-pipe bound): 8 flop per
+              (query, point) pair / its CUDA-event time when launched alone through the C ABI
+  cpu_baseline  the reference's own CPU path (oracle/_ref: kd-tree search, single thread)
+  extra       further workloads (large bipartite kNN, radius_graph), same method
+
+``--impl reference`` times the reference's CPU implementation on the same workload instead.
+With N > 1 (torchrun) every rank runs the workload on its own clouds (weak scaling, no
+data-path collective); the time is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FP32_LANES_PER_SM = 128
+L2_FLUSH_BYTES = 256 << 20
+
+
+# ---- workloads -----------------------------------------------------------------------------------
+
+def make_knn_graph_batched(seed=2, clouds=32, points=4096):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(clouds * points, 3, generator=g)
+    batch = torch.arange(clouds).repeat_interleave(points)
+    return dict(x=x, batch=batch, k=20, clouds=clouds, points=points, queries=clouds * points,
+                pairs=clouds * points * points)
+
+
+def make_knn_bipartite(seed=3, clouds=8, nx=131072, ny=8192):
+    g = torch.Generator().manual_seed(seed)
+    x = 100 * torch.rand(clouds * nx, 3, generator=g)
+    y = 100 * torch.rand(clouds * ny, 3, generator=g)
+    return dict(x=x, y=y, batch_x=torch.arange(clouds).repeat_interleave(nx),
+                batch_y=torch.arange(clouds).repeat_interleave(ny), k=32, queries=clouds * ny,
+                pairs=clouds * nx * ny)
+
+
+def make_radius_mixture(seed=5, clouds=64, points=8192):
+    g = torch.Generator().manual_seed(seed)
+    n = clouds * points
+    centres = torch.rand(clouds, 32, 3, generator=g)
+    pick = torch.randint(0, 32, (clouds, points), generator=g)
+    x = torch.gather(centres, 1, pick.unsqueeze(-1).expand(-1, -1, 3)) + 0.02 * torch.randn(clouds, points, 3, generator=g)
+    bg = torch.rand(clouds, points, generator=g) < 0.2
+    x[bg] = torch.rand(int(bg.sum()), 3, generator=g)
+    one_below = float(torch.nextafter(torch.tensor(1.0), torch.tensor(0.0)))
+    x = x.clamp_(0, one_below).reshape(n, 3).contiguous()
+    return dict(x=x, batch=torch.arange(clouds).repeat_interleave(points), r=0.05, queries=n,
+                pairs=clouds * points * points)
+
+
+# ---- helpers ---------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                 parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def timed_steps(fn, steps, warmup, flush):
+    """CUDA-event time of `steps` calls of fn(), L2 flushed (outside the timed span) before each."""
+    for _ in range(warmup):
+        flush.fill_(1)
+        fn()
+    torch.cuda.synchronize()
+    total_ms = 0.0
+    for _ in range(steps):
+        flush.fill_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        total_ms += a.elapsed_time(b)
+    return total_ms
+
+
+def max_over_ranks(ms, world):
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f)
+    except OSError:
+        return {}
+
+
+# ---- reference arm (CPU) ------------------------------------------------------------------------------
+
+def reference_knn_graph_cpu(x, k, batch, clouds):
+    """The reference's knn_graph on CPU tensors (torch_cluster/knn.py:131-144) over its compiled
+    CPU operator (oracle/_ref)."""
+    from oracle import reference_cpu as rc
+
+    ptr = torch.bucketize(torch.arange(clouds + 1), batch)
+    e = rc.knn(x, x, ptr, ptr, k + 1, num_workers=os.cpu_count() or 1)
+    row, col = e[1], e[0]
+    mask = row != col
+    return torch.stack([row[mask], col[mask]], dim=0)
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    from oracle import reference_cpu as rc
+
+    w = make_knn_graph_batched()
+    if not rc.available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref (reference CPU path) is not built"}))
+        return
+    for _ in range(max(1, min(args.warmup, 1))):
+        reference_knn_graph_cpu(w["x"], w["k"], w["batch"], w["clouds"])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        reference_knn_graph_cpu(w["x"], w["k"], w["batch"], w["clouds"])
+    dt = time.perf_counter() - t0
+    value = w["queries"] * args.steps / dt
+    line = {
+        "impl": "reference", "metric": "knn_graph queries/s", "value": value, "unit": "queries/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "knn_graph_batched: 32 clouds x 4096 points, 3-D fp32 N(0,1), k=20, loop=False"},
+        "cpu_baseline": {"value": value, "unit": "queries/s", "cores": 1, "kind": "reference",
+                         "sample": "the full workload each step; the reference's CPU path ignores num_workers "
+                                   "(csrc/cpu/knn_cpu.cpp:10), so it runs on one core"},
+        "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---- our arm ------------------------------------------------------------------------------------------------
+
+def run_ours(args, rank, world, local_rank):
+    import pytorch_cluster_b200 as pc
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    peaks = load_peaks()
+    props = torch.cuda.get_device_properties(dev)
+
+    # every rank works on its own clouds (different seed), same shapes: weak scaling
+    w = make_knn_graph_batched(seed=2 + 1000 * rank)
+    x, batch, k = w["x"].to(dev), w["batch"].to(dev), w["k"]
+    hx, hb = w["x"].pin_memory(), w["batch"].pin_memory()
+
+    def step_resident():
+        return pc.knn_graph(x, k, batch)
+
+    out_host = {}
+
+    def step_e2e():
+        dx = hx.to(dev, non_blocking=True)
+        db = hb.to(dev, non_blocking=True)
+        e = pc.knn_graph(dx, k, db)
+        out_host["e"] = e.cpu()
+
+    e0 = step_resident()
+    edges = e0.shape[1]
+    assert edges == w["queries"] * k
+
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local_rank) as clocks:
+        ms = timed_steps(step_resident, args.steps, args.warmup, flush)
+        torch.cuda.synchronize()
+    ms = max_over_ranks(ms, world)
+    if world > 1:
+        dist.barrier()
+    ms_e2e = max_over_ranks(timed_steps(step_e2e, args.steps, args.warmup, flush), world)
+
+    # dominant kernel alone, through the C ABI (memset of one counter + one kernel launch)
+    ptr = torch.ops.torch_cluster.segment_ptr(batch, w["clouds"])
+    ms_kernel = timed_steps(lambda: _cabi.knn_padded_nosync(x, x, k + 1, ptr, ptr), args.steps, args.warmup, flush)
+    ms_kernel = max_over_ranks(ms_kernel, world)
+
+    if rank != 0:
+        return
+    total_queries = w["queries"] * world
+    sm_max = peaks.get("sm_max_mhz") or 1965.0
+    fp32_peak = props.multi_processor_count * FP32_LANES_PER_SM * 2 * sm_max * 1e6 / 1e12
+    flops = 8.0 * w["pairs"]
+    achieved = flops / (ms_kernel / args.steps * 1e-3) / 1e12
+    line = {
+        "metric": "knn_graph queries/s", "value": total_queries * args.steps / (ms * 1e-3), "unit": "queries/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "knn_graph_batched: 32 clouds x 4096 points per GPU, 3-D fp32 N(0,1), k=20, "
+                               "loop=False", "l2": "256 MiB buffer rewritten between timed steps"},
+        "e2e": {"value": total_queries * args.steps / (ms_e2e * 1e-3), "unit": "queries/s",
+                "h2d_bytes_per_step": hx.numel() * 4 + hb.numel() * 8, "d2h_bytes_per_step": 2 * edges * 8},
+        "gpu_launches": 3 * args.steps,
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "fp32", "kernel": "knn_lowd_kernel<float,3,32>", "achieved": achieved,
+                     "peak": fp32_peak, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
+                     "peak_source": f"nominal: {props.multi_processor_count} SMs x 128 lanes x 2 flop x "
+                                    f"{sm_max:.0f} MHz (MEASURED_PEAKS.json holds no fp32 figure)",
+                     "flops_per_launch": flops, "ms_per_launch": ms_kernel / args.steps, "traffic": None},
+    }
+    if not args.no_cpu_baseline:
+        from oracle import reference_cpu as rc
+
+        if rc.available():
+            base = make_knn_graph_batched()
+            t0 = time.perf_counter()
+            reference_knn_graph_cpu(base["x"], base["k"], base["batch"], base["clouds"])
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": base["queries"] / dt, "unit": "queries/s", "cores": 1,
+                                    "kind": "reference",
+                                    "sample": "one pass over the full workload (reference kd-tree path, which "
+                                              "ignores num_workers)"}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

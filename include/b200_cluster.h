@@ -1,0 +1,123 @@
+/*
+ * b200_cluster.h — C ABI of the sm_100a neighbour-graph kernels.
+ *
+ * This is the boundary a maintainer of torch_cluster would bind instead of the
+ * reference's CUDA backend functions `knn_cuda` (csrc/cuda/knn_cuda.h:5-8) and
+ * `radius_cuda` (csrc/cuda/radius_cuda.h:5-9).  Everything is plain pointers
+ * and sizes: no torch types, no allocation inside (except where stated), all
+ * work is enqueued on the caller's stream.  All pointers are DEVICE pointers
+ * unless a parameter says otherwise.  Every function returns a B200C_* status;
+ * b200c_last_error() gives the message of the calling thread's last failure.
+ *
+ * Conventions shared with the reference operators:
+ *   x [n, dim], y [m, dim]   row-major, contiguous, dtype f32 or f64
+ *   ptr_x, ptr_y [num_segments + 1]   int64 segment boundaries (CSR style);
+ *                            NULL means one segment covering all rows
+ *   edge rows                row 0 = query (y) index, row 1 = point (x) index,
+ *                            global row numbers, ordered by query
+ */
+#ifndef B200_CLUSTER_H_
+#define B200_CLUSTER_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *b200c_stream_t; /* a cudaStream_t */
+
+enum {
+  B200C_OK = 0,
+  B200C_ERR_INVALID = 1,     /* bad argument ("Input mismatch" family)            */
+  B200C_ERR_UNSUPPORTED = 2, /* valid in the reference, not built here             */
+  B200C_ERR_CUDA = 3,        /* a CUDA runtime call or launch failed               */
+  B200C_ERR_WORKSPACE = 4,   /* workspace too small / scratch limit exceeded       */
+  B200C_ERR_DEVICE = 5       /* the GPU is not an sm_100 device                    */
+};
+
+enum { B200C_F32 = 0, B200C_F64 = 1 };
+
+/* Largest k accepted, as in the reference (csrc/cuda/knn_cuda.cu:98). */
+#define B200C_MAX_K 100
+
+int b200c_version(void);
+const char *b200c_last_error(void);
+
+/* Segment pointers from a sorted batch vector:
+ *   ptr[i] = number of entries of batch[0..n) that are < i,  i = 0..num_segments.
+ * Replaces `torch.bucketize(arange(B + 1), batch)` of torch_cluster/knn.py:77-79
+ * and torch_cluster/radius.py:82-84. */
+int b200c_segment_ptr(const int64_t *batch, int64_t n, int64_t num_segments,
+                      int64_t *ptr, b200c_stream_t stream);
+
+/* Exclusive prefix sum of per-query edge counts:
+ *   offsets[0] = 0, offsets[i + 1] = offsets[i] + counts[i];  offsets[m] = E.
+ * Replaces the mask + masked_select compaction of csrc/cuda/radius_cuda.cu:94-95
+ * and csrc/cuda/knn_cuda.cu:133-134.  `workspace` needs
+ * b200c_scan_workspace_bytes(m) bytes. */
+size_t b200c_scan_workspace_bytes(int64_t m);
+int b200c_exclusive_scan(const int32_t *counts, int64_t m, int64_t *offsets,
+                         void *workspace, size_t workspace_bytes,
+                         b200c_stream_t stream);
+
+/* k nearest neighbours — replaces knn_kernel + knn_cuda
+ * (csrc/cuda/knn_cuda.cu:30-84, 86-135).
+ *
+ * For every query row of y, the k points of x of the same segment with the
+ * smallest distance, ascending by (distance, x index); distance is the squared
+ * L2 norm accumulated as fma(d, d, acc) over ascending features, or, with
+ * `cosine`, 1 - dot / (|x| * |y|) as the reference evaluates it.  Candidates
+ * with distance >= 1e10 or NaN are never selected.
+ *
+ * Output (padded form): edge_padded is int64 [2, m * k]; slot q * k + e of row 0
+ * holds q, of row 1 the e-th neighbour or -1 when the segment had fewer than k
+ * admissible points.  counts[q] (int32 [m]) is the number of valid slots of q
+ * and *num_valid (one int64) their total.  When *num_valid == m * k the padded
+ * form already is the final edge_index; otherwise run b200c_exclusive_scan on
+ * counts and b200c_knn_compact.
+ *
+ * workspace: b200c_knn_workspace_bytes(...) bytes (may be 0). */
+size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t k,
+                                 int dtype, int cosine, int64_t num_segments);
+int b200c_knn(const void *x, const void *y, const int64_t *ptr_x,
+              const int64_t *ptr_y, int64_t num_segments, int64_t n, int64_t m,
+              int64_t dim, int64_t k, int dtype, int cosine,
+              int64_t *edge_padded, int32_t *counts, int64_t *num_valid,
+              void *workspace, size_t workspace_bytes, b200c_stream_t stream);
+
+/* Drops the -1 slots: edge_index (int64 [2, num_edges]) receives, for each
+ * query q, its counts[q] valid slots at offsets[q].. (csrc/cuda/knn_cuda.cu:133-134). */
+int b200c_knn_compact(const int64_t *edge_padded, const int32_t *counts,
+                      const int64_t *offsets, int64_t m, int64_t k,
+                      int64_t num_edges, int64_t *edge_index,
+                      b200c_stream_t stream);
+
+/* Fixed-radius search, pass 1 — replaces the scan of radius_kernel
+ * (csrc/cuda/radius_cuda.cu:26-41) without its -1 padded output:
+ *   counts[q] = min(max_num_neighbors, #{x in segment(q): dist < (T)(r * r),
+ *                                        and not (ignore_same_index and x == q)}).
+ * The comparison is strict and r * r is formed in double and narrowed to the
+ * data type (csrc/cuda/radius_cuda.cu:33, 90). */
+int b200c_radius_count(const void *x, const void *y, const int64_t *ptr_x,
+                       const int64_t *ptr_y, int64_t num_segments, int64_t n,
+                       int64_t m, int64_t dim, double r,
+                       int64_t max_num_neighbors, int ignore_same_index,
+                       int dtype, int32_t *counts, b200c_stream_t stream);
+
+/* Fixed-radius search, pass 2: writes, for each query q, its first counts[q]
+ * hits in ascending x order at offsets[q].. of edge_index (int64 [2, num_edges];
+ * row 0 = q, row 1 = x index) — the truncation rule of
+ * csrc/cuda/radius_cuda.cu:33-40.  offsets is the exclusive scan of counts. */
+int b200c_radius_fill(const void *x, const void *y, const int64_t *ptr_x,
+                      const int64_t *ptr_y, int64_t num_segments, int64_t n,
+                      int64_t m, int64_t dim, double r,
+                      int64_t max_num_neighbors, int ignore_same_index,
+                      int dtype, const int64_t *offsets, int64_t num_edges,
+                      int64_t *edge_index, b200c_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_CLUSTER_H_ */

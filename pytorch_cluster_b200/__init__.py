@@ -1,0 +1,16 @@
+"""B200-native neighbour-graph construction behind the torch_cluster API.
+
+``knn``, ``knn_graph``, ``radius`` and ``radius_graph`` keep the reference's signatures and run
+hand-written sm_100a CUDA kernels through ``torch.ops.torch_cluster.knn`` / ``radius``.
+Importing the package loads the in-tree native libraries and raises if they are not built.
+"""
+from . import _native
+
+_native.load_ops()
+
+from .knn import knn, knn_graph  # noqa: E402
+from .radius import radius, radius_graph  # noqa: E402
+
+__version__ = '0.1.0'
+
+__all__ = ['knn', 'knn_graph', 'radius', 'radius_graph', '__version__']

@@ -1,0 +1,96 @@
+"""Direct calls of the C ABI (include/b200_cluster.h) through ctypes on torch CUDA tensors:
+the same entry points the torch operator layer uses, without the operator layer.  Used by the
+GPU parity tests and the benchmark's kernel timing."""
+from __future__ import annotations
+
+import torch
+
+from . import _native
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dtype(x):
+    return {torch.float32: _native.B200C_F32, torch.float64: _native.B200C_F64}[x.dtype]
+
+
+def segment_ptr(batch, num_segments):
+    lib = _native.cabi()
+    ptr = torch.empty(num_segments + 1, dtype=torch.long, device=batch.device)
+    _native.check(lib.b200c_segment_ptr(_p(batch), batch.numel(), num_segments, _p(ptr), _stream()))
+    return ptr
+
+
+def exclusive_scan(counts):
+    lib = _native.cabi()
+    m = counts.numel()
+    offsets = torch.empty(m + 1, dtype=torch.long, device=counts.device)
+    nbytes = lib.b200c_scan_workspace_bytes(m)
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=counts.device)
+    _native.check(lib.b200c_exclusive_scan(_p(counts), m, _p(offsets), _p(ws), nbytes, _stream()))
+    return offsets
+
+
+def knn_padded_nosync(x, y, k, ptr_x=None, ptr_y=None, cosine=False):
+    """-> (edge_padded int64 [2, m*k], counts int32 [m], num_valid int64 [1]); nothing is read back."""
+    lib = _native.cabi()
+    n, m, dim = x.shape[0], y.shape[0], x.shape[1]
+    nseg = 1 if ptr_x is None else ptr_x.numel() - 1
+    padded = torch.empty(2, m * k, dtype=torch.long, device=x.device)
+    counts = torch.empty(m, dtype=torch.int32, device=x.device)
+    nvalid = torch.empty(1, dtype=torch.long, device=x.device)
+    nbytes = lib.b200c_knn_workspace_bytes(n, m, dim, k, _dtype(x), int(cosine), nseg)
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+    _native.check(lib.b200c_knn(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, k, _dtype(x),
+                                int(cosine), _p(padded), _p(counts), _p(nvalid), _p(ws), nbytes, _stream()))
+    return padded, counts, nvalid
+
+
+def knn_padded(x, y, k, ptr_x=None, ptr_y=None, cosine=False):
+    """-> (edge_padded int64 [2, m*k], counts int32 [m], num_valid int)"""
+    padded, counts, nvalid = knn_padded_nosync(x, y, k, ptr_x, ptr_y, cosine)
+    return padded, counts, int(nvalid.item())
+
+
+def knn(x, y, k, ptr_x=None, ptr_y=None, cosine=False):
+    """Compacted edge_index through b200c_knn (+ scan + compact when needed)."""
+    lib = _native.cabi()
+    padded, counts, nvalid = knn_padded(x, y, k, ptr_x, ptr_y, cosine)
+    m = y.shape[0]
+    if nvalid == m * k:
+        return padded
+    offsets = exclusive_scan(counts)
+    out = torch.empty(2, nvalid, dtype=torch.long, device=x.device)
+    _native.check(lib.b200c_knn_compact(_p(padded), _p(counts), _p(offsets), m, k, nvalid, _p(out), _stream()))
+    return out
+
+
+def radius_counts(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_index=False):
+    lib = _native.cabi()
+    n, m, dim = x.shape[0], y.shape[0], x.shape[1]
+    nseg = 1 if ptr_x is None else ptr_x.numel() - 1
+    counts = torch.empty(m, dtype=torch.int32, device=x.device)
+    _native.check(lib.b200c_radius_count(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, float(r),
+                                         max_num_neighbors, int(ignore_same_index), _dtype(x), _p(counts),
+                                         _stream()))
+    return counts
+
+
+def radius(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_index=False):
+    lib = _native.cabi()
+    n, m, dim = x.shape[0], y.shape[0], x.shape[1]
+    nseg = 1 if ptr_x is None else ptr_x.numel() - 1
+    counts = radius_counts(x, y, r, ptr_x, ptr_y, max_num_neighbors, ignore_same_index)
+    offsets = exclusive_scan(counts)
+    total = int(offsets[-1].item())
+    out = torch.empty(2, total, dtype=torch.long, device=x.device)
+    _native.check(lib.b200c_radius_fill(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, float(r),
+                                        max_num_neighbors, int(ignore_same_index), _dtype(x), _p(offsets),
+                                        total, _p(out), _stream()))
+    return out

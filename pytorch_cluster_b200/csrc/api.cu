@@ -1,0 +1,146 @@
+// extern "C" entry points: argument checks (the reference's "Input mismatch" rules,
+// csrc/cuda/knn_cuda.cu:91-114 and csrc/cuda/radius_cuda.cu:50-73, as far as they can be
+// checked on raw pointers) and kernel selection.
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+#include "launchers.h"
+
+namespace b200c {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+// The kernels are built for sm_100a only; refuse other devices with a clear message instead of
+// a launch failure.
+static int check_device() {
+  static thread_local int checked_device = -1;
+  int dev = 0;
+  B200C_CUDA(cudaGetDevice(&dev));
+  if (dev == checked_device) return B200C_OK;
+  int major = 0;
+  B200C_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10) {
+    set_error("device %d has compute capability %d.x; this library is built for sm_100a only", dev, major);
+    return B200C_ERR_DEVICE;
+  }
+  checked_device = dev;
+  return B200C_OK;
+}
+
+static int check_common(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                        int64_t num_segments, int64_t n, int64_t m, int64_t dim, int dtype) {
+  B200C_CHECK_ARG(x != nullptr && y != nullptr, "x and y must be CUDA tensors");
+  B200C_CHECK_ARG(n >= 0 && m >= 0 && dim >= 1, "Input mismatch");
+  B200C_CHECK_ARG(n <= 0x7fffffffLL && m <= 0x7fffffffLL, "more than 2^31-1 rows are not supported");
+  B200C_CHECK_ARG(dtype == B200C_F32 || dtype == B200C_F64, "unsupported dtype");
+  B200C_CHECK_ARG((ptr_x == nullptr) == (ptr_y == nullptr), "Input mismatch");
+  B200C_CHECK_ARG(ptr_x == nullptr ? num_segments == 1 : (num_segments >= 1 && num_segments <= 0x7fffffffLL),
+                  "Input mismatch");
+  return B200C_OK;
+}
+
+}  // namespace b200c
+
+using namespace b200c;
+
+extern "C" int b200c_version(void) { return 100; }
+
+extern "C" const char *b200c_last_error(void) { return g_error; }
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+extern "C" size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t k, int dtype, int cosine,
+                                            int64_t num_segments) {
+  (void)dim; (void)k; (void)num_segments;
+  const size_t elem = dtype == B200C_F64 ? 8 : 4;
+  // cosine: |row| of every x and y row
+  return cosine ? align256((size_t)n * elem) + align256((size_t)m * elem) : 0;
+}
+
+extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                         int64_t num_segments, int64_t n, int64_t m, int64_t dim, int64_t k, int dtype,
+                         int cosine, int64_t *edge_padded, int32_t *counts, int64_t *num_valid,
+                         void *workspace, size_t workspace_bytes, b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int st = check_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, dtype);
+  if (st != B200C_OK) return st;
+  B200C_CHECK_ARG(k >= 1, "`k` needs to be positive");
+  B200C_CHECK_ARG(k <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
+  B200C_CHECK_ARG(edge_padded && counts && num_valid, "null output pointer");
+  if ((st = check_device()) != B200C_OK) return st;
+  B200C_CUDA(cudaMemsetAsync(num_valid, 0, sizeof(int64_t), stream));
+  if (m == 0) return B200C_OK;
+
+  B200C_CHECK_ARG(dim <= 0x7fffffffLL / 4, "Input mismatch");
+  const size_t need = b200c_knn_workspace_bytes(n, m, dim, k, dtype, cosine, num_segments);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need)) {
+    set_error("kNN workspace too small: %zu < %zu", workspace_bytes, need);
+    return B200C_ERR_WORKSPACE;
+  }
+  KnnArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, (int)k, cosine, nullptr, nullptr,
+            edge_padded, edge_padded + m * k, counts, (unsigned long long *)num_valid, stream};
+  const bool f32 = dtype == B200C_F32;
+  if (cosine) {
+    const size_t elem = f32 ? 4 : 8;
+    char *ws = (char *)workspace;
+    a.norms_x = ws;
+    a.norms_y = ws + align256((size_t)n * elem);
+    st = f32 ? launch_row_norms_f32(x, n, (int)dim, (void *)a.norms_x, stream)
+             : launch_row_norms_f64(x, n, (int)dim, (void *)a.norms_x, stream);
+    if (st != B200C_OK) return st;
+    st = f32 ? launch_row_norms_f32(y, m, (int)dim, (void *)a.norms_y, stream)
+             : launch_row_norms_f64(y, m, (int)dim, (void *)a.norms_y, stream);
+    if (st != B200C_OK) return st;
+    return f32 ? launch_knn_generic_f32(a) : launch_knn_generic_f64(a);
+  }
+  if (dim <= 8) return f32 ? launch_knn_lowd_f32(a) : launch_knn_lowd_f64(a);
+  return f32 ? launch_knn_generic_f32(a) : launch_knn_generic_f64(a);
+}
+
+static int radius_common(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                         int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
+                         int64_t max_num_neighbors, int ignore_same_index, int dtype, int32_t *counts,
+                         const int64_t *offsets, int64_t *out_row, int64_t *out_col, bool fill,
+                         cudaStream_t stream) {
+  int st = check_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, dtype);
+  if (st != B200C_OK) return st;
+  B200C_CHECK_ARG(max_num_neighbors >= 1, "max_num_neighbors must be positive");
+  if ((st = check_device()) != B200C_OK) return st;
+  if (m == 0) return B200C_OK;
+  RadiusArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, r, max_num_neighbors,
+               ignore_same_index, counts, offsets, out_row, out_col, stream};
+  B200C_CHECK_ARG(dim <= 0x7fffffffLL / 4, "Input mismatch");
+  if (dim <= 8) return dtype == B200C_F32 ? launch_radius_lowd_f32(a, fill) : launch_radius_lowd_f64(a, fill);
+  return dtype == B200C_F32 ? launch_radius_generic_f32(a, fill) : launch_radius_generic_f64(a, fill);
+}
+
+extern "C" int b200c_radius_count(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                                  int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
+                                  int64_t max_num_neighbors, int ignore_same_index, int dtype,
+                                  int32_t *counts, b200c_stream_t stream) {
+  B200C_CHECK_ARG(counts != nullptr || m == 0, "null output pointer");
+  return radius_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
+                       ignore_same_index, dtype, counts, nullptr, nullptr, nullptr, false,
+                       (cudaStream_t)stream);
+}
+
+extern "C" int b200c_radius_fill(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                                 int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
+                                 int64_t max_num_neighbors, int ignore_same_index, int dtype,
+                                 const int64_t *offsets, int64_t num_edges, int64_t *edge_index,
+                                 b200c_stream_t stream) {
+  B200C_CHECK_ARG(num_edges >= 0, "Input mismatch");
+  if (num_edges == 0) return B200C_OK;
+  B200C_CHECK_ARG(offsets != nullptr && edge_index != nullptr, "null pointer");
+  return radius_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
+                       ignore_same_index, dtype, nullptr, offsets, edge_index, edge_index + num_edges,
+                       true, (cudaStream_t)stream);
+}

@@ -1,0 +1,50 @@
+// Internal launch entry points (one per translation unit, so that the template instantiations
+// compile in parallel).  Each returns a B200C_* status.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200c {
+
+struct KnnArgs {
+  const void *x, *y;
+  const int64_t *ptr_x, *ptr_y;
+  int num_segments;
+  int64_t n, m;
+  int dim, k;
+  int cosine;
+  const void *norms_x, *norms_y;  // cosine only: |row| of x and y
+  int64_t *out_row, *out_col;
+  int32_t *counts;
+  unsigned long long *num_valid;
+  cudaStream_t stream;
+};
+
+struct RadiusArgs {
+  const void *x, *y;
+  const int64_t *ptr_x, *ptr_y;
+  int num_segments;
+  int64_t n, m;
+  int dim;
+  double r;
+  int64_t max_nn;
+  int ignore_same;
+  int32_t *counts;          // count pass
+  const int64_t *offsets;   // fill pass
+  int64_t *out_row, *out_col;
+  cudaStream_t stream;
+};
+
+int launch_knn_lowd_f32(const KnnArgs &a);
+int launch_knn_lowd_f64(const KnnArgs &a);
+int launch_radius_lowd_f32(const RadiusArgs &a, bool fill);
+int launch_radius_lowd_f64(const RadiusArgs &a, bool fill);
+int launch_knn_generic_f32(const KnnArgs &a);
+int launch_knn_generic_f64(const KnnArgs &a);
+int launch_radius_generic_f32(const RadiusArgs &a, bool fill);
+int launch_radius_generic_f64(const RadiusArgs &a, bool fill);
+int launch_row_norms_f32(const void *a, int64_t rows, int dim, void *out, cudaStream_t s);
+int launch_row_norms_f64(const void *a, int64_t rows, int dim, void *out, cudaStream_t s);
+
+}  // namespace b200c

@@ -1,0 +1,189 @@
+// Small HBM-bound passes around the search kernels: segment pointers, the exclusive scan of the
+// per-query edge counts, and the compaction of padded kNN output.
+#include "common.cuh"
+#include "launchers.h"
+
+namespace b200c {
+
+// ---- segment pointers ----------------------------------------------------------------------------
+// ptr[i] = lower_bound(batch, i): one thread per boundary bisects the sorted batch vector
+// (torch.bucketize(arange(B + 1), batch), torch_cluster/knn.py:77-79).
+__global__ void segment_ptr_kernel(const int64_t *__restrict__ batch, int64_t n, int64_t num_segments,
+                                   int64_t *__restrict__ ptr) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > num_segments) return;
+  int64_t lo = 0, hi = n;
+  while (lo < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (batch[mid] < i)
+      lo = mid + 1;
+    else
+      hi = mid;
+  }
+  ptr[i] = lo;
+}
+
+// ---- exclusive scan, int32 counts -> int64 offsets --------------------------------------------------
+constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_ITEMS = 8;
+constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;
+
+__device__ __forceinline__ int64_t block_exclusive_scan(int64_t v, int64_t *total, int64_t *warp_sums) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int64_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int64_t t = __shfl_up_sync(FULL_MASK, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int64_t w = lane < SCAN_THREADS / 32 ? warp_sums[lane] : 0;
+    int64_t winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int64_t t = __shfl_up_sync(FULL_MASK, winc, o);
+      if (lane >= o) winc += t;
+    }
+    if (lane < SCAN_THREADS / 32) warp_sums[lane] = winc - w;
+    if (lane == SCAN_THREADS / 32 - 1) *total = winc;
+  }
+  __syncthreads();
+  return inc - v + warp_sums[warp];
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_tile_sums_kernel(const int32_t *__restrict__ counts, int64_t m, int64_t *__restrict__ tile_sums) {
+  __shared__ int64_t warp_sums[SCAN_THREADS / 32];
+  const int64_t base = (int64_t)blockIdx.x * SCAN_TILE;
+  int64_t s = 0;
+#pragma unroll
+  for (int i = 0; i < SCAN_ITEMS; ++i) {
+    const int64_t j = base + (int64_t)i * SCAN_THREADS + threadIdx.x;
+    if (j < m) s += counts[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL_MASK, s, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int64_t t = 0;
+    for (int w = 0; w < SCAN_THREADS / 32; ++w) t += warp_sums[w];
+    tile_sums[blockIdx.x] = t;
+  }
+}
+
+// One CTA turns the tile sums into exclusive tile offsets (in place) and stores the grand total.
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_tile_offsets_kernel(int64_t *__restrict__ tile_sums, int64_t num_tiles, int64_t *__restrict__ total_out) {
+  __shared__ int64_t warp_sums[SCAN_THREADS / 32];
+  __shared__ int64_t block_total;
+  int64_t carry = 0;
+  for (int64_t base = 0; base < num_tiles; base += SCAN_THREADS) {
+    const int64_t j = base + threadIdx.x;
+    const int64_t v = j < num_tiles ? tile_sums[j] : 0;
+    const int64_t ex = block_exclusive_scan(v, &block_total, warp_sums);
+    if (j < num_tiles) tile_sums[j] = carry + ex;
+    carry += block_total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *total_out = carry;
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_apply_kernel(const int32_t *__restrict__ counts, int64_t m, const int64_t *__restrict__ tile_offsets,
+                  int64_t *__restrict__ offsets) {
+  __shared__ int64_t warp_sums[SCAN_THREADS / 32];
+  __shared__ int64_t block_total;
+  // thread t owns SCAN_ITEMS consecutive elements so that one block scan suffices
+  const int64_t first = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
+  int32_t v[SCAN_ITEMS];
+  int64_t s = 0;
+#pragma unroll
+  for (int i = 0; i < SCAN_ITEMS; ++i) {
+    v[i] = first + i < m ? counts[first + i] : 0;
+    s += v[i];
+  }
+  int64_t run = tile_offsets[blockIdx.x] + block_exclusive_scan(s, &block_total, warp_sums);
+#pragma unroll
+  for (int i = 0; i < SCAN_ITEMS; ++i) {
+    if (first + i < m) offsets[first + i] = run;
+    run += v[i];
+  }
+}
+
+// ---- compaction of padded kNN output ------------------------------------------------------------------
+__global__ void knn_compact_kernel(const int64_t *__restrict__ col_padded, const int32_t *__restrict__ counts,
+                                   const int64_t *__restrict__ offsets, int64_t m, int k,
+                                   int64_t *__restrict__ out_row, int64_t *__restrict__ out_col) {
+  const int64_t slot = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (slot >= m * k) return;
+  const int64_t q = slot / k;
+  const int e = (int)(slot - q * k);
+  if (e < counts[q]) {
+    const int64_t o = offsets[q] + e;
+    out_row[o] = q;
+    out_col[o] = col_padded[slot];
+  }
+}
+
+}  // namespace b200c
+
+using namespace b200c;
+
+extern "C" int b200c_segment_ptr(const int64_t *batch, int64_t n, int64_t num_segments, int64_t *ptr,
+                                 b200c_stream_t stream) {
+  B200C_CHECK_ARG(n >= 0 && num_segments >= 0, "Input mismatch");
+  B200C_CHECK_ARG(ptr != nullptr && (batch != nullptr || n == 0), "null pointer");
+  const int64_t total = num_segments + 1;
+  const int threads = 128;
+  segment_ptr_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(
+      batch, n, num_segments, ptr);
+  B200C_LAUNCH_CHECK("segment_ptr_kernel");
+  return B200C_OK;
+}
+
+extern "C" size_t b200c_scan_workspace_bytes(int64_t m) {
+  const int64_t tiles = m > 0 ? (m + SCAN_TILE - 1) / SCAN_TILE : 1;
+  return (size_t)tiles * sizeof(int64_t);
+}
+
+extern "C" int b200c_exclusive_scan(const int32_t *counts, int64_t m, int64_t *offsets, void *workspace,
+                                    size_t workspace_bytes, b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  B200C_CHECK_ARG(m >= 0, "Input mismatch");
+  B200C_CHECK_ARG(offsets != nullptr, "null pointer");
+  if (m == 0) {
+    B200C_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int64_t), stream));
+    return B200C_OK;
+  }
+  B200C_CHECK_ARG(counts != nullptr && workspace != nullptr, "null pointer");
+  if (workspace_bytes < b200c_scan_workspace_bytes(m)) {
+    set_error("scan workspace too small: %zu < %zu", workspace_bytes, b200c_scan_workspace_bytes(m));
+    return B200C_ERR_WORKSPACE;
+  }
+  const int64_t tiles = (m + SCAN_TILE - 1) / SCAN_TILE;
+  int64_t *tile_sums = (int64_t *)workspace;
+  scan_tile_sums_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, stream>>>(counts, m, tile_sums);
+  B200C_LAUNCH_CHECK("scan_tile_sums_kernel");
+  scan_tile_offsets_kernel<<<1, SCAN_THREADS, 0, stream>>>(tile_sums, tiles, offsets + m);
+  B200C_LAUNCH_CHECK("scan_tile_offsets_kernel");
+  scan_apply_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, stream>>>(counts, m, tile_sums, offsets);
+  B200C_LAUNCH_CHECK("scan_apply_kernel");
+  return B200C_OK;
+}
+
+extern "C" int b200c_knn_compact(const int64_t *edge_padded, const int32_t *counts, const int64_t *offsets,
+                                 int64_t m, int64_t k, int64_t num_edges, int64_t *edge_index,
+                                 b200c_stream_t stream) {
+  B200C_CHECK_ARG(m >= 0 && k >= 1 && k <= B200C_MAX_K && num_edges >= 0, "Input mismatch");
+  if (m == 0 || num_edges == 0) return B200C_OK;
+  B200C_CHECK_ARG(edge_padded && counts && offsets && edge_index, "null pointer");
+  const int64_t slots = m * k;
+  const int threads = 256;
+  knn_compact_kernel<<<(unsigned)((slots + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(
+      edge_padded + slots, counts, offsets, m, (int)k, edge_index, edge_index + num_edges);
+  B200C_LAUNCH_CHECK("knn_compact_kernel");
+  return B200C_OK;
+}

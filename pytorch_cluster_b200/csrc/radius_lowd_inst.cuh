@@ -1,0 +1,53 @@
+// Dispatch of radius_lowd_kernel over DIM; included once per data type.
+#pragma once
+
+#include "launchers.h"
+#include "radius_lowd.cuh"
+
+namespace b200c {
+
+template <typename T, int DIM, bool FILL>
+static int launch_radius_lowd_one(const RadiusArgs &a) {
+  using Cfg = RadiusLowD<T, DIM>;
+  auto kern = radius_lowd_kernel<T, DIM, FILL>;
+  static bool configured = false;
+  if (!configured) {
+    B200C_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)Cfg::SMEM_BYTES));
+    configured = true;
+  }
+  const int64_t tiles = (a.m + Cfg::TQ - 1) / Cfg::TQ;
+  if (tiles > 0x7fffffffLL) {
+    set_error("too many query tiles");
+    return B200C_ERR_INVALID;
+  }
+  const T r2 = (T)(a.r * a.r);  // formed in double, narrowed once (csrc/cuda/radius_cuda.cu:90)
+  kern<<<(unsigned)tiles, CTA_THREADS, Cfg::SMEM_BYTES, a.stream>>>(
+      (const T *)a.x, (const T *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, r2, a.max_nn,
+      a.ignore_same, a.counts, a.offsets, a.out_row, a.out_col);
+  B200C_LAUNCH_CHECK("radius_lowd_kernel");
+  return B200C_OK;
+}
+
+template <typename T, int DIM>
+static int launch_radius_lowd_dim(const RadiusArgs &a, bool fill) {
+  return fill ? launch_radius_lowd_one<T, DIM, true>(a) : launch_radius_lowd_one<T, DIM, false>(a);
+}
+
+template <typename T>
+static int launch_radius_lowd(const RadiusArgs &a, bool fill) {
+  switch (a.dim) {
+    case 1: return launch_radius_lowd_dim<T, 1>(a, fill);
+    case 2: return launch_radius_lowd_dim<T, 2>(a, fill);
+    case 3: return launch_radius_lowd_dim<T, 3>(a, fill);
+    case 4: return launch_radius_lowd_dim<T, 4>(a, fill);
+    case 5: return launch_radius_lowd_dim<T, 5>(a, fill);
+    case 6: return launch_radius_lowd_dim<T, 6>(a, fill);
+    case 7: return launch_radius_lowd_dim<T, 7>(a, fill);
+    case 8: return launch_radius_lowd_dim<T, 8>(a, fill);
+  }
+  set_error("low-dimensional radius kernel called with dim=%d", a.dim);
+  return B200C_ERR_INVALID;
+}
+
+}  // namespace b200c

@@ -1,0 +1,167 @@
+// Torch operator layer: registers `torch_cluster::knn` and `torch_cluster::radius` with the
+// schemas of the reference (csrc/knn.cpp:22-40, csrc/radius.cpp:22-39) and forwards to the C ABI
+// of include/b200_cluster.h.  Host logic only: argument checks with the reference's messages
+// (csrc/cuda/utils.cuh:5-9, csrc/cuda/knn_cuda.cu:91-114), output allocation through the ATen
+// caching allocator, the caller's current stream, and one device-to-host read of the edge
+// count where the output size depends on the data.  There is no CPU branch: a CPU tensor is an
+// error here, not a fallback.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/script.h>
+
+#include "b200_cluster.h"
+
+namespace {
+
+#define CHECK_CUDA(x) TORCH_CHECK(x.device().is_cuda(), #x " must be CUDA tensor")
+#define CHECK_INPUT(x) TORCH_CHECK(x, "Input mismatch")
+#define CHECK_CONTIGUOUS(x) TORCH_CHECK(x.is_contiguous(), #x " must be contiguous")
+
+void check_status(int status) {
+  TORCH_CHECK(status == B200C_OK, "b200_cluster: ", b200c_last_error());
+}
+
+// fp16 / bf16 inputs are widened to fp32 (every fp16/bf16 value is an fp32 value); the search
+// then runs with fp32 accumulation.
+torch::Tensor as_supported(const torch::Tensor &t) {
+  const auto st = t.scalar_type();
+  if (st == at::kHalf || st == at::kBFloat16) return t.to(at::kFloat);
+  TORCH_CHECK(st == at::kFloat || st == at::kDouble, "expected a floating point tensor, got ", st);
+  return t;
+}
+
+struct Prepared {
+  torch::Tensor x, y, ptr_x, ptr_y;
+  const int64_t *px = nullptr, *py = nullptr;
+  int64_t num_segments = 1;
+  int dtype = B200C_F32;
+};
+
+Prepared prepare(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
+                 std::optional<torch::Tensor> ptr_y) {
+  CHECK_CUDA(x);
+  CHECK_CONTIGUOUS(x);
+  CHECK_INPUT(x.dim() == 2);
+  CHECK_CUDA(y);
+  CHECK_CONTIGUOUS(y);
+  CHECK_INPUT(y.dim() == 2);
+  CHECK_INPUT(x.size(1) == y.size(1));
+  CHECK_INPUT(x.get_device() == y.get_device());
+  CHECK_INPUT(x.scalar_type() == y.scalar_type());
+
+  Prepared p;
+  p.x = as_supported(x);
+  p.y = as_supported(y);
+  p.dtype = p.x.scalar_type() == at::kDouble ? B200C_F64 : B200C_F32;
+
+  if (ptr_x.has_value() || ptr_y.has_value()) {
+    // a missing side defaults to one segment over all rows (csrc/cuda/knn_cuda.cu:100-112)
+    const auto opts = x.options().dtype(torch::kLong);
+    p.ptr_x = ptr_x.has_value() ? ptr_x.value() : torch::arange(0, x.size(0) + 1, x.size(0) > 0 ? x.size(0) : 1, opts);
+    p.ptr_y = ptr_y.has_value() ? ptr_y.value() : torch::arange(0, y.size(0) + 1, y.size(0) > 0 ? y.size(0) : 1, opts);
+    CHECK_CUDA(p.ptr_x);
+    CHECK_INPUT(p.ptr_x.dim() == 1);
+    CHECK_CUDA(p.ptr_y);
+    CHECK_INPUT(p.ptr_y.dim() == 1);
+    CHECK_INPUT(p.ptr_x.numel() == p.ptr_y.numel());
+    CHECK_INPUT(p.ptr_x.numel() >= 2);
+    TORCH_CHECK(p.ptr_x.scalar_type() == at::kLong && p.ptr_y.scalar_type() == at::kLong,
+                "ptr_x and ptr_y must be int64 tensors");
+    p.ptr_x = p.ptr_x.contiguous();
+    p.ptr_y = p.ptr_y.contiguous();
+    p.px = p.ptr_x.data_ptr<int64_t>();
+    p.py = p.ptr_y.data_ptr<int64_t>();
+    p.num_segments = p.ptr_x.numel() - 1;
+  }
+  return p;
+}
+
+torch::Tensor knn(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
+                  std::optional<torch::Tensor> ptr_y, int64_t k, bool cosine, int64_t num_workers) {
+  (void)num_workers;  // no effect on the GPU, as in the reference
+  Prepared p = prepare(x, y, ptr_x, ptr_y);
+  TORCH_CHECK(k <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
+  TORCH_CHECK(k >= 1, "`k` needs to be positive");
+
+  c10::cuda::CUDAGuard guard(x.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const auto lopts = x.options().dtype(torch::kLong);
+  const int64_t n = p.x.size(0), m = p.y.size(0), dim = p.x.size(1);
+  if (m == 0) return torch::empty({2, 0}, lopts);
+
+  auto padded = torch::empty({2, m * k}, lopts);
+  auto counts = torch::empty({m}, x.options().dtype(torch::kInt));
+  auto num_valid = torch::empty({1}, lopts);
+  const size_t ws_bytes = b200c_knn_workspace_bytes(n, m, dim, k, p.dtype, cosine, p.num_segments);
+  auto ws = torch::empty({(int64_t)ws_bytes}, x.options().dtype(torch::kByte));
+
+  check_status(b200c_knn(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, k, p.dtype,
+                         cosine ? 1 : 0, padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(),
+                         num_valid.data_ptr<int64_t>(), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                         stream.stream()));
+  const int64_t total = num_valid.item<int64_t>();  // the one host sync: the output size
+  if (total == m * k) return padded;
+
+  // some query had fewer than k admissible points: drop the -1 slots
+  auto offsets = torch::empty({m + 1}, lopts);
+  const size_t scan_bytes = b200c_scan_workspace_bytes(m);
+  auto scan_ws = torch::empty({(int64_t)scan_bytes}, x.options().dtype(torch::kByte));
+  check_status(b200c_exclusive_scan(counts.data_ptr<int32_t>(), m, offsets.data_ptr<int64_t>(),
+                                    scan_ws.data_ptr(), scan_bytes, stream.stream()));
+  auto out = torch::empty({2, total}, lopts);
+  check_status(b200c_knn_compact(padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(),
+                                 offsets.data_ptr<int64_t>(), m, k, total, out.data_ptr<int64_t>(),
+                                 stream.stream()));
+  return out;
+}
+
+torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
+                     std::optional<torch::Tensor> ptr_y, double r, int64_t max_num_neighbors,
+                     int64_t num_workers, bool ignore_same_index) {
+  (void)num_workers;
+  Prepared p = prepare(x, y, ptr_x, ptr_y);
+
+  c10::cuda::CUDAGuard guard(x.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const auto lopts = x.options().dtype(torch::kLong);
+  const int64_t n = p.x.size(0), m = p.y.size(0), dim = p.x.size(1);
+  if (m == 0 || max_num_neighbors <= 0) return torch::empty({2, 0}, lopts);
+
+  auto counts = torch::empty({m}, x.options().dtype(torch::kInt));
+  check_status(b200c_radius_count(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
+                                  max_num_neighbors, ignore_same_index ? 1 : 0, p.dtype,
+                                  counts.data_ptr<int32_t>(), stream.stream()));
+  auto offsets = torch::empty({m + 1}, lopts);
+  const size_t scan_bytes = b200c_scan_workspace_bytes(m);
+  auto scan_ws = torch::empty({(int64_t)scan_bytes}, x.options().dtype(torch::kByte));
+  check_status(b200c_exclusive_scan(counts.data_ptr<int32_t>(), m, offsets.data_ptr<int64_t>(),
+                                    scan_ws.data_ptr(), scan_bytes, stream.stream()));
+  const int64_t total = offsets[m].item<int64_t>();  // the one host sync: the output size
+  auto out = torch::empty({2, total}, lopts);
+  check_status(b200c_radius_fill(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
+                                 max_num_neighbors, ignore_same_index ? 1 : 0, p.dtype,
+                                 offsets.data_ptr<int64_t>(), total, out.data_ptr<int64_t>(), stream.stream()));
+  return out;
+}
+
+// Device-side construction of the segment pointers from a sorted batch vector
+// (what torch_cluster/knn.py:77-79 does with torch.bucketize).
+torch::Tensor segment_ptr(torch::Tensor batch, int64_t num_segments) {
+  CHECK_CUDA(batch);
+  CHECK_INPUT(batch.dim() == 1);
+  TORCH_CHECK(batch.scalar_type() == at::kLong, "batch must be an int64 tensor");
+  CHECK_INPUT(num_segments >= 0);
+  batch = batch.contiguous();
+  c10::cuda::CUDAGuard guard(batch.device());
+  auto ptr = torch::empty({num_segments + 1}, batch.options());
+  check_status(b200c_segment_ptr(batch.data_ptr<int64_t>(), batch.numel(), num_segments,
+                                 ptr.data_ptr<int64_t>(), at::cuda::getCurrentCUDAStream().stream()));
+  return ptr;
+}
+
+}  // namespace
+
+static auto registry = torch::RegisterOperators()
+                           .op("torch_cluster::knn", &knn)
+                           .op("torch_cluster::radius", &radius)
+                           .op("torch_cluster::segment_ptr", &segment_ptr);

@@ -1,0 +1,92 @@
+"""``knn`` / ``knn_graph`` with the reference's signatures (torch_cluster/knn.py:6-15, 85-94),
+TorchScript-able, on top of ``torch.ops.torch_cluster.knn``."""
+from typing import Optional, Tuple
+
+import torch
+
+
+def _num_segments(rows: int, batch: Optional[torch.Tensor]) -> int:
+    # `batch` is sorted (a documented precondition, torch_cluster/knn.py:27), so its largest
+    # id is its last entry: one element crosses to the host instead of a reduction.
+    if batch is None:
+        return 1
+    assert rows == batch.numel()
+    return int(batch[-1]) + 1
+
+
+def _segment_ptrs(x: torch.Tensor, y: torch.Tensor, batch_x: Optional[torch.Tensor],
+                  batch_y: Optional[torch.Tensor],
+                  batch_size: Optional[int]) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """Segment boundaries of x and y rows (torch_cluster/knn.py:62-79): B is inferred from the
+    batch vectors unless given, and pointers are only built for B > 1."""
+    num_segments = 1
+    if batch_size is None:
+        num_segments = max(_num_segments(x.size(0), batch_x), _num_segments(y.size(0), batch_y))
+    else:
+        num_segments = batch_size
+    assert num_segments > 0
+    ptr_x: Optional[torch.Tensor] = None
+    ptr_y: Optional[torch.Tensor] = None
+    if num_segments > 1:
+        assert batch_x is not None
+        assert batch_y is not None
+        ptr_x = torch.ops.torch_cluster.segment_ptr(batch_x, num_segments)
+        ptr_y = torch.ops.torch_cluster.segment_ptr(batch_y, num_segments)
+    return ptr_x, ptr_y
+
+
+def knn(
+    x: torch.Tensor,
+    y: torch.Tensor,
+    k: int,
+    batch_x: Optional[torch.Tensor] = None,
+    batch_y: Optional[torch.Tensor] = None,
+    cosine: bool = False,
+    num_workers: int = 1,
+    batch_size: Optional[int] = None,
+) -> torch.Tensor:
+    r"""For each row of :obj:`y`, the :obj:`k` nearest rows of :obj:`x` (of the same example).
+
+    Arguments as in the reference: :obj:`batch_x` / :obj:`batch_y` are sorted ``int64`` example ids,
+    :obj:`cosine` selects the cosine distance, :obj:`num_workers` has no effect on the GPU,
+    :obj:`batch_size` skips the inference of the number of examples.  Returns ``int64 [2, E]``:
+    row 0 indexes :obj:`y`, row 1 indexes :obj:`x`; per query ascending by (distance, index).
+    Inputs must be CUDA tensors.
+    """
+    if x.numel() == 0 or y.numel() == 0:
+        return torch.empty(2, 0, dtype=torch.long, device=x.device)
+    if x.dim() == 1:
+        x = x.view(-1, 1)
+    if y.dim() == 1:
+        y = y.view(-1, 1)
+    x = x.contiguous()
+    y = y.contiguous()
+    ptr_x, ptr_y = _segment_ptrs(x, y, batch_x, batch_y, batch_size)
+    return torch.ops.torch_cluster.knn(x, y, ptr_x, ptr_y, k, cosine, num_workers)
+
+
+def knn_graph(
+    x: torch.Tensor,
+    k: int,
+    batch: Optional[torch.Tensor] = None,
+    loop: bool = False,
+    flow: str = 'source_to_target',
+    cosine: bool = False,
+    num_workers: int = 1,
+    batch_size: Optional[int] = None,
+) -> torch.Tensor:
+    r"""Edges from every node to its :obj:`k` nearest nodes.
+
+    As the reference does (torch_cluster/knn.py:131-144): search k (+1 without self loops)
+    neighbours of x in x, orient by :obj:`flow`, and drop the ``row == col`` entries when
+    :obj:`loop` is false.
+    """
+    assert flow in ['source_to_target', 'target_to_source']
+    found = knn(x, x, k if loop else k + 1, batch, batch, cosine, num_workers, batch_size)
+    query, neighbour = found[0], found[1]
+    if not loop:
+        keep = query != neighbour
+        query, neighbour = query[keep], neighbour[keep]
+    if flow == 'source_to_target':
+        return torch.stack([neighbour, query], dim=0)
+    return torch.stack([query, neighbour], dim=0)

@@ -1,0 +1,255 @@
+"""GPU parity through the C ABI: the sm_100a kernels against the CPU oracle, bit for bit
+(index work, so the bar is exact equality — including the order inside each query)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import neighbor_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"f32": torch.float32, "f64": torch.float64}
+
+
+def _segments(sizes):
+    return torch.tensor(np.concatenate([[0], np.cumsum(sizes)]), dtype=torch.long)
+
+
+def _data(seed, n, m, dim, dtype, scale=1.0, grid=None):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, dim, generator=g, dtype=dtype) * scale
+    y = torch.randn(m, dim, generator=g, dtype=dtype) * scale
+    if grid:  # snap to a coarse grid: many exactly equal distances
+        x, y = torch.round(x * grid) / grid, torch.round(y * grid) / grid
+    return x, y
+
+
+def _check_knn(x, y, k, px=None, py=None, cosine=False):
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    dx, dy = x.to(DEV), y.to(DEV)
+    dpx = None if px is None else px.to(DEV)
+    dpy = None if py is None else py.to(DEV)
+    padded, counts, nvalid = _cabi.knn_padded(dx, dy, k, dpx, dpy, cosine)
+    torch.cuda.synchronize()
+    want_col, _ = orc.knn_padded(x.numpy(), y.numpy(), k, None if px is None else px.numpy(),
+                                 None if py is None else py.numpy(), cosine=cosine)
+    m = y.shape[0]
+    got = padded.cpu().numpy()
+    assert np.array_equal(got[0].reshape(m, k), np.repeat(np.arange(m), k).reshape(m, k))
+    got_col = got[1].reshape(m, k)
+    bad = np.nonzero((got_col != want_col).any(axis=1))[0]
+    assert bad.size == 0, (f"{bad.size} of {m} queries differ; first {bad[:5]}: got {got_col[bad[:3]]} "
+                           f"want {want_col[bad[:3]]}")
+    want_counts = (want_col >= 0).sum(1)
+    assert np.array_equal(counts.cpu().numpy(), want_counts)
+    assert nvalid == int(want_counts.sum())
+    # compacted form
+    e = _cabi.knn(dx, dy, k, dpx, dpy, cosine).cpu().numpy()
+    want = orc.knn(x.numpy(), y.numpy(), k, None if px is None else px.numpy(),
+                   None if py is None else py.numpy(), cosine=cosine)
+    assert np.array_equal(e, want)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+@pytest.mark.parametrize("dim", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_knn_lowd_single_segment(dim, dt):
+    x, y = _data(dim, 1500, 300, dim, DT[dt])
+    _check_knn(x, y, 16)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+@pytest.mark.parametrize("k", [1, 2, 17, 21, 32, 33, 64, 65, 100])
+def test_knn_lowd_all_k_ranges(k, dt):
+    x, y = _data(100 + k, 2100, 130, 3, DT[dt])
+    _check_knn(x, y, k)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+def test_knn_lowd_uneven_and_empty_segments(dt):
+    sx = [300, 0, 17, 650, 5, 1, 2049, 0]
+    sy = [40, 3, 0, 200, 31, 7, 65, 0]
+    px, py = _segments(sx), _segments(sy)
+    x, y = _data(7, sum(sx), sum(sy), 3, DT[dt])
+    _check_knn(x, y, 9, px, py)      # segments with fewer than k points -> -1 slots, compaction
+    _check_knn(x, y, 40, px, py)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+def test_knn_lowd_many_tiny_segments(dt):
+    g = torch.Generator().manual_seed(5)
+    sx = torch.randint(0, 12, (300,), generator=g).tolist()
+    sy = torch.randint(0, 6, (300,), generator=g).tolist()
+    x, y = _data(8, sum(sx), sum(sy), 2, DT[dt])
+    _check_knn(x, y, 4, _segments(sx), _segments(sy))
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+def test_knn_lowd_ties_keep_lower_index(dt):
+    # coarse grid => lots of exactly equal distances, incl. exact duplicates of points
+    x, y = _data(9, 3000, 200, 3, DT[dt], grid=4)
+    _check_knn(x, y, 21)
+    x2 = torch.cat([x[:500], x[:500]])  # duplicates
+    _check_knn(x2, y, 32)
+
+
+def test_knn_lowd_nan_and_huge_distances_are_skipped():
+    x, y = _data(10, 700, 64, 3, torch.float32)
+    x[5] = float("nan")
+    x[17, 1] = float("inf")
+    x[100:140] *= 1e6        # squared distance >= 1e10: never selected (initial bound 1e10)
+    y[3, 0] = float("nan")   # a query that can select nothing
+    _check_knn(x, y, 16)
+    sx = [20, 680]
+    _check_knn(x, y, 16, _segments(sx), _segments([10, 54]))
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+def test_knn_lowd_long_segment_large_coordinates(dt):
+    g = torch.Generator().manual_seed(11)
+    x = (100 * torch.rand(40000, 3, generator=g)).to(DT[dt])
+    y = (100 * torch.rand(257, 3, generator=g)).to(DT[dt])
+    _check_knn(x, y, 32)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+@pytest.mark.parametrize("dim", [9, 16, 17, 33, 64, 100])
+def test_knn_general_dim(dim, dt):
+    x, y = _data(20 + dim, 900, 150, dim, DT[dt])
+    _check_knn(x, y, 12)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+def test_knn_general_dim_batched_k_ranges(dt):
+    sx, sy = [400, 0, 300, 37], [90, 4, 110, 9]
+    x, y = _data(31, sum(sx), sum(sy), 24, DT[dt])
+    for k in (5, 40, 100):
+        _check_knn(x, y, k, _segments(sx), _segments(sy))
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+@pytest.mark.parametrize("dim", [2, 3, 16, 64])
+def test_knn_cosine(dim, dt):
+    sx, sy = [500, 300], [100, 80]
+    x, y = _data(40 + dim, sum(sx), sum(sy), dim, DT[dt])
+    _check_knn(x, y, 10, cosine=True)
+    _check_knn(x, y, 21, _segments(sx), _segments(sy), cosine=True)
+
+
+def test_knn_cosine_zero_rows():
+    x, y = _data(50, 400, 50, 8, torch.float32)
+    x[7] = 0  # zero norm: distance is NaN and never selected
+    y[2] = 0
+    _check_knn(x, y, 6, cosine=True)
+
+
+# ---- radius ---------------------------------------------------------------------------------------
+
+def _check_radius(x, y, r, px=None, py=None, max_nn=32, ignore=False):
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    dx, dy = x.to(DEV), y.to(DEV)
+    dpx = None if px is None else px.to(DEV)
+    dpy = None if py is None else py.to(DEV)
+    got = _cabi.radius(dx, dy, r, dpx, dpy, max_nn, ignore).cpu().numpy()
+    want = orc.radius(x.numpy(), y.numpy(), r, None if px is None else px.numpy(),
+                      None if py is None else py.numpy(), max_nn, ignore)
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert np.array_equal(got, want)
+    return got.shape[1]
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+@pytest.mark.parametrize("dim", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_radius_lowd(dim, dt):
+    g = torch.Generator().manual_seed(60 + dim)
+    x = torch.rand(3000, dim, generator=g, dtype=DT[dt])
+    y = torch.rand(400, dim, generator=g, dtype=DT[dt])
+    r = 0.5 * (0.02 ** (1.0 / dim)) * (dim ** 0.5)
+    e = _check_radius(x, y, r, max_nn=100000)
+    assert e > 0
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+@pytest.mark.parametrize("max_nn", [1, 8, 64, 100000])
+def test_radius_truncation_keeps_first_hits(max_nn, dt):
+    g = torch.Generator().manual_seed(70)
+    x = torch.rand(5000, 3, generator=g, dtype=DT[dt])
+    _check_radius(x, x[:700].clone(), 0.2, max_nn=max_nn)
+    _check_radius(x, x.clone(), 0.1, max_nn=max_nn, ignore=True)   # radius_graph without self loops
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+def test_radius_uneven_segments_and_same_index(dt):
+    sx = [300, 0, 900, 12, 2100]
+    sy = [100, 5, 0, 60, 500]
+    g = torch.Generator().manual_seed(71)
+    x = torch.rand(sum(sx), 3, generator=g, dtype=DT[dt])
+    y = torch.rand(sum(sy), 3, generator=g, dtype=DT[dt])
+    for ignore in (False, True):
+        _check_radius(x, y, 0.2, _segments(sx), _segments(sy), max_nn=100000, ignore=ignore)
+        _check_radius(x, y, 0.2, _segments(sx), _segments(sy), max_nn=5, ignore=ignore)
+
+
+def test_radius_boundary_is_strict():
+    # points at distance exactly r are not neighbours (test/test_radius.py:37-39 relies on it)
+    x = torch.tensor([[0.0, 0.0], [3.0, 4.0], [5.0, 0.0], [4.9999995, 0.0]])
+    y = torch.tensor([[0.0, 0.0]])
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    got = _cabi.radius(x.to(DEV), y.to(DEV), 5.0, max_num_neighbors=10).cpu()
+    assert got.t().tolist() == [[0, 0], [0, 3]]
+
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+@pytest.mark.parametrize("dim", [9, 16, 40])
+def test_radius_general_dim(dim, dt):
+    g = torch.Generator().manual_seed(80 + dim)
+    x = torch.rand(1200, dim, generator=g, dtype=DT[dt])
+    y = torch.rand(300, dim, generator=g, dtype=DT[dt])
+    r = 0.33 * dim ** 0.5
+    e = _check_radius(x, y, r, max_nn=100000)
+    assert e > 0
+    _check_radius(x, y, r, max_nn=3)
+    sx, sy = [700, 500], [100, 200]
+    _check_radius(x, y, r, _segments(sx), _segments(sy), max_nn=100000, ignore=True)
+
+
+# ---- small passes ----------------------------------------------------------------------------------
+
+def test_segment_ptr_matches_bucketize():
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    g = torch.Generator().manual_seed(90)
+    for n, b in [(1, 1), (50, 9), (100000, 64), (5000, 4000)]:
+        batch = torch.sort(torch.randint(0, b, (n,), generator=g)).values
+        want = torch.bucketize(torch.arange(b + 1), batch)
+        got = _cabi.segment_ptr(batch.to(DEV), b).cpu()
+        assert torch.equal(got, want)
+        assert got.tolist() == orc.segment_ptr(batch.numpy(), b).tolist()
+
+
+@pytest.mark.parametrize("m", [1, 31, 2048, 2049, 1000003])
+def test_exclusive_scan(m):
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    g = torch.Generator().manual_seed(m)
+    counts = torch.randint(0, 1000, (m,), generator=g, dtype=torch.int32)
+    got = _cabi.exclusive_scan(counts.to(DEV)).cpu()
+    want = torch.zeros(m + 1, dtype=torch.long)
+    want[1:] = torch.cumsum(counts.long(), 0)
+    assert torch.equal(got, want)
+
+
+def test_argument_errors():
+    from pytorch_cluster_b200 import _native
+
+    lib = _native.cabi()
+    x = torch.rand(10, 3, device=DEV)
+    out = torch.empty(2, 10 * 101, dtype=torch.long, device=DEV)
+    cnt = torch.empty(10, dtype=torch.int32, device=DEV)
+    nv = torch.empty(1, dtype=torch.long, device=DEV)
+    st = lib.b200c_knn(x.data_ptr(), x.data_ptr(), None, None, 1, 10, 10, 3, 101, 0, 0, out.data_ptr(),
+                       cnt.data_ptr(), nv.data_ptr(), None, 0, None)
+    assert st == 1 and b"smaller than or equal to 100" in lib.b200c_last_error()
