@@ -156,6 +156,11 @@ template <typename K>
 __device__ __forceinline__ K key_min(const K &a, const K &b) { return b.less(a) ? b : a; }
 template <typename K>
 __device__ __forceinline__ K key_max(const K &a, const K &b) { return b.less(a) ? a : b; }
+// One compare per exchange: keep the smaller of (mine, other) when take_min, else the larger.
+template <typename K>
+__device__ __forceinline__ K key_pick(const K &mine, const K &other, bool take_min) {
+  return (other.less(mine) == take_min) ? other : mine;
+}
 
 // Ascending bitonic sort of one key per lane.
 template <typename K>
@@ -167,7 +172,21 @@ __device__ __forceinline__ K warp_sort32(K v, int lane) {
       K o = v.shfl_xor(stride);
       bool lower = (lane & stride) == 0;
       bool asc = (lane & size) == 0;
-      v = (lower == asc) ? key_min(v, o) : key_max(v, o);
+      v = key_pick(v, o, lower == asc);
+    }
+  }
+  return v;
+}
+
+// Ascending bitonic sort of one 32-bit value per lane.
+__device__ __forceinline__ uint32_t warp_sort32_u32(uint32_t v, int lane) {
+#pragma unroll
+  for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      uint32_t o = __shfl_xor_sync(FULL_MASK, v, stride);
+      bool take_min = ((lane & stride) == 0) == ((lane & size) == 0);
+      v = ((o < v) == take_min) ? o : v;
     }
   }
   return v;
@@ -179,7 +198,7 @@ __device__ __forceinline__ K warp_bitonic_merge32(K v, int lane) {
 #pragma unroll
   for (int stride = 16; stride > 0; stride >>= 1) {
     K o = v.shfl_xor(stride);
-    v = ((lane & stride) == 0) ? key_min(v, o) : key_max(v, o);
+    v = key_pick(v, o, (lane & stride) == 0);
   }
   return v;
 }

@@ -39,7 +39,8 @@ struct GenSmem {
   static constexpr size_t STAGE_BYTES = 2 * (size_t)G::STAGE_ELEMS * sizeof(T);
   static constexpr size_t OFF_KEYS = (STAGE_BYTES + 15) / 16 * 16;
   static constexpr size_t KEYS_BYTES = KP > 0 ? (size_t)G::TQ * 2 * KP * sizeof(Key<T>) : 0;
-  static constexpr size_t SMEM_BYTES = OFF_KEYS + KEYS_BYTES;
+  static constexpr size_t OFF_CNT = OFF_KEYS + KEYS_BYTES;  // kNN: queue fill per query
+  static constexpr size_t SMEM_BYTES = OFF_CNT + (KP > 0 ? (size_t)G::TQ * sizeof(int) : 0);
 };
 
 // Stage features [d0, d0 + DC) of points [first, first + XC) and of the CTA's query rows.
@@ -101,6 +102,7 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   K *my_keys = keys_all + (size_t)warp * QW * 2 * (KP > 0 ? KP : 1);
+  int *my_cnt = reinterpret_cast<int *>(smem + S::OFF_CNT) + warp * QW;
   const bool may_stop_early = max_nn < (int64_t)(1 << 20);
 
   const int64_t tile_lo = (int64_t)blockIdx.x * TQ;
@@ -124,7 +126,7 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
     // per-query state in registers (query loops are fully unrolled)
     T bound[QW];      // kNN: current k-th distance; radius: r2
     T ny[QW];         // cosine: |y_q|
-    int cnt[QW];      // kNN: queue fill; count: lane's hits; fill: hits so far
+    int cnt[QW];      // count: lane's hits; fill: hits so far
     int64_t base[QW];
     int limit[QW];
 #pragma unroll
@@ -137,7 +139,10 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
       if (qi < nq) {
         const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
         if constexpr (COSINE) ny[qi] = norms_y[q];
-        if constexpr (MODE == GEN_KNN) knn_reset<T, KP>(my_keys + qi * 2 * KP, lane);
+        if constexpr (MODE == GEN_KNN) {
+          knn_reset<T, KP>(my_keys + qi * 2 * KP, lane);
+          if (lane == 0) my_cnt[qi] = 0;
+        }
         if constexpr (MODE == GEN_RADIUS_FILL) {
           base[qi] = offsets[q];
           limit[qi] = (int)(offsets[q + 1] - base[qi]);
@@ -254,8 +259,8 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
                 const T dmin = min_of(dist);
                 if (__any_sync(FULL_MASK, dmin < bound[qi])) {
                   if constexpr (MODE == GEN_KNN)
-                    knn_offer<T, KP, NR>(my_keys + qi * 2 * KP, cnt[qi], bound[qi], dist, (uint32_t)idx0, k,
-                                         lane);
+                    knn_offer<T, KP, NR, !COSINE>(my_keys + qi * 2 * KP, my_cnt + qi, bound[qi], dist,
+                                                  (uint32_t)idx0, k, lane);
                   else
                     radius_fill_offer<T, NR>(dist, bound[qi], idx0, q, ignore_same != 0, cnt[qi], limit[qi],
                                              base[qi], out_row, out_col, lane);
@@ -291,7 +296,7 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
       if (qi < nq) {
         const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
         if constexpr (MODE == GEN_KNN) {
-          const int valid = knn_finish<T, KP>(my_keys + qi * 2 * KP, cnt[qi], k, q, out_row, out_col, lane);
+          const int valid = knn_finish<T, KP>(my_keys + qi * 2 * KP, my_cnt[qi], k, q, out_row, out_col, lane);
           if (lane == 0) {
             counts[q] = valid;
             my_valid += valid;

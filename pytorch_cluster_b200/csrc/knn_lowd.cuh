@@ -26,7 +26,7 @@ struct KnnLowD {
 };
 
 template <typename T, int DIM, int KP>
-__global__ void __launch_bounds__(CTA_THREADS)
+__global__ void __launch_bounds__(CTA_THREADS, KP == 32 ? 3 : 2)
 knn_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *__restrict__ ptr_x,
                 const int64_t *__restrict__ ptr_y, int num_segments, int64_t n, int64_t m, int k,
                 int64_t *__restrict__ out_row, int64_t *__restrict__ out_col,
@@ -105,14 +105,12 @@ knn_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t 
             T bound = pts.dists(rec, dist);
             const T dmin = min_of(dist);
             if (__any_sync(FULL_MASK, dmin < bound)) {
-              K *keys = my_keys + qi * (KP + Cfg::QCAP);
-              int cnt = my_cnt[qi];
-              knn_offer<T, KP, R>(keys, cnt, bound, dist, idx0, k, lane);
-              if (lane == 0) {
-                my_cnt[qi] = cnt;
-                *LanePoints<T, DIM>::bound_ptr(rec) = bound;
+              const T before = bound;
+              knn_offer<T, KP, R, true>(my_keys + qi * (KP + Cfg::QCAP), my_cnt + qi, bound, dist, idx0, k, lane);
+              if (bound != before) {
+                if (lane == 0) *LanePoints<T, DIM>::bound_ptr(rec) = bound;
+                __syncwarp();
               }
-              __syncwarp();
             }
           }
         }

@@ -50,30 +50,102 @@ __device__ __forceinline__ void knn_reset(Key<T> *keys, int lane) {
 }
 
 // Offer NR candidates per lane to one query: candidate r of lane l has distance dist[r] and
-// index idx0 + 32 r (idx0 already includes the lane).  `cnt` (queue fill) and `bound` are
-// warp-uniform and updated in place.  Must be called by the whole warp.
-template <typename T, int KP, int NR>
-__device__ __forceinline__ void knn_offer(Key<T> *keys, int &cnt, T &bound, const T (&dist)[NR],
+// index idx0 + 32 r (idx0 already includes the lane).  `cnt_s` is the query's queue fill in
+// shared memory, `bound` its current bound (warp-uniform, updated in place).  Must be called by
+// the whole warp.  NONNEG promises dist >= 0 (squared L2), which enables the cold-start shortcut.
+//
+// Fast path: lanes count their own hits, one warp reduction tells whether they fit into the
+// queue, and each hitting lane reserves its slots with one shared-memory atomic (the queue is
+// unordered; order is restored by the keys when it is merged).
+// Cold start (nothing known yet, more hits than the queue holds): the k-th smallest of the 32
+// per-lane minima is an upper bound of the k-th smallest of all 32 NR candidates, so it is used
+// as a first filter instead of merging group after group.
+template <typename T, int KP, int NR, bool NONNEG>
+__device__ __forceinline__ void knn_offer(Key<T> *keys, int *cnt_s, T &bound, const T (&dist)[NR],
                                           uint32_t idx0, int k, int lane) {
   using K = Key<T>;
-  const unsigned lt_mask = (1u << lane) - 1u;
+  int cnt = *cnt_s;
+  T limit = bound;  // candidates must be < limit
+  int nl = 0;
 #pragma unroll
-  for (int r = 0; r < NR; ++r) {
-    bool hit = dist[r] < bound;
-    unsigned mask = __ballot_sync(FULL_MASK, hit);
-    if (mask) {
-      int nh = __popc(mask);
-      if (cnt + nh > KP) {
-        bound = knn_merge<T, KP>(keys, cnt, k, lane);
-        cnt = 0;
-        hit = dist[r] < bound;
-        mask = __ballot_sync(FULL_MASK, hit);
-        nh = __popc(mask);
+  for (int r = 0; r < NR; ++r) nl += dist[r] < limit ? 1 : 0;
+  int tot = __reduce_add_sync(FULL_MASK, nl);
+
+  if (cnt + tot > KP) {
+    if (cnt > 0) {
+      bound = knn_merge<T, KP>(keys, cnt, k, lane);
+      cnt = 0;
+      limit = bound;
+    } else if (NONNEG && KP == 32 && sizeof(T) == 4) {
+      // cold start on an empty queue
+      float lmin = (float)dist[0];
+#pragma unroll
+      for (int r = 1; r < NR; ++r) lmin = fminf(lmin, (float)dist[r]);
+      const uint32_t kth = __shfl_sync(FULL_MASK, warp_sort32_u32(__float_as_uint(lmin), lane), k - 1);
+      // non-negative floats order like their bit patterns; NaN patterns sort above +inf
+      if (kth < 0x7f800000u) {
+        const float cap = __uint_as_float(kth + 1u);  // "<= kth" as a strict bound
+        if (cap < (float)limit) limit = (T)cap;
       }
-      if (hit) keys[KP + cnt + __popc(mask & lt_mask)] = K::make(dist[r], idx0 + 32u * r);
-      cnt += nh;
+    }
+    nl = 0;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) nl += dist[r] < limit ? 1 : 0;
+    tot = __reduce_add_sync(FULL_MASK, nl);
+    if (cnt + tot > KP) {
+      // still too many at once: go group by group, merging whenever the queue is full
+      const unsigned lt_mask = (1u << lane) - 1u;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        bool hit = dist[r] < bound;
+        unsigned mask = __ballot_sync(FULL_MASK, hit);
+        if (mask) {
+          int nh = __popc(mask);
+          if (cnt + nh > KP) {
+            bound = knn_merge<T, KP>(keys, cnt, k, lane);
+            cnt = 0;
+            hit = dist[r] < bound;
+            mask = __ballot_sync(FULL_MASK, hit);
+            nh = __popc(mask);
+          }
+          if (hit) keys[KP + cnt + __popc(mask & lt_mask)] = K::make(dist[r], idx0 + 32u * r);
+          cnt += nh;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) *cnt_s = cnt;
+      __syncwarp();
+      return;
+    }
+    __syncwarp();
+    if (lane == 0) *cnt_s = cnt;
+    __syncwarp();
+  }
+  if (nl > 0) {
+    int p = KP + atomicAdd(cnt_s, nl);
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      if (dist[r] < limit) {
+        keys[p] = K::make(dist[r], idx0 + 32u * r);
+        ++p;
+      }
     }
   }
+  __syncwarp();
+}
+
+// Out-of-line form of knn_offer for hot loops that must stay small: the distances travel by
+// value (registers), the new bound comes back as the result.
+template <typename T, int NR>
+struct DistPack {
+  T v[NR];
+};
+
+template <typename T, int KP, int NR, bool NONNEG>
+__device__ __noinline__ T knn_offer_call(Key<T> *keys, int *cnt_s, T bound, DistPack<T, NR> pack,
+                                         uint32_t idx0, int k) {
+  knn_offer<T, KP, NR, NONNEG>(keys, cnt_s, bound, pack.v, idx0, k, (int)(threadIdx.x & 31));
+  return bound;
 }
 
 // Final merge and padded output of one query (row q): slots q*k .. q*k+k-1.  Returns the number
