@@ -62,6 +62,31 @@ int b200c_exclusive_scan(const int32_t *counts, int64_t m, int64_t *offsets,
                          void *workspace, size_t workspace_bytes,
                          b200c_stream_t stream);
 
+/* The same exclusive prefix sum for callers that cannot hand over a workspace.
+ *
+ * This entry point has no counterpart in the reference.  It exists for hosts that must not, or
+ * cannot, allocate device memory around the call: a plugin living inside an application whose
+ * GPU memory was planned and handed out up front, an inference loop with a "no allocation after
+ * warm-up" rule (cudaMalloc and cudaFree synchronise the whole device), or a caller that simply
+ * has no allocator of its own to carve the scratch from.  They still pass `counts` and `offsets`;
+ * the per-tile partial sums that b200c_exclusive_scan keeps in its workspace live instead in a
+ * fixed array inside the library: 8 bytes per 2048 rows, 64 KiB in total, resident on every GPU
+ * that loads the library until the process exits.
+ *
+ *   - m may not exceed B200C_SCAN_STATIC_MAX_ROWS; larger inputs are refused with
+ *     B200C_ERR_WORKSPACE and an explanatory message, nothing is launched.
+ *   - No cudaMalloc, cudaFree or other allocating routine is called, ever.
+ *   - The first call on each device looks up the device address of the array (one
+ *     cudaGetSymbolAddress with that device current) and remembers it; make that first call
+ *     outside of any stream capture.  Later calls only launch kernels.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left
+ *     there.  Nothing in it has to start at zero: every partial sum a call reads was written by
+ *     that same call first.  Two calls that overlap on the GPU (different streams, or different
+ *     host threads) race on the array; run them one after the other. */
+#define B200C_SCAN_STATIC_MAX_ROWS (1 << 24)
+int b200c_exclusive_scan_static(const int32_t *counts, int64_t m, int64_t *offsets,
+                                b200c_stream_t stream);
+
 /* k nearest neighbours — replaces knn_kernel + knn_cuda
  * (csrc/cuda/knn_cuda.cu:30-84, 86-135).
  *

@@ -1,5 +1,7 @@
 // Small HBM-bound passes around the search kernels: segment pointers, the exclusive scan of the
 // per-query edge counts, and the compaction of padded kNN output.
+#include <mutex>
+
 #include "common.cuh"
 #include "launchers.h"
 
@@ -113,6 +115,36 @@ scan_apply_kernel(const int32_t *__restrict__ counts, int64_t m, const int64_t *
   }
 }
 
+// ---- scratch of the workspace-free scan ---------------------------------------------------------------
+// Partial sums of b200c_exclusive_scan_static: one per tile of 2048 rows, enough for
+// B200C_SCAN_STATIC_MAX_ROWS rows.  Device code may name the array; host code may not (there the
+// name is only a handle for cudaGetSymbolAddress), so the kernels receive its address as a pointer.
+constexpr int64_t SCAN_STATIC_TILES = B200C_SCAN_STATIC_MAX_ROWS / SCAN_TILE;
+static __device__ __align__(256) int64_t g_scan_static_tile_sums[SCAN_STATIC_TILES];
+
+constexpr int SCAN_STATIC_MAX_DEVICES = 64;
+static std::mutex g_scan_static_mutex;
+static int64_t *g_scan_static_addr[SCAN_STATIC_MAX_DEVICES] = {};
+
+// Device address of the array on the current device; looked up once per device.
+static int scan_static_scratch(int64_t **out) {
+  int dev = -1;
+  B200C_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= SCAN_STATIC_MAX_DEVICES) {
+    set_error("device ordinal %d is outside the range this entry point tracks (0..%d)", dev,
+              SCAN_STATIC_MAX_DEVICES - 1);
+    return B200C_ERR_INVALID;
+  }
+  std::lock_guard<std::mutex> lock(g_scan_static_mutex);
+  if (g_scan_static_addr[dev] == nullptr) {
+    void *addr = nullptr;
+    B200C_CUDA(cudaGetSymbolAddress(&addr, g_scan_static_tile_sums));
+    g_scan_static_addr[dev] = static_cast<int64_t *>(addr);
+  }
+  *out = g_scan_static_addr[dev];
+  return B200C_OK;
+}
+
 // ---- compaction of padded kNN output ------------------------------------------------------------------
 __global__ void knn_compact_kernel(const int64_t *__restrict__ col_padded, const int32_t *__restrict__ counts,
                                    const int64_t *__restrict__ offsets, int64_t m, int k,
@@ -165,6 +197,37 @@ extern "C" int b200c_exclusive_scan(const int32_t *counts, int64_t m, int64_t *o
   }
   const int64_t tiles = (m + SCAN_TILE - 1) / SCAN_TILE;
   int64_t *tile_sums = (int64_t *)workspace;
+  scan_tile_sums_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, stream>>>(counts, m, tile_sums);
+  B200C_LAUNCH_CHECK("scan_tile_sums_kernel");
+  scan_tile_offsets_kernel<<<1, SCAN_THREADS, 0, stream>>>(tile_sums, tiles, offsets + m);
+  B200C_LAUNCH_CHECK("scan_tile_offsets_kernel");
+  scan_apply_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, stream>>>(counts, m, tile_sums, offsets);
+  B200C_LAUNCH_CHECK("scan_apply_kernel");
+  return B200C_OK;
+}
+
+// The scan of b200c_exclusive_scan with its partial sums in the library's own fixed array, for
+// callers without an allocator (see include/b200_cluster.h).  Allocates nothing.
+extern "C" int b200c_exclusive_scan_static(const int32_t *counts, int64_t m, int64_t *offsets,
+                                           b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  B200C_CHECK_ARG(m >= 0, "Input mismatch");
+  if (m > (int64_t)B200C_SCAN_STATIC_MAX_ROWS) {
+    set_error("b200c_exclusive_scan_static handles at most %lld rows (its scratch is a fixed 64 KiB array); "
+              "got %lld - use b200c_exclusive_scan with a caller-provided workspace",
+              (long long)B200C_SCAN_STATIC_MAX_ROWS, (long long)m);
+    return B200C_ERR_WORKSPACE;
+  }
+  B200C_CHECK_ARG(offsets != nullptr, "null pointer");
+  if (m == 0) {
+    B200C_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int64_t), stream));
+    return B200C_OK;
+  }
+  B200C_CHECK_ARG(counts != nullptr, "null pointer");
+  int64_t *tile_sums = nullptr;
+  const int st = scan_static_scratch(&tile_sums);
+  if (st != B200C_OK) return st;
+  const int64_t tiles = (m + SCAN_TILE - 1) / SCAN_TILE;
   scan_tile_sums_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, stream>>>(counts, m, tile_sums);
   B200C_LAUNCH_CHECK("scan_tile_sums_kernel");
   scan_tile_offsets_kernel<<<1, SCAN_THREADS, 0, stream>>>(tile_sums, tiles, offsets + m);
