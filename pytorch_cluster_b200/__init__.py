@@ -10,7 +10,8 @@ _native.load_ops()
 
 from .knn import knn, knn_graph  # noqa: E402
 from .radius import radius, radius_graph  # noqa: E402
+from .sharded import knn_sharded, radius_sharded  # noqa: E402
 
 __version__ = '0.1.0'
 
-__all__ = ['knn', 'knn_graph', 'radius', 'radius_graph', '__version__']
+__all__ = ['knn', 'knn_graph', 'radius', 'radius_graph', 'knn_sharded', 'radius_sharded', '__version__']
