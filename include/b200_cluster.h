@@ -119,28 +119,39 @@ int b200c_knn_compact(const int64_t *edge_padded, const int32_t *counts,
                       int64_t num_edges, int64_t *edge_index,
                       b200c_stream_t stream);
 
-/* Fixed-radius search, pass 1 — replaces the scan of radius_kernel
- * (csrc/cuda/radius_cuda.cu:26-41) without its -1 padded output:
+/* Fixed-radius search — replaces radius_kernel and its -1 padded output
+ * (csrc/cuda/radius_cuda.cu:9-42, 75-95) by count -> exclusive scan -> fill.
+ *
+ * Pass 1, b200c_radius_count:
  *   counts[q] = min(max_num_neighbors, #{x in segment(q): dist < (T)(r * r),
  *                                        and not (ignore_same_index and x == q)}).
  * The comparison is strict and r * r is formed in double and narrowed to the
- * data type (csrc/cuda/radius_cuda.cu:33, 90). */
+ * data type (csrc/cuda/radius_cuda.cu:33, 90).
+ * Pass 2, b200c_radius_fill: writes, for each query q, its first counts[q] hits
+ * in ascending x order at offsets[q].. of edge_index (int64 [2, num_edges];
+ * row 0 = q, row 1 = x index) — the truncation rule of
+ * csrc/cuda/radius_cuda.cu:33-40.  offsets is the exclusive scan of counts.
+ *
+ * Workspace (optional): b200c_radius_workspace_bytes(m, dim, max_num_neighbors)
+ * is non-zero when a one-pass mode applies (small neighbour caps): pass 1 then
+ * also parks the hits in the workspace (m * max_num_neighbors int32) and pass 2
+ * only copies them, instead of scanning the points a second time.  Give both
+ * passes the same workspace, untouched in between; with NULL / too few bytes
+ * both passes scan. */
+size_t b200c_radius_workspace_bytes(int64_t m, int64_t dim, int64_t max_num_neighbors);
 int b200c_radius_count(const void *x, const void *y, const int64_t *ptr_x,
                        const int64_t *ptr_y, int64_t num_segments, int64_t n,
                        int64_t m, int64_t dim, double r,
                        int64_t max_num_neighbors, int ignore_same_index,
-                       int dtype, int32_t *counts, b200c_stream_t stream);
-
-/* Fixed-radius search, pass 2: writes, for each query q, its first counts[q]
- * hits in ascending x order at offsets[q].. of edge_index (int64 [2, num_edges];
- * row 0 = q, row 1 = x index) — the truncation rule of
- * csrc/cuda/radius_cuda.cu:33-40.  offsets is the exclusive scan of counts. */
+                       int dtype, int32_t *counts, void *workspace,
+                       size_t workspace_bytes, b200c_stream_t stream);
 int b200c_radius_fill(const void *x, const void *y, const int64_t *ptr_x,
                       const int64_t *ptr_y, int64_t num_segments, int64_t n,
                       int64_t m, int64_t dim, double r,
                       int64_t max_num_neighbors, int ignore_same_index,
-                      int dtype, const int64_t *offsets, int64_t num_edges,
-                      int64_t *edge_index, b200c_stream_t stream);
+                      int dtype, const int32_t *counts, const int64_t *offsets,
+                      int64_t num_edges, int64_t *edge_index, void *workspace,
+                      size_t workspace_bytes, b200c_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -6,7 +6,8 @@
 ``_torch_ops.so``       the torch operator layer (``torch_cluster::knn`` / ``radius``),
                         compiled by g++ against libtorch and linked to the first.
 
-``python -m pytorch_cluster_b200.build`` builds both (incremental by mtime).
+``python pytorch_cluster_b200/build.py`` builds both (incremental by mtime).  Run it as a script:
+importing the package needs the libraries this step produces.
 """
 from __future__ import annotations
 

@@ -71,26 +71,37 @@ def knn(x, y, k, ptr_x=None, ptr_y=None, cosine=False):
     return out
 
 
-def radius_counts(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_index=False):
+def _radius_workspace(x, m, dim, max_num_neighbors, one_pass):
+    lib = _native.cabi()
+    nbytes = lib.b200c_radius_workspace_bytes(m, dim, max_num_neighbors) if one_pass else 0
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+    return ws, nbytes
+
+
+def radius_counts(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_index=False, workspace=None):
+    """Pass 1.  workspace = (tensor, nbytes) from _radius_workspace, or None for the two-scan mode."""
     lib = _native.cabi()
     n, m, dim = x.shape[0], y.shape[0], x.shape[1]
     nseg = 1 if ptr_x is None else ptr_x.numel() - 1
     counts = torch.empty(m, dtype=torch.int32, device=x.device)
+    ws, nbytes = workspace if workspace is not None else (None, 0)
     _native.check(lib.b200c_radius_count(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, float(r),
                                          max_num_neighbors, int(ignore_same_index), _dtype(x), _p(counts),
-                                         _stream()))
+                                         _p(ws) if nbytes else None, nbytes, _stream()))
     return counts
 
 
-def radius(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_index=False):
+def radius(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_index=False, one_pass=True):
     lib = _native.cabi()
     n, m, dim = x.shape[0], y.shape[0], x.shape[1]
     nseg = 1 if ptr_x is None else ptr_x.numel() - 1
-    counts = radius_counts(x, y, r, ptr_x, ptr_y, max_num_neighbors, ignore_same_index)
+    ws, nbytes = _radius_workspace(x, m, dim, max_num_neighbors, one_pass)
+    counts = radius_counts(x, y, r, ptr_x, ptr_y, max_num_neighbors, ignore_same_index, (ws, nbytes))
     offsets = exclusive_scan(counts)
     total = int(offsets[-1].item())
     out = torch.empty(2, total, dtype=torch.long, device=x.device)
     _native.check(lib.b200c_radius_fill(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, float(r),
-                                        max_num_neighbors, int(ignore_same_index), _dtype(x), _p(offsets),
-                                        total, _p(out), _stream()))
+                                        max_num_neighbors, int(ignore_same_index), _dtype(x), _p(counts),
+                                        _p(offsets), total, _p(out), _p(ws) if nbytes else None, nbytes,
+                                        _stream()))
     return out

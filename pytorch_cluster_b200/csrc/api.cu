@@ -105,18 +105,33 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
   return f32 ? launch_knn_generic_f32(a) : launch_knn_generic_f64(a);
 }
 
+// One-pass mode keeps a row of max_num_neighbors int32 slots per query; it is used when that
+// scratch is modest, i.e. for the small neighbour caps that are typical in practice.
+static constexpr int64_t RADIUS_DIRECT_MAX_NN = 256;
+static constexpr int64_t RADIUS_DIRECT_MAX_BYTES = 2ll << 30;
+
+extern "C" size_t b200c_radius_workspace_bytes(int64_t m, int64_t dim, int64_t max_num_neighbors) {
+  if (m <= 0 || dim < 1 || dim > 8 || max_num_neighbors < 1 || max_num_neighbors > RADIUS_DIRECT_MAX_NN) return 0;
+  const int64_t bytes = m * max_num_neighbors * 4;
+  return bytes <= RADIUS_DIRECT_MAX_BYTES ? (size_t)bytes : 0;
+}
+
 static int radius_common(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
                          int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
                          int64_t max_num_neighbors, int ignore_same_index, int dtype, int32_t *counts,
                          const int64_t *offsets, int64_t *out_row, int64_t *out_col, bool fill,
-                         cudaStream_t stream) {
+                         void *workspace, size_t workspace_bytes, cudaStream_t stream) {
   int st = check_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, dtype);
   if (st != B200C_OK) return st;
   B200C_CHECK_ARG(max_num_neighbors >= 1, "max_num_neighbors must be positive");
   if ((st = check_device()) != B200C_OK) return st;
   if (m == 0) return B200C_OK;
+  const size_t direct_bytes = b200c_radius_workspace_bytes(m, dim, max_num_neighbors);
+  int32_t *direct = (direct_bytes > 0 && workspace != nullptr && workspace_bytes >= direct_bytes)
+                        ? (int32_t *)workspace
+                        : nullptr;
   RadiusArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, r, max_num_neighbors,
-               ignore_same_index, counts, offsets, out_row, out_col, stream};
+               ignore_same_index, counts, offsets, out_row, out_col, direct, stream};
   B200C_CHECK_ARG(dim <= 0x7fffffffLL / 4, "Input mismatch");
   if (dim <= 8) return dtype == B200C_F32 ? launch_radius_lowd_f32(a, fill) : launch_radius_lowd_f64(a, fill);
   return dtype == B200C_F32 ? launch_radius_generic_f32(a, fill) : launch_radius_generic_f64(a, fill);
@@ -125,22 +140,24 @@ static int radius_common(const void *x, const void *y, const int64_t *ptr_x, con
 extern "C" int b200c_radius_count(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
                                   int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
                                   int64_t max_num_neighbors, int ignore_same_index, int dtype,
-                                  int32_t *counts, b200c_stream_t stream) {
+                                  int32_t *counts, void *workspace, size_t workspace_bytes,
+                                  b200c_stream_t stream) {
   B200C_CHECK_ARG(counts != nullptr || m == 0, "null output pointer");
   return radius_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
-                       ignore_same_index, dtype, counts, nullptr, nullptr, nullptr, false,
-                       (cudaStream_t)stream);
+                       ignore_same_index, dtype, counts, nullptr, nullptr, nullptr, false, workspace,
+                       workspace_bytes, (cudaStream_t)stream);
 }
 
 extern "C" int b200c_radius_fill(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
                                  int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
                                  int64_t max_num_neighbors, int ignore_same_index, int dtype,
-                                 const int64_t *offsets, int64_t num_edges, int64_t *edge_index,
+                                 const int32_t *counts, const int64_t *offsets, int64_t num_edges,
+                                 int64_t *edge_index, void *workspace, size_t workspace_bytes,
                                  b200c_stream_t stream) {
   B200C_CHECK_ARG(num_edges >= 0, "Input mismatch");
   if (num_edges == 0) return B200C_OK;
-  B200C_CHECK_ARG(offsets != nullptr && edge_index != nullptr, "null pointer");
+  B200C_CHECK_ARG(counts != nullptr && offsets != nullptr && edge_index != nullptr, "null pointer");
   return radius_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
-                       ignore_same_index, dtype, nullptr, offsets, edge_index, edge_index + num_edges,
-                       true, (cudaStream_t)stream);
+                       ignore_same_index, dtype, (int32_t *)counts, offsets, edge_index,
+                       edge_index + num_edges, true, workspace, workspace_bytes, (cudaStream_t)stream);
 }

@@ -33,6 +33,7 @@ struct RadiusArgs {
   int32_t *counts;          // count pass
   const int64_t *offsets;   // fill pass
   int64_t *out_row, *out_col;
+  int32_t *direct_rows;     // one-pass mode: [m, max_nn] int32 scratch, else nullptr
   cudaStream_t stream;
 };
 

@@ -20,8 +20,9 @@ template <typename T, int DIM>
 struct LowD {
   static constexpr int R = sizeof(T) == 4 ? 8 : 4;  // points per lane per step
   static constexpr int STEP = 32 * R;               // points per warp step
-  // chunk: about 12 KB per buffer, a whole number of steps
-  static constexpr int XC_RAW = 12288 / (DIM * (int)sizeof(T));
+  // chunk: about 12 KB per buffer, at most 1024 points, a whole number of steps
+  static constexpr int XC_FIT = 12288 / (DIM * (int)sizeof(T));
+  static constexpr int XC_RAW = XC_FIT < 1024 ? XC_FIT : 1024;
   static constexpr int XC = (XC_RAW / STEP) > 0 ? (XC_RAW / STEP) * STEP : STEP;
   static constexpr int XP = XC + 4;  // plane stride (elements)
   static constexpr int PLANES_ELEMS = DIM * XP;

@@ -1,8 +1,17 @@
-// Fixed-radius search for low-dimensional points: count pass and ordered fill pass.
+// Fixed-radius search for low-dimensional points (1 <= DIM <= 8).
 //
-// Both passes use the scan of lowd.cuh; the count pass keeps one counter per (lane, query) in
-// registers and needs no warp communication in its inner loop, the fill pass appends through
-// radius_fill_offer (select.cuh).
+// The scan of lowd.cuh without a single data-dependent branch in its inner loop: for every
+// (query, group of 32 consecutive points) the warp's hit predicates become one ballot word, and
+// lane 0 parks the 8 words of a step in shared memory.  After a chunk (1024 points = 32 words per
+// query) the warp resolves the words of its queries, lane l taking word l:
+//   COUNT   counts[q] += popc                      (pass 1 of count -> scan -> fill)
+//   FILL    hits are written at offsets[q] + running total + (hits of lower lanes) + (lower bits)
+//   DIRECT  as FILL, but into a row of `max_nn` int32 slots per query (one pass; a compaction
+//           copy follows the scan) — used when that scratch is small enough
+// Ballot words cover points in ascending index order and one warp owns a query for the whole
+// scan, so "append in ascending x order, stop at max_num_neighbors"
+// (csrc/cuda/radius_cuda.cu:33-40) needs no atomics.  A warp stops scanning once all its queries
+// reached their quota, which is what makes truncation cheap.
 #pragma once
 
 #include "lowd.cuh"
@@ -10,36 +19,44 @@
 
 namespace b200c {
 
+enum RadiusMode { RADIUS_COUNT = 0, RADIUS_FILL = 1, RADIUS_DIRECT = 2 };
+
 template <typename T, int DIM>
 struct RadiusLowD {
   using C = LowD<T, DIM>;
   static constexpr int QW = 8;
   static constexpr int TQ = QW * WARPS_PER_CTA;
+  static constexpr int WORDS = C::XC / 32;  // ballot words per query and chunk
+  static_assert(WORDS <= 32, "one lane resolves one word");
   static constexpr size_t PLANES_BYTES = 2 * (size_t)C::PLANES_ELEMS * sizeof(T);
   static constexpr size_t OFF_REC = (PLANES_BYTES + 15) / 16 * 16;
-  static constexpr size_t SMEM_BYTES = OFF_REC + (size_t)TQ * C::REC * sizeof(T);
+  static constexpr size_t OFF_MASK = (OFF_REC + (size_t)TQ * C::REC * sizeof(T) + 15) / 16 * 16;
+  static constexpr size_t SMEM_BYTES = OFF_MASK + (size_t)TQ * 32 * sizeof(uint32_t);
 };
 
-// FILL == false: counts[q] = min(max_nn, hits(q)).
-// FILL == true : edge rows written at offsets[q] .. offsets[q + 1].
-template <typename T, int DIM, bool FILL>
-__global__ void __launch_bounds__(CTA_THREADS)
+template <typename T, int DIM, int MODE>
+__global__ void __launch_bounds__(CTA_THREADS, 3)
 radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
                    const int64_t *__restrict__ ptr_x, const int64_t *__restrict__ ptr_y,
                    int num_segments, int64_t n, int64_t m, T r2, int64_t max_nn, int ignore_same,
                    int32_t *__restrict__ counts, const int64_t *__restrict__ offsets,
-                   int64_t *__restrict__ out_row, int64_t *__restrict__ out_col) {
+                   int64_t *__restrict__ out_row, int64_t *__restrict__ out_col,
+                   int32_t *__restrict__ direct_rows) {
   using Cfg = RadiusLowD<T, DIM>;
   using C = LowD<T, DIM>;
   constexpr int QW = Cfg::QW, TQ = Cfg::TQ, R = C::R;
+  constexpr int STEP_WORDS = C::STEP / 32;  // = R
 
   extern __shared__ __align__(16) unsigned char smem[];
   T *planes = reinterpret_cast<T *>(smem);
   T *recs = reinterpret_cast<T *>(smem + Cfg::OFF_REC);
+  uint32_t *masks = reinterpret_cast<uint32_t *>(smem + Cfg::OFF_MASK);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   T *my_recs = recs + warp * QW * C::REC;
-  const bool may_stop_early = max_nn < (int64_t)(1 << 20);
+  uint32_t *my_masks = masks + warp * QW * 32;
+  const unsigned lt_mask = (1u << lane) - 1u;
+  const int quota_all = max_nn < 0x7fffffffLL ? (int)max_nn : 0x7fffffff;
 
   const int64_t tile_lo = (int64_t)blockIdx.x * TQ;
   const int64_t tile_hi = tile_lo + TQ < m ? tile_lo + TQ : m;
@@ -57,32 +74,35 @@ radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
     const int nq_tile = (int)(q_hi - q_lo);
     const int nq = nq_tile > warp ? (nq_tile - warp + WARPS_PER_CTA - 1) / WARPS_PER_CTA : 0;
 
-    // per-query state, all in registers (the query loops below are fully unrolled)
-    int cnt[QW];        // count pass: this lane's hits; fill pass: hits of the query so far
-    int64_t base[QW];   // fill pass: offsets[q]
-    int limit[QW];      // fill pass: number of edges to write
+    // per-query state in registers, warp-uniform (the query loops are fully unrolled)
+    int run[QW];       // hits so far
+    int quota[QW];     // hits to keep: max_nn (count/direct) or offsets[q+1]-offsets[q] (fill)
+    int64_t base[QW];  // fill: offsets[q]; direct: q * max_nn
 #pragma unroll
     for (int qi = 0; qi < QW; ++qi) {
-      cnt[qi] = 0;
+      run[qi] = 0;
+      quota[qi] = 0;
       base[qi] = 0;
-      limit[qi] = 0;
+      T *rec = my_recs + qi * C::REC;
       if (qi < nq) {
         const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
-        if (lane == 0) LanePoints<T, DIM>::write_rec(my_recs + qi * C::REC, y + q * DIM, r2);
-        if constexpr (FILL) {
+        if (lane == 0) LanePoints<T, DIM>::write_rec(rec, y + q * DIM, r2);
+        if constexpr (MODE == RADIUS_FILL) {
           base[qi] = offsets[q];
-          limit[qi] = (int)(offsets[q + 1] - base[qi]);
+          quota[qi] = (int)(offsets[q + 1] - base[qi]);
+        } else {
+          quota[qi] = quota_all;
+          base[qi] = q * max_nn;
         }
+      } else if (lane == 0) {
+        // an unused slot: bound = -inf, no distance is below it
+        LanePoints<T, DIM>::write_rec(rec, y + q_lo * DIM, -pos_inf<T>());
       }
     }
     __syncwarp();
-    bool active = nq > 0;
-    if constexpr (FILL) {
-      bool todo = false;
+    bool active = false;
 #pragma unroll
-      for (int qi = 0; qi < QW; ++qi) todo |= limit[qi] > 0;
-      active = active && todo;
-    }
+    for (int qi = 0; qi < QW; ++qi) active |= run[qi] < quota[qi];
 
     const int64_t nx = x_hi > x_lo ? x_hi - x_lo : 0;
     const int nchunks = (int)((nx + C::XC - 1) / C::XC);
@@ -102,74 +122,104 @@ radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
         cp_async_wait<0>();
       }
       __syncthreads();
-      const T *buf = planes + (c & 1) * C::PLANES_ELEMS;
-      const int nsub = (npts + C::STEP - 1) / C::STEP;
       if (active) {
+        const T *buf = planes + (c & 1) * C::PLANES_ELEMS;
+        const int nsub = (npts + C::STEP - 1) / C::STEP;
+        // ---- scan: ballots only, no branches on the data ----
         for (int sub = 0; sub < nsub; ++sub) {
           LanePoints<T, DIM> pts;
           pts.load(buf, sub * C::STEP + lane);
-          const int64_t idx0 = first + sub * C::STEP + lane;
 #pragma unroll
           for (int qi = 0; qi < QW; ++qi) {
-            if (qi < nq) {
-              T dist[R];
-              const T bound = pts.dists(my_recs + qi * C::REC, dist);
-              if constexpr (!FILL) {
+            T dist[R];
+            const T bound = pts.dists(my_recs + qi * C::REC, dist);
+            uint32_t w[R];
 #pragma unroll
-                for (int r = 0; r < R; ++r) cnt[qi] += dist[r] < bound ? 1 : 0;
-              } else {
-                const T dmin = min_of(dist);
-                if (__any_sync(FULL_MASK, dmin < bound)) {
-                  const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
-                  radius_fill_offer<T, R>(dist, bound, idx0, q, ignore_same != 0, cnt[qi], limit[qi], base[qi],
-                                          out_row, out_col, lane);
+            for (int r = 0; r < R; ++r) w[r] = __ballot_sync(FULL_MASK, dist[r] < bound);
+            if (lane == 0) {
+              uint4 *dst = reinterpret_cast<uint4 *>(my_masks + qi * 32 + sub * STEP_WORDS);
+#pragma unroll
+              for (int v = 0; v < R / 4; ++v) dst[v] = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+            }
+          }
+        }
+        __syncwarp();
+        // ---- resolve: lane l owns word l (points first + 32 l ... + 31) of each query ----
+        const int nwords = nsub * STEP_WORDS;
+        bool todo = false;
+#pragma unroll
+        for (int qi = 0; qi < QW; ++qi) {
+          if (qi < nq && run[qi] < quota[qi]) {
+            const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
+            uint32_t word = lane < nwords ? my_masks[qi * 32 + lane] : 0u;
+            if (ignore_same) {
+              const int64_t rel = q - first;  // the pair with equal row numbers is skipped
+              if (rel >= 0 && (rel >> 5) == lane) word &= ~(1u << (rel & 31));
+            }
+            const int mine = __popc(word);
+            const int total = __reduce_add_sync(FULL_MASK, mine);
+            if constexpr (MODE != RADIUS_COUNT) {
+              if (total > 0) {
+                // hits of lower lanes: inclusive scan over the lanes, minus own
+                int incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                  const int t = __shfl_up_sync(FULL_MASK, incl, o);
+                  if (lane >= o) incl += t;
+                }
+                int pos = run[qi] + incl - mine;
+                const int64_t idx0 = first + 32 * lane;
+                while (word != 0u && pos < quota[qi]) {
+                  const int bit = __ffs(word) - 1;
+                  word &= word - 1u;
+                  if constexpr (MODE == RADIUS_FILL) {
+                    out_row[base[qi] + pos] = q;
+                    out_col[base[qi] + pos] = idx0 + bit;
+                  } else {
+                    direct_rows[base[qi] + pos] = (int32_t)(idx0 + bit);
+                  }
+                  ++pos;
                 }
               }
             }
+            run[qi] += total;
+            todo |= run[qi] < quota[qi];
           }
         }
-        // a warp whose queries all reached their quota has nothing left to find
-        if constexpr (FILL) {
-          bool todo = false;
-#pragma unroll
-          for (int qi = 0; qi < QW; ++qi) todo |= cnt[qi] < limit[qi];
-          active = todo;
-        } else if (may_stop_early) {
-          bool todo = false;
-#pragma unroll
-          for (int qi = 0; qi < QW; ++qi) {
-            if (qi < nq) {
-              int tot = cnt[qi];
-#pragma unroll
-              for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(FULL_MASK, tot, o);
-              todo |= (int64_t)tot - (ignore_same ? 1 : 0) < max_nn;
-            }
-          }
-          active = todo;
-        }
+        active = todo;  // a warp whose queries all reached their quota has nothing left to find
+        __syncwarp();
       }
       __syncthreads();
     }
 
-    if constexpr (!FILL) {
+    if constexpr (MODE != RADIUS_FILL) {
 #pragma unroll
       for (int qi = 0; qi < QW; ++qi) {
-        if (qi < nq) {
+        if (qi < nq && lane == 0) {
           const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
-          int tot = cnt[qi];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(FULL_MASK, tot, o);
-          if (lane == 0) {
-            int64_t c = tot;
-            if (ignore_same && q >= x_lo && q < x_hi &&
-                row_sqdist<T, DIM>(x + q * DIM, y + q * DIM) < r2)
-              c -= 1;
-            counts[q] = (int32_t)(c < max_nn ? c : max_nn);
-          }
+          counts[q] = run[qi] < quota[qi] ? run[qi] : quota[qi];
         }
       }
     }
     __syncthreads();
+  }
+}
+
+// Compaction after a DIRECT pass: copies the first counts[q] int32 slots of every query's row to
+// offsets[q].. of the int64 edge rows.  One warp per query.
+static __global__ void radius_direct_compact_kernel(const int32_t *__restrict__ direct_rows,
+                                             const int32_t *__restrict__ counts,
+                                             const int64_t *__restrict__ offsets, int64_t m, int64_t max_nn,
+                                             int64_t *__restrict__ out_row, int64_t *__restrict__ out_col) {
+  const int lane = threadIdx.x & 31;
+  const int64_t q = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (q >= m) return;
+  const int c = counts[q];
+  const int64_t o = offsets[q];
+  const int32_t *src = direct_rows + q * max_nn;
+  for (int e = lane; e < c; e += 32) {
+    out_row[o + e] = q;
+    out_col[o + e] = src[e];
   }
 }
 

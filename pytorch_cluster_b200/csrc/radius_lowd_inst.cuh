@@ -6,10 +6,10 @@
 
 namespace b200c {
 
-template <typename T, int DIM, bool FILL>
+template <typename T, int DIM, int MODE>
 static int launch_radius_lowd_one(const RadiusArgs &a) {
   using Cfg = RadiusLowD<T, DIM>;
-  auto kern = radius_lowd_kernel<T, DIM, FILL>;
+  auto kern = radius_lowd_kernel<T, DIM, MODE>;
   static bool configured = false;
   if (!configured) {
     B200C_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -24,14 +24,24 @@ static int launch_radius_lowd_one(const RadiusArgs &a) {
   const T r2 = (T)(a.r * a.r);  // formed in double, narrowed once (csrc/cuda/radius_cuda.cu:90)
   kern<<<(unsigned)tiles, CTA_THREADS, Cfg::SMEM_BYTES, a.stream>>>(
       (const T *)a.x, (const T *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, r2, a.max_nn,
-      a.ignore_same, a.counts, a.offsets, a.out_row, a.out_col);
+      a.ignore_same, a.counts, a.offsets, a.out_row, a.out_col, a.direct_rows);
   B200C_LAUNCH_CHECK("radius_lowd_kernel");
   return B200C_OK;
 }
 
+// fill == false: pass 1 (counts; with direct_rows also the hits themselves).
+// fill == true : pass 2 (edges from a second scan, or from direct_rows by a compaction copy).
 template <typename T, int DIM>
 static int launch_radius_lowd_dim(const RadiusArgs &a, bool fill) {
-  return fill ? launch_radius_lowd_one<T, DIM, true>(a) : launch_radius_lowd_one<T, DIM, false>(a);
+  if (!fill)
+    return a.direct_rows ? launch_radius_lowd_one<T, DIM, RADIUS_DIRECT>(a)
+                         : launch_radius_lowd_one<T, DIM, RADIUS_COUNT>(a);
+  if (!a.direct_rows) return launch_radius_lowd_one<T, DIM, RADIUS_FILL>(a);
+  const int64_t threads = a.m * 32;
+  radius_direct_compact_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, a.stream>>>(
+      a.direct_rows, a.counts, a.offsets, a.m, a.max_nn, a.out_row, a.out_col);
+  B200C_LAUNCH_CHECK("radius_direct_compact_kernel");
+  return B200C_OK;
 }
 
 template <typename T>

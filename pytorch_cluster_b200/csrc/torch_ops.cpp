@@ -128,9 +128,13 @@ torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tens
   if (m == 0 || max_num_neighbors <= 0) return torch::empty({2, 0}, lopts);
 
   auto counts = torch::empty({m}, x.options().dtype(torch::kInt));
+  // small neighbour caps: one scan that also parks the hits, then a copy (see b200_cluster.h)
+  const size_t ws_bytes = b200c_radius_workspace_bytes(m, dim, max_num_neighbors);
+  auto ws = torch::empty({(int64_t)ws_bytes}, x.options().dtype(torch::kByte));
+  void *ws_ptr = ws_bytes ? ws.data_ptr() : nullptr;
   check_status(b200c_radius_count(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
                                   max_num_neighbors, ignore_same_index ? 1 : 0, p.dtype,
-                                  counts.data_ptr<int32_t>(), stream.stream()));
+                                  counts.data_ptr<int32_t>(), ws_ptr, ws_bytes, stream.stream()));
   auto offsets = torch::empty({m + 1}, lopts);
   const size_t scan_bytes = b200c_scan_workspace_bytes(m);
   auto scan_ws = torch::empty({(int64_t)scan_bytes}, x.options().dtype(torch::kByte));
@@ -140,7 +144,8 @@ torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tens
   auto out = torch::empty({2, total}, lopts);
   check_status(b200c_radius_fill(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
                                  max_num_neighbors, ignore_same_index ? 1 : 0, p.dtype,
-                                 offsets.data_ptr<int64_t>(), total, out.data_ptr<int64_t>(), stream.stream()));
+                                 counts.data_ptr<int32_t>(), offsets.data_ptr<int64_t>(), total,
+                                 out.data_ptr<int64_t>(), ws_ptr, ws_bytes, stream.stream()));
   return out;
 }
 

@@ -153,6 +153,9 @@ def _check_radius(x, y, r, px=None, py=None, max_nn=32, ignore=False):
     dpx = None if px is None else px.to(DEV)
     dpy = None if py is None else py.to(DEV)
     got = _cabi.radius(dx, dy, r, dpx, dpy, max_nn, ignore).cpu().numpy()
+    # the same through count + second scan (no one-pass scratch)
+    two = _cabi.radius(dx, dy, r, dpx, dpy, max_nn, ignore, one_pass=False).cpu().numpy()
+    assert np.array_equal(got, two)
     want = orc.radius(x.numpy(), y.numpy(), r, None if px is None else px.numpy(),
                       None if py is None else py.numpy(), max_nn, ignore)
     assert got.shape == want.shape, (got.shape, want.shape)
