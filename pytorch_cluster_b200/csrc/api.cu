@@ -59,10 +59,16 @@ static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 extern "C" size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t k, int dtype, int cosine,
                                             int64_t num_segments) {
-  (void)dim; (void)k; (void)num_segments;
   const size_t elem = dtype == B200C_F64 ? 8 : 4;
   // cosine: |row| of every x and y row
-  return cosine ? align256((size_t)n * elem) + align256((size_t)m * elem) : 0;
+  const size_t exact = cosine ? align256((size_t)n * elem) + align256((size_t)m * elem) : 0;
+  // tensor-core candidate path: norms, candidate lists (and normalised copies for cosine)
+  if (dtype == B200C_F32 && num_segments >= 1 &&
+      knn_tensor_applicable(n, m, (int)dim, (int)k, num_segments, nullptr, nullptr)) {
+    const size_t tensor = knn_tensor_workspace_bytes(n, m, (int)dim, cosine);
+    return tensor > exact ? tensor : exact;
+  }
+  return exact;
 }
 
 extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
@@ -88,6 +94,9 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
   KnnArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, (int)k, cosine, nullptr, nullptr,
             edge_padded, edge_padded + m * k, counts, (unsigned long long *)num_valid, stream};
   const bool f32 = dtype == B200C_F32;
+  if (f32 && knn_tensor_applicable(n, m, (int)dim, (int)k, num_segments, x, y) &&
+      workspace_bytes >= knn_tensor_workspace_bytes(n, m, (int)dim, cosine))
+    return launch_knn_tensor_f32(a, workspace);
   if (cosine) {
     const size_t elem = f32 ? 4 : 8;
     char *ws = (char *)workspace;

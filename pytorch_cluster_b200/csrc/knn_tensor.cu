@@ -1,0 +1,474 @@
+// Feature-space kNN (fp32, 32 <= D <= 128, D % 8 == 0, k <= 32): tensor-core candidates, exact re-rank.
+//
+// Stage 1, knn_tensor_candidates_kernel — tcgen05 / TMEM.  A CTA owns 128 query rows.  The query
+// tile and, one after the other, 128-point tiles of the queries' segment are laid out in shared
+// memory in the canonical K-major, no-swizzle operand layout of the 5th-generation tensor cores
+// (8 x 16-byte core matrices; cp.async, 16 bytes per copy); one thread issues D / 8
+// `tcgen05.mma.cta_group::1.kind::tf32` instructions (M = 128, N = 128, K = 8) that accumulate
+// S = Q X^T into 128 columns of tensor memory, `tcgen05.commit` signals an mbarrier, and every
+// thread reads back its own query's row with `tcgen05.ld.32x32b`.  From S the approximate distance
+// a = |x|^2 - 2 S + |q|^2 (or 1 - S on pre-normalised rows for cosine) costs one FFMA per pair.
+// The segment is swept twice:
+//   pass A keeps, per query, the minimum of a over each group of consecutive points (at most 64
+//          groups).  The k-th smallest of those minima, T, is an upper bound of the k-th smallest
+//          approximate distance: k different points lie at or below it.
+//   pass B records every point with a <= T + 2 E as a candidate of that query (thread-owned list,
+//          no atomics), E being a bound of |a - d_exact| for tf32 operands (each truncated to 10
+//          mantissa bits: |dS| <= 2^-9 |x||q|).  If d_k is the exact k-th distance, then
+//          d_k <= T + E, so every true neighbour (d <= d_k) has a <= T + 2 E: no neighbour is lost.
+// Stage 2, knn_rerank_kernel — one warp per query evaluates its candidates exactly as the
+// reference does (sequential fused multiply-adds over ascending features,
+// csrc/cuda/knn_cuda.cu:9-28, 55-64) and selects the k best by (distance, index) with the
+// selection of select.cuh.  A query whose candidate list overflowed (or whose segment is too
+// short to give k group minima) is searched exhaustively by its warp instead.  Only exact
+// distances are compared, so the result equals the exact kernels' bit for bit.
+//
+// Every wait on the mbarrier is bounded; on expiry the CTA raises an error flag and the re-rank
+// kernel searches every query exhaustively instead of trusting the candidate lists.
+#include "common.cuh"
+#include "launchers.h"
+#include "select.cuh"
+
+namespace b200c {
+
+constexpr int TC_M = 128;        // queries per CTA = TMEM lanes
+constexpr int TC_N = 128;        // points per tile = TMEM columns
+constexpr int TC_GMAX = 64;      // group minima kept per query
+constexpr int TC_CAP = 128;      // candidates kept per query
+constexpr int TC_THREADS = 128;
+constexpr int TC_SPIN_LIMIT = 1 << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: start address, leading byte offset (between
+// the two 16-byte K slices of one MMA), stride byte offset (between 8-row groups), version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+  d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+
+// rows [row0, row0 + 128) of src ([*, dim] row-major) into the canonical operand layout:
+// (row, 16-byte K slice s) -> (row / 8) * sbo + s * 128 + (row % 8) * 16.  Rows >= row_end are zero.
+__device__ __forceinline__ void stage_operand(unsigned char *dst, const float *__restrict__ src, int64_t row0,
+                                              int64_t row_end, int dim, int tid) {
+  const int slices = dim >> 2;
+  const uint32_t sbo = (uint32_t)slices * 128u;
+  for (int p = tid; p < TC_M * slices; p += TC_THREADS) {
+    const int row = p & (TC_M - 1), s = p >> 7;
+    unsigned char *d = dst + (row >> 3) * sbo + s * 128 + (row & 7) * 16;
+    const int64_t g = row0 + row;
+    if (g < row_end)
+      cp_async_16(d, src + g * dim + s * 4);
+    else
+      *reinterpret_cast<float4 *>(d) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// Waits for phase `parity` of the mbarrier with a bounded number of polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t *mbar, uint32_t parity) {
+  uint32_t done = 0;
+  for (int it = 0; it < TC_SPIN_LIMIT && !done; ++it) {
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(smem_u32(mbar)), "r"(parity)
+        : "memory");
+  }
+  return done != 0;
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct TensorArgs {
+  const float *xa, *ya;        // operands of the product: x, y (L2) or their normalised copies (cosine)
+  const float *sq_x, *sq_y;    // L2: |row|^2 ; cosine: unused
+  const float *xmax;           // L2: largest |x| over all rows (one float)
+  const int64_t *ptr_x, *ptr_y;
+  int num_segments;
+  int64_t n, m;
+  int dim, k;
+  int32_t *cand;               // [m, TC_CAP]
+  int32_t *cand_count;         // [m]; > TC_CAP marks an overflow
+  int *error_flag;
+};
+
+template <bool COSINE>
+__global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(TensorArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const int dim = a.dim;
+  const uint32_t tile_bytes = (uint32_t)TC_M * dim * 4;
+  unsigned char *sQ = smem;
+  unsigned char *sX = smem + tile_bytes;
+  float *s_sqx = reinterpret_cast<float *>(smem + 2 * tile_bytes);  // |x|^2 of the current tile
+  float *gmin = s_sqx + TC_N;                                       // [TC_M][TC_GMAX + 1]
+  __shared__ __align__(8) uint64_t mbar;
+  __shared__ uint32_t tmem_base_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar)));
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                 "r"(TC_N));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t my_taddr = tmem + ((uint32_t)(warp * 32) << 16);
+  // D = f32, A = B = tf32, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TC_N >> 3) << 17) |
+                         ((uint32_t)(TC_M >> 4) << 24);
+  const uint32_t sbo = (uint32_t)(dim >> 2) * 128u;
+  uint32_t phase = 0;
+  bool failed = false;
+
+  const int64_t tile_lo = (int64_t)blockIdx.x * TC_M;
+  const int64_t tile_hi = tile_lo + TC_M < a.m ? tile_lo + TC_M : a.m;
+  const int b_first = segment_of(a.ptr_y, a.num_segments, tile_lo);
+  const int b_last = segment_of(a.ptr_y, a.num_segments, tile_hi - 1);
+  const float xmax = COSINE ? 1.f : *a.xmax;
+
+  for (int b = b_first; b <= b_last && !failed; ++b) {
+    int64_t y_lo, y_hi, x_lo, x_hi;
+    segment_rows(a.ptr_y, a.num_segments, a.m, b, y_lo, y_hi);
+    const int64_t q_lo = y_lo > tile_lo ? y_lo : tile_lo;
+    const int64_t q_hi = y_hi < tile_hi ? y_hi : tile_hi;
+    if (q_lo >= q_hi) continue;
+    segment_points(a.ptr_x, a.n, b, x_lo, x_hi);
+    const int64_t nx = x_hi > x_lo ? x_hi - x_lo : 0;
+    const int64_t q = q_lo + tid;
+    const bool have_q = q < q_hi;
+    if (nx == 0) {
+      if (have_q) a.cand_count[q] = 0;
+      continue;
+    }
+
+    // groups of `gs` consecutive points (a multiple of 32), at most TC_GMAX of them
+    const int64_t per = (nx + TC_GMAX - 1) / TC_GMAX;
+    const int gs = (int)((per + 31) / 32 * 32);
+    const int ngroups = (int)((nx + gs - 1) / gs);
+    const int ntiles = (int)((nx + TC_N - 1) / TC_N);
+
+    float qterm = 0.f, err = 0.f;  // a = xterm - 2 S + qterm (L2) or 1 - S (cosine); |a - d| <= err
+    if (COSINE) {
+      err = 0.00390625f * 1.05f + 1e-6f;  // 2 * 2^-9 on unit vectors, plus slack
+    } else if (have_q) {
+      qterm = a.sq_y[q];
+      const float qn = sqrtf(qterm);
+      err = 0.00390625f * 1.05f * qn * xmax + 4e-6f * (xmax * xmax + qterm);
+    }
+    float *my_gmin = gmin + tid * (TC_GMAX + 1);
+
+    stage_operand(sQ, a.ya, q_lo, q_hi, dim, tid);  // joins the first point tile's copy group
+
+    float thr = 0.f;
+    int ncand = 0;
+    for (int pass = 0; pass < 2 && !failed; ++pass) {
+      float run_min = pos_inf<float>();
+      int group = 0, in_group = 0;
+      for (int t = 0; t < ntiles && !failed; ++t) {
+        const int64_t p0 = x_lo + (int64_t)t * TC_N;
+        stage_operand(sX, a.xa, p0, x_hi, dim, tid);
+        if (!COSINE) s_sqx[tid] = p0 + tid < x_hi ? a.sq_x[p0 + tid] : 0.f;
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (tid == 0) {
+          for (int ks = 0; ks < (dim >> 3); ++ks) {
+            const uint64_t da = umma_desc(smem_u32(sQ) + ks * 256, 128, sbo);
+            const uint64_t db = umma_desc(smem_u32(sX) + ks * 256, 128, sbo);
+            const uint32_t accumulate = ks > 0 ? 1u : 0u;
+            asm volatile(
+                "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+                : "memory");
+          }
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                       ::"r"(smem_u32(&mbar))
+                       : "memory");
+        }
+        const bool arrived = mbar_wait(&mbar, phase);
+        if (__syncthreads_or(!arrived)) {  // the same decision for the whole CTA
+          failed = true;
+          break;
+        }
+        phase ^= 1u;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+        const int valid = (x_hi - p0) < TC_N ? (int)(x_hi - p0) : TC_N;
+#pragma unroll 1
+        for (int c0 = 0; c0 < TC_N; c0 += 32) {
+          uint32_t v[32];
+          tmem_load32(my_taddr + c0, v);
+          if (c0 >= valid) continue;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float s = __uint_as_float(v[j]);
+            const float approx = COSINE ? 1.f - s : __fmaf_rn(-2.f, s, s_sqx[c0 + j]) + qterm;
+            const bool ok = c0 + j < valid;
+            if (pass == 0) {
+              if (ok) run_min = fminf(run_min, approx);
+            } else if (ok && approx <= thr) {
+              if (ncand < TC_CAP && have_q) a.cand[q * TC_CAP + ncand] = (int32_t)(p0 + c0 + j);
+              ++ncand;
+            }
+          }
+          if (pass == 0) {
+            in_group += 32;
+            if (in_group >= gs) {  // groups are multiples of 32 points and start at the segment's first point
+              my_gmin[group++] = run_min;
+              run_min = pos_inf<float>();
+              in_group = 0;
+            }
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();  // everyone is done with sX, s_sqx and the accumulator
+      }
+      if (pass == 0 && !failed) {
+        if (in_group > 0) my_gmin[group++] = run_min;
+        // k-th smallest of this query's group minima (partial selection sort, thread-private row)
+        if (group >= a.k) {
+          for (int i = 0; i < a.k; ++i) {
+            int best = i;
+            float bv = my_gmin[i];
+            for (int j = i + 1; j < group; ++j) {
+              const float vj = my_gmin[j];
+              if (vj < bv) {
+                bv = vj;
+                best = j;
+              }
+            }
+            my_gmin[best] = my_gmin[i];
+            my_gmin[i] = bv;
+          }
+          thr = my_gmin[a.k - 1] + 2.f * err;
+          if (!(thr == thr)) thr = pos_inf<float>();  // NaN minima (degenerate rows): keep everything
+        } else {
+          thr = pos_inf<float>();  // fewer groups than k (short segment): the re-rank searches exhaustively
+        }
+        (void)ngroups;
+      }
+    }
+    if (have_q && !failed) a.cand_count[q] = ncand;
+    __syncthreads();
+  }
+  if (failed && tid == 0) *a.error_flag = 1;
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_N));
+}
+
+// ---- exact re-rank: one warp per query ---------------------------------------------------------------------
+constexpr int RR_WARPS = 4;
+
+template <bool COSINE>
+__global__ void __launch_bounds__(RR_WARPS * 32)
+knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, const int64_t *__restrict__ ptr_x,
+                  const int64_t *__restrict__ ptr_y, int num_segments, int64_t n, int64_t m, int dim, int k,
+                  const float *__restrict__ norms_x, const float *__restrict__ norms_y,
+                  const int32_t *__restrict__ cand, const int32_t *__restrict__ cand_count,
+                  const int *__restrict__ error_flag, int64_t *__restrict__ out_row, int64_t *__restrict__ out_col,
+                  int32_t *__restrict__ counts, unsigned long long *__restrict__ num_valid) {
+  using K = Key<float>;
+  constexpr int KP = 32;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // per warp: query row (dim floats, padded to 4), 2 * KP keys, queue fill
+  const int qstride = (dim + 3) & ~3;
+  float *my_q = reinterpret_cast<float *>(smem) + warp * qstride;
+  K *my_keys = reinterpret_cast<K *>(smem + (size_t)RR_WARPS * qstride * 4) + warp * 2 * KP;
+  int *my_cnt = reinterpret_cast<int *>(smem + (size_t)RR_WARPS * qstride * 4 + (size_t)RR_WARPS * 2 * KP * sizeof(K)) + warp;
+
+  const int64_t q = (int64_t)blockIdx.x * RR_WARPS + warp;
+  if (q >= m) return;
+  const int b = segment_of(ptr_y, num_segments, q);
+  int64_t x_lo, x_hi;
+  segment_points(ptr_x, n, b, x_lo, x_hi);
+
+  for (int d = lane; d < dim; d += 32) my_q[d] = y[q * dim + d];
+  knn_reset<float, KP>(my_keys, lane);
+  if (lane == 0) *my_cnt = 0;
+  __syncwarp();
+  const float ny = COSINE ? norms_y[q] : 1.f;
+
+  const int nc = cand_count[q];
+  const bool exhaustive = *error_flag != 0 || nc > TC_CAP;
+  const int64_t total = exhaustive ? (x_hi > x_lo ? x_hi - x_lo : 0) : nc;
+  float bound = 1e10f;
+  for (int64_t base = 0; base < total; base += 32) {
+    const int64_t i = base + lane;
+    float dist[1] = {pos_inf<float>()};
+    uint32_t idx = 0;
+    if (i < total) {
+      idx = exhaustive ? (uint32_t)(x_lo + i) : (uint32_t)cand[q * TC_CAP + i];
+      const float4 *row = reinterpret_cast<const float4 *>(x + (size_t)idx * dim);
+      float acc = 0.f;
+      for (int d4 = 0; d4 < (dim >> 2); ++d4) {
+        const float4 xv = row[d4];
+        const float4 qv = *reinterpret_cast<const float4 *>(my_q + 4 * d4);
+        if (COSINE) {
+          acc = __fmaf_rn(xv.x, qv.x, acc);
+          acc = __fmaf_rn(xv.y, qv.y, acc);
+          acc = __fmaf_rn(xv.z, qv.z, acc);
+          acc = __fmaf_rn(xv.w, qv.w, acc);
+        } else {
+          float df = xv.x - qv.x;
+          acc = __fmaf_rn(df, df, acc);
+          df = xv.y - qv.y;
+          acc = __fmaf_rn(df, df, acc);
+          df = xv.z - qv.z;
+          acc = __fmaf_rn(df, df, acc);
+          df = xv.w - qv.w;
+          acc = __fmaf_rn(df, df, acc);
+        }
+      }
+      dist[0] = COSINE ? 1.f - acc / (norms_x[idx] * ny) : acc;
+    }
+    if (__any_sync(FULL_MASK, dist[0] < bound)) {
+      // candidate r = 0 of lane l is offered with index idx0 + 32 * 0; pass the lane's own index
+      using K1 = Key<float>;
+      const bool hit = dist[0] < bound;
+      const unsigned mask = __ballot_sync(FULL_MASK, hit);
+      int cnt = *my_cnt;
+      const int nh = __popc(mask);
+      if (cnt + nh > KP) {
+        bound = knn_merge<float, KP>(my_keys, cnt, k, lane);
+        cnt = 0;
+      }
+      const bool hit2 = dist[0] < bound;
+      const unsigned mask2 = __ballot_sync(FULL_MASK, hit2);
+      if (hit2) my_keys[KP + cnt + __popc(mask2 & ((1u << lane) - 1u))] = K1::make(dist[0], idx);
+      cnt += __popc(mask2);
+      __syncwarp();
+      if (lane == 0) *my_cnt = cnt;
+      __syncwarp();
+    }
+  }
+  const int valid = knn_finish<float, KP>(my_keys, *my_cnt, k, q, out_row, out_col, lane);
+  if (lane == 0) {
+    counts[q] = valid;
+    if (valid) atomicAdd(num_valid, (unsigned long long)valid);
+  }
+}
+
+// |row|^2 (sequential fused sum), optional largest |row| (float bits, atomicMax) and optional normalised copy.
+__global__ void tensor_prep_kernel(const float *__restrict__ a, int64_t rows, int dim, float *__restrict__ sq,
+                                   unsigned *__restrict__ max_bits, float *__restrict__ normalised) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows) return;
+  float s = 0.f;
+  for (int d = 0; d < dim; ++d) {
+    const float v = a[i * dim + d];
+    s = __fmaf_rn(v, v, s);
+  }
+  if (sq) sq[i] = s;
+  const float nrm = sqrtf(s);
+  if (max_bits && nrm == nrm) atomicMax(max_bits, __float_as_uint(nrm));  // nrm >= 0: bits order like values
+  if (normalised)
+    for (int d = 0; d < dim; ++d) normalised[i * dim + d] = a[i * dim + d] / nrm;
+}
+
+size_t knn_tensor_smem_bytes(int dim) {
+  return 2 * (size_t)TC_M * dim * 4 + TC_N * 4 + (size_t)TC_M * (TC_GMAX + 1) * 4 + 1024;
+}
+
+static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
+
+// workspace: [sq_x n][sq_y m][xmax + error flag 256][cand m*CAP][cand_count m]
+//            cosine adds [norms_x n][norms_y m][xhat n*dim][yhat m*dim]
+size_t knn_tensor_workspace_bytes(int64_t n, int64_t m, int dim, int cosine) {
+  size_t b = al256((size_t)n * 4) + al256((size_t)m * 4) + 256 + al256((size_t)m * TC_CAP * 4) + al256((size_t)m * 4);
+  if (cosine) b += al256((size_t)n * 4) + al256((size_t)m * 4) + al256((size_t)n * dim * 4) + al256((size_t)m * dim * 4);
+  return b;
+}
+
+bool knn_tensor_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_segments, const void *x, const void *y) {
+  if (dim < 32 || dim > 128 || (dim & 7) || k > 32 || m < 1 || n < 1) return false;
+  if (((uintptr_t)x | (uintptr_t)y) & 15) return false;
+  return n / num_segments >= 32 * (int64_t)k;  // enough points per segment for k group minima, on average
+}
+
+int launch_knn_tensor_f32(const KnnArgs &a, void *workspace) {
+  char *ws = (char *)workspace;
+  float *sq_x = (float *)ws; ws += al256((size_t)a.n * 4);
+  float *sq_y = (float *)ws; ws += al256((size_t)a.m * 4);
+  float *xmax = (float *)ws;
+  int *error_flag = (int *)(ws + 128); ws += 256;
+  int32_t *cand = (int32_t *)ws; ws += al256((size_t)a.m * TC_CAP * 4);
+  int32_t *cand_count = (int32_t *)ws; ws += al256((size_t)a.m * 4);
+  float *norms_x = nullptr, *norms_y = nullptr, *xhat = nullptr, *yhat = nullptr;
+  if (a.cosine) {
+    norms_x = (float *)ws; ws += al256((size_t)a.n * 4);
+    norms_y = (float *)ws; ws += al256((size_t)a.m * 4);
+    xhat = (float *)ws; ws += al256((size_t)a.n * a.dim * 4);
+    yhat = (float *)ws; ws += al256((size_t)a.m * a.dim * 4);
+  }
+  B200C_CUDA(cudaMemsetAsync(xmax, 0, 256, a.stream));
+  const int threads = 128;
+  tensor_prep_kernel<<<(unsigned)((a.n + threads - 1) / threads), threads, 0, a.stream>>>(
+      (const float *)a.x, a.n, a.dim, sq_x, (unsigned *)xmax, xhat);
+  B200C_LAUNCH_CHECK("tensor_prep_kernel");
+  tensor_prep_kernel<<<(unsigned)((a.m + threads - 1) / threads), threads, 0, a.stream>>>(
+      (const float *)a.y, a.m, a.dim, sq_y, nullptr, yhat);
+  B200C_LAUNCH_CHECK("tensor_prep_kernel");
+  if (a.cosine) {
+    int st = launch_row_norms_f32(a.x, a.n, a.dim, norms_x, a.stream);
+    if (st != B200C_OK) return st;
+    st = launch_row_norms_f32(a.y, a.m, a.dim, norms_y, a.stream);
+    if (st != B200C_OK) return st;
+  }
+
+  TensorArgs t{a.cosine ? xhat : (const float *)a.x, a.cosine ? yhat : (const float *)a.y, sq_x, sq_y, xmax,
+               a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, cand, cand_count, error_flag};
+  const size_t smem = knn_tensor_smem_bytes(a.dim);
+  const unsigned ctas = (unsigned)((a.m + TC_M - 1) / TC_M);
+  if (a.cosine) {
+    B200C_CUDA(cudaFuncSetAttribute(knn_tensor_candidates_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    knn_tensor_candidates_kernel<true><<<ctas, TC_THREADS, smem, a.stream>>>(t);
+  } else {
+    B200C_CUDA(cudaFuncSetAttribute(knn_tensor_candidates_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    knn_tensor_candidates_kernel<false><<<ctas, TC_THREADS, smem, a.stream>>>(t);
+  }
+  B200C_LAUNCH_CHECK("knn_tensor_candidates_kernel");
+
+  const int qstride = (a.dim + 3) & ~3;
+  const size_t rr_smem = (size_t)RR_WARPS * qstride * 4 + (size_t)RR_WARPS * 64 * sizeof(Key<float>) + RR_WARPS * 4;
+  const unsigned rr_ctas = (unsigned)((a.m + RR_WARPS - 1) / RR_WARPS);
+  if (a.cosine)
+    knn_rerank_kernel<true><<<rr_ctas, RR_WARPS * 32, rr_smem, a.stream>>>(
+        (const float *)a.x, (const float *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, norms_x,
+        norms_y, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid);
+  else
+    knn_rerank_kernel<false><<<rr_ctas, RR_WARPS * 32, rr_smem, a.stream>>>(
+        (const float *)a.x, (const float *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, nullptr,
+        nullptr, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid);
+  B200C_LAUNCH_CHECK("knn_rerank_kernel");
+  return B200C_OK;
+}
+
+}  // namespace b200c

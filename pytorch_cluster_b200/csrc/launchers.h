@@ -48,4 +48,9 @@ int launch_radius_generic_f64(const RadiusArgs &a, bool fill);
 int launch_row_norms_f32(const void *a, int64_t rows, int dim, void *out, cudaStream_t s);
 int launch_row_norms_f64(const void *a, int64_t rows, int dim, void *out, cudaStream_t s);
 
+// tensor-core candidate path (fp32, 32 <= dim <= 128, dim % 8 == 0, k <= 32)
+bool knn_tensor_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_segments, const void *x, const void *y);
+size_t knn_tensor_workspace_bytes(int64_t n, int64_t m, int dim, int cosine);
+int launch_knn_tensor_f32(const KnnArgs &a, void *workspace);
+
 }  // namespace b200c

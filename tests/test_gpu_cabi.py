@@ -144,6 +144,42 @@ def test_knn_cosine_zero_rows():
     _check_knn(x, y, 6, cosine=True)
 
 
+# ---- tensor-core candidate path (fp32, 32 <= D <= 128, D % 8 == 0, k <= 32, long segments) ---------------
+
+@pytest.mark.parametrize("cosine", [False, True])
+@pytest.mark.parametrize("dim,k", [(64, 21), (32, 32), (128, 8), (40, 1)])
+def test_knn_tensor_path_equals_oracle(dim, k, cosine):
+    sx, sy = [2048, 1500, 3000], [700, 300, 1029]
+    x, y = _data(200 + dim, sum(sx), sum(sy), dim, torch.float32)
+    _check_knn(x, y, k, _segments(sx), _segments(sy), cosine=cosine)
+
+
+def test_knn_tensor_path_short_and_empty_segments():
+    # some segments are far too short for k group minima: those queries are searched exhaustively
+    sx, sy = [4000, 5, 0, 3000, 40, 2500], [300, 7, 3, 0, 50, 260]
+    x, y = _data(301, sum(sx), sum(sy), 64, torch.float32)
+    _check_knn(x, y, 16, _segments(sx), _segments(sy))
+    _check_knn(x, y, 16, _segments(sx), _segments(sy), cosine=True)
+
+
+def test_knn_tensor_path_ties_and_scale():
+    # coarse grid => many exactly equal distances; large offsets => big |x| next to small distances
+    x, y = _data(302, 6000, 500, 64, torch.float32, grid=2)
+    _check_knn(x, y, 21)
+    x2, y2 = _data(303, 5000, 300, 64, torch.float32)
+    _check_knn(x2 + 50.0, y2 + 50.0, 21)
+    _check_knn(torch.cat([x2[:2500], x2[:2500]]), y2, 20)   # exact duplicates
+
+
+def test_knn_tensor_path_config4_slice():
+    # four clouds of the EdgeConv configuration: 2048 points, 64 features, k = 20 (+1)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(4 * 2048, 64, generator=g)
+    ptr = torch.arange(0, 4 * 2048 + 1, 2048)
+    _check_knn(x, x, 21, ptr, ptr)
+    _check_knn(x, x, 21, ptr, ptr, cosine=True)
+
+
 # ---- radius ---------------------------------------------------------------------------------------
 
 def _check_radius(x, y, r, px=None, py=None, max_nn=32, ignore=False):
