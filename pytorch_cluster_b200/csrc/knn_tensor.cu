@@ -2,8 +2,10 @@
 //
 // Stage 1, knn_tensor_candidates_kernel — tcgen05 / TMEM.  A CTA owns 128 query rows.  The query
 // tile and, one after the other, 128-point tiles of the queries' segment are laid out in shared
-// memory in the canonical K-major, no-swizzle operand layout of the 5th-generation tensor cores
-// (8 x 16-byte core matrices; cp.async, 16 bytes per copy); one thread issues D / 8
+// memory in the K-major, 128-byte-swizzled operand layout of the 5th-generation tensor cores (rows
+// of 32 tf32 values = 128 bytes, 16-byte chunk c of row r stored at chunk c ^ (r & 7); cp.async, 16
+// bytes per copy, coalesced on the global side and conflict-free on the shared side; the copy of
+// the next tile runs while the current one is read back); one thread issues D / 8
 // `tcgen05.mma.cta_group::1.kind::tf32` instructions (M = 128, N = 128, K = 8) that accumulate
 // S = Q X^T into 128 columns of tensor memory, `tcgen05.commit` signals an mbarrier, and every
 // thread reads back its own query's row with `tcgen05.ld.32x32b`.  From S the approximate distance
@@ -40,14 +42,15 @@ constexpr int TC_SPIN_LIMIT = 1 << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-// Shared-memory matrix descriptor, K-major, no swizzle: start address, leading byte offset (between
-// the two 16-byte K slices of one MMA), stride byte offset (between 8-row groups), version 1.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address, stride byte offset
+// 1024 (8 rows of 128 bytes), leading byte offset unused, descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3fffu);
-  d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
-  d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
   d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
   return d;
 }
 
@@ -55,18 +58,18 @@ __device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
 }
 
-// rows [row0, row0 + 128) of src ([*, dim] row-major) into the canonical operand layout:
-// (row, 16-byte K slice s) -> (row / 8) * sbo + s * 128 + (row % 8) * 16.  Rows >= row_end are zero.
+// Rows [row0, row0 + 128) of src ([*, dim] row-major) into the swizzled operand layout: features
+// [32 a, 32 a + 32) of all rows form "atom" a (128 rows x 128 bytes = 16 KiB); inside an atom the
+// 16-byte chunk c of row r sits at r * 128 + ((c ^ (r & 7)) * 16).  Rows >= row_end are zero.
 __device__ __forceinline__ void stage_operand(unsigned char *dst, const float *__restrict__ src, int64_t row0,
                                               int64_t row_end, int dim, int tid) {
-  const int slices = dim >> 2;
-  const uint32_t sbo = (uint32_t)slices * 128u;
-  for (int p = tid; p < TC_M * slices; p += TC_THREADS) {
-    const int row = p & (TC_M - 1), s = p >> 7;
-    unsigned char *d = dst + (row >> 3) * sbo + s * 128 + (row & 7) * 16;
+  const int chunks = dim >> 2;  // 16-byte chunks per row
+  for (int p = tid; p < TC_M * chunks; p += TC_THREADS) {
+    const int row = p / chunks, ch = p - row * chunks;  // consecutive threads: consecutive chunks of a row
+    unsigned char *d = dst + (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
     const int64_t g = row0 + row;
     if (g < row_end)
-      cp_async_16(d, src + g * dim + s * 4);
+      cp_async_16(d, src + g * dim + ch * 4);
     else
       *reinterpret_cast<float4 *>(d) = make_float4(0.f, 0.f, 0.f, 0.f);
   }
@@ -98,6 +101,26 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Ascending bitonic sort of 64 values held in registers (all indices are compile-time constants).
+__device__ __forceinline__ void sort64(float (&v)[64]) {
+#pragma unroll
+  for (int size = 2; size <= 64; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const int l = i ^ stride;
+        if (l > i) {
+          const float lo = fminf(v[i], v[l]), hi = fmaxf(v[i], v[l]);
+          const bool asc = (i & size) == 0;
+          v[i] = asc ? lo : hi;
+          v[l] = asc ? hi : lo;
+        }
+      }
+    }
+  }
+}
+
 struct TensorArgs {
   const float *xa, *ya;        // operands of the product: x, y (L2) or their normalised copies (cosine)
   const float *sq_x, *sq_y;    // L2: |row|^2 ; cosine: unused
@@ -115,11 +138,11 @@ template <bool COSINE>
 __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(TensorArgs a) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int dim = a.dim;
-  const uint32_t tile_bytes = (uint32_t)TC_M * dim * 4;
+  const uint32_t tile_bytes = (uint32_t)((dim + 31) >> 5) * 16384u;  // whole atoms of 32 features
   unsigned char *sQ = smem;
   unsigned char *sX = smem + tile_bytes;
-  float *s_sqx = reinterpret_cast<float *>(smem + 2 * tile_bytes);  // |x|^2 of the current tile
-  float *gmin = s_sqx + TC_N;                                       // [TC_M][TC_GMAX + 1]
+  float *s_sqx = reinterpret_cast<float *>(smem + 2 * tile_bytes);  // |x|^2 of the current and the next tile
+  float *gmin = s_sqx + 2 * TC_N;                                   // [TC_M][TC_GMAX + 1]
   __shared__ __align__(8) uint64_t mbar;
   __shared__ uint32_t tmem_base_s;
 
@@ -138,7 +161,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
   // D = f32, A = B = tf32, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TC_N >> 3) << 17) |
                          ((uint32_t)(TC_M >> 4) << 24);
-  const uint32_t sbo = (uint32_t)(dim >> 2) * 128u;
   uint32_t phase = 0;
   bool failed = false;
 
@@ -169,13 +191,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
     const int ngroups = (int)((nx + gs - 1) / gs);
     const int ntiles = (int)((nx + TC_N - 1) / TC_N);
 
-    float qterm = 0.f, err = 0.f;  // a = xterm - 2 S + qterm (L2) or 1 - S (cosine); |a - d| <= err
-    if (COSINE) {
-      err = 0.00390625f * 1.05f + 1e-6f;  // 2 * 2^-9 on unit vectors, plus slack
-    } else if (have_q) {
-      qterm = a.sq_y[q];
-      const float qn = sqrtf(qterm);
-      err = 0.00390625f * 1.05f * qn * xmax + 4e-6f * (xmax * xmax + qterm);
+    // Everything is compared in "shifted" form a' = bias_x + scale * S, i.e. the approximate distance
+    // minus the query's own constant (|q|^2 for L2, 1 for cosine): bias_x = |x|^2 or 0, +inf for
+    // columns past the segment's end; scale = -2 or -1.  err bounds |a' - (d_exact - constant)|.
+    const float scale = COSINE ? -1.f : -2.f;
+    float err = 0.00390625f * 1.05f + 1e-6f;  // cosine: 2 * 2^-9 on unit vectors, plus slack
+    if (!COSINE && have_q) {
+      const float qsq = a.sq_y[q];
+      err = 0.00390625f * 1.05f * sqrtf(qsq) * xmax + 4e-6f * (xmax * xmax + qsq);
     }
     float *my_gmin = gmin + tid * (TC_GMAX + 1);
 
@@ -186,19 +209,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
     for (int pass = 0; pass < 2 && !failed; ++pass) {
       float run_min = pos_inf<float>();
       int group = 0, in_group = 0;
+      // first tile of the pass (the query tile's copies, issued above, join this group in pass A)
+      stage_operand(sX, a.xa, x_lo, x_hi, dim, tid);
+      s_sqx[tid] = x_lo + tid < x_hi ? (COSINE ? 0.f : a.sq_x[x_lo + tid]) : pos_inf<float>();
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
       for (int t = 0; t < ntiles && !failed; ++t) {
         const int64_t p0 = x_lo + (int64_t)t * TC_N;
-        stage_operand(sX, a.xa, p0, x_hi, dim, tid);
-        if (!COSINE) s_sqx[tid] = p0 + tid < x_hi ? a.sq_x[p0 + tid] : 0.f;
-        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
+        __syncthreads();  // tile t is in place; everyone has finished reading the accumulator of tile t - 1
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (tid == 0) {
           for (int ks = 0; ks < (dim >> 3); ++ks) {
-            const uint64_t da = umma_desc(smem_u32(sQ) + ks * 256, 128, sbo);
-            const uint64_t db = umma_desc(smem_u32(sX) + ks * 256, 128, sbo);
+            const uint32_t off = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
+            const uint64_t da = umma_desc_sw128(smem_u32(sQ) + off);
+            const uint64_t db = umma_desc_sw128(smem_u32(sX) + off);
             const uint32_t accumulate = ks > 0 ? 1u : 0u;
             asm volatile(
                 "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
@@ -217,61 +243,69 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
         }
         phase ^= 1u;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // the tensor core is done with sX: fetch the next tile while this one is read back
+        if (t + 1 < ntiles) {
+          const int64_t p1 = p0 + TC_N;
+          stage_operand(sX, a.xa, p1, x_hi, dim, tid);
+          s_sqx[((t + 1) & 1) * TC_N + tid] = p1 + tid < x_hi ? (COSINE ? 0.f : a.sq_x[p1 + tid]) : pos_inf<float>();
+          asm volatile("cp.async.commit_group;\n" ::: "memory");
+        }
+        const float *sqx = s_sqx + (t & 1) * TC_N;
 
         const int valid = (x_hi - p0) < TC_N ? (int)(x_hi - p0) : TC_N;
 #pragma unroll 1
         for (int c0 = 0; c0 < TC_N; c0 += 32) {
           uint32_t v[32];
           tmem_load32(my_taddr + c0, v);
-          if (c0 >= valid) continue;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float s = __uint_as_float(v[j]);
-            const float approx = COSINE ? 1.f - s : __fmaf_rn(-2.f, s, s_sqx[c0 + j]) + qterm;
-            const bool ok = c0 + j < valid;
-            if (pass == 0) {
-              if (ok) run_min = fminf(run_min, approx);
-            } else if (ok && approx <= thr) {
-              if (ncand < TC_CAP && have_q) a.cand[q * TC_CAP + ncand] = (int32_t)(p0 + c0 + j);
-              ++ncand;
-            }
-          }
+          if (c0 >= valid) continue;  // uniform: a block past the segment's end
           if (pass == 0) {
+            float m = run_min;
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              const float4 bx = *reinterpret_cast<const float4 *>(sqx + c0 + 4 * j4);
+              m = fminf(m, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 0]), bx.x));
+              m = fminf(m, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 1]), bx.y));
+              m = fminf(m, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 2]), bx.z));
+              m = fminf(m, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 3]), bx.w));
+            }
+            run_min = m;
             in_group += 32;
             if (in_group >= gs) {  // groups are multiples of 32 points and start at the segment's first point
               my_gmin[group++] = run_min;
               run_min = pos_inf<float>();
               in_group = 0;
             }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float ap = __fmaf_rn(scale, __uint_as_float(v[j]), sqx[c0 + j]);
+              if (ap <= thr) {  // rare
+                if (ncand < TC_CAP && have_q) a.cand[q * TC_CAP + ncand] = (int32_t)(p0 + c0 + j);
+                ++ncand;
+              }
+            }
           }
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();  // everyone is done with sX, s_sqx and the accumulator
       }
       if (pass == 0 && !failed) {
         if (in_group > 0) my_gmin[group++] = run_min;
-        // k-th smallest of this query's group minima (partial selection sort, thread-private row)
+        // k-th smallest of this query's group minima: k different points lie at or below it
         if (group >= a.k) {
-          for (int i = 0; i < a.k; ++i) {
-            int best = i;
-            float bv = my_gmin[i];
-            for (int j = i + 1; j < group; ++j) {
-              const float vj = my_gmin[j];
-              if (vj < bv) {
-                bv = vj;
-                best = j;
-              }
-            }
-            my_gmin[best] = my_gmin[i];
-            my_gmin[i] = bv;
-          }
-          thr = my_gmin[a.k - 1] + 2.f * err;
-          if (!(thr == thr)) thr = pos_inf<float>();  // NaN minima (degenerate rows): keep everything
+          float g[TC_GMAX];
+#pragma unroll
+          for (int i = 0; i < TC_GMAX; ++i) g[i] = i < group ? my_gmin[i] : pos_inf<float>();
+          sort64(g);
+          float kth = g[0];
+#pragma unroll
+          for (int i = 1; i < 32; ++i) kth = (i == a.k - 1) ? g[i] : kth;  // k <= 32
+          thr = kth + 2.f * err;
+          if (!(thr < 3.0e38f)) thr = 3.0e38f;  // NaN or infinite: keep every real column (padding is +inf)
         } else {
-          thr = pos_inf<float>();  // fewer groups than k (short segment): the re-rank searches exhaustively
+          thr = 3.0e38f;  // fewer groups than k (short segment): keep every real column (padding is +inf)
         }
         (void)ngroups;
       }
+      __syncthreads();  // all read-backs of this pass are done before its buffers are restaged
     }
     if (have_q && !failed) a.cand_count[q] = ncand;
     __syncthreads();
@@ -394,7 +428,7 @@ __global__ void tensor_prep_kernel(const float *__restrict__ a, int64_t rows, in
 }
 
 size_t knn_tensor_smem_bytes(int dim) {
-  return 2 * (size_t)TC_M * dim * 4 + TC_N * 4 + (size_t)TC_M * (TC_GMAX + 1) * 4 + 1024;
+  return 2 * (size_t)((dim + 31) / 32) * 16384 + 2 * TC_N * 4 + (size_t)TC_M * (TC_GMAX + 1) * 4 + 1024;
 }
 
 static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
