@@ -1,6 +1,6 @@
 """Benchmark of the neighbour-graph path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extra]
 
 Headline workload (``knn_graph_batched``): 32 clouds x 4096 points, 3-D fp32 ~ N(0,1), sorted
 batch vector, k = 20, loop = False — synthetic, seeded.  One step = one ``knn_graph`` call over
@@ -11,7 +11,8 @@ the whole batch.  Printed: ONE JSON line with
   roofline    of the dominant kernel (knn_lowd_kernel, FP32-pipe bound): 8 flop per
               (query, point) pair / its CUDA-event time when launched alone through the C ABI
   cpu_baseline  the reference's own CPU path (oracle/_ref: kd-tree search, single thread)
-  extra       further workloads (large bipartite kNN, radius_graph), same method
+  extra       the other configurations (single cloud, large bipartite kNN, 64-D feature kNN with and
+              without cosine, radius_graph with and without truncation), kernel/API times and rates
 
 ``--impl reference`` times the reference's CPU implementation on the same workload instead.
 With N > 1 (torchrun) every rank runs the workload on its own clouds (weak scaling, no
@@ -34,6 +35,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FP32_LANES_PER_SM = 128
+KNN_LOWD_CFG2_DRAM_BYTES = None  # filled from the ncu capture summarised under profiles/
 L2_FLUSH_BYTES = 256 << 20
 
 
@@ -86,7 +88,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -160,6 +162,74 @@ def load_peaks():
         return {}
 
 
+def fp32_peak_tf(props, peaks):
+    sm_max = peaks.get("sm_max_mhz") or 1965.0
+    return props.multi_processor_count * FP32_LANES_PER_SM * 2 * sm_max * 1e6 / 1e12
+
+
+def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank):
+    """The other configurations, a few repetitions each: kernel time through the C ABI and call time
+    through the public API, with the rates they imply."""
+    reps, warm = 5, 2
+    out = {}
+
+    def ms_of(fn):
+        return timed_steps(fn, reps, warm, flush) / reps
+
+    # one cloud of 1024 points, k = 16
+    g = torch.Generator().manual_seed(1)
+    x1 = torch.rand(1024, 3, generator=g).to(dev)
+    t = ms_of(lambda: pc.knn_graph(x1, 16))
+    out["knn_graph_1024x3_k16"] = {"api_ms": t, "queries_per_s": 1024 / (t * 1e-3)}
+
+    # large bipartite kNN: 8 clouds x (131072 points, 8192 queries), k = 32
+    w = make_knn_bipartite()
+    x, y = w["x"].to(dev), w["y"].to(dev)
+    bx, by = w["batch_x"].to(dev), w["batch_y"].to(dev)
+    px, py = torch.ops.torch_cluster.segment_ptr(bx, 8), torch.ops.torch_cluster.segment_ptr(by, 8)
+    tk = ms_of(lambda: cabi.knn_padded_nosync(x, y, 32, px, py))
+    ta = ms_of(lambda: pc.knn(x, y, 32, bx, by))
+    out["knn_bipartite_8x131072x8192_k32"] = {
+        "kernel_ms": tk, "api_ms": ta, "queries_per_s": w["queries"] / (ta * 1e-3),
+        "fp32_frac": 8.0 * w["pairs"] / (tk * 1e-3) / 1e12 / peak_tf}
+    if world > 1:
+        from pytorch_cluster_b200 import knn_sharded
+
+        ts = max_over_ranks(ms_of(lambda: knn_sharded(x, y, 32, bx, by, batch_size=8)), world)
+        tl = max_over_ranks(ms_of(lambda: knn_sharded(x, y, 32, bx, by, batch_size=8, assemble=False)), world)
+        out["knn_bipartite_8x131072x8192_k32"].update(
+            {"sharded_ms": ts, "sharded_no_assembly_ms": tl, "sharded_queries_per_s": w["queries"] / (ts * 1e-3)})
+    del x, y
+
+    # feature-space kNN: 16 clouds x 2048 points x 64 features, k = 20
+    g = torch.Generator().manual_seed(4)
+    xf = torch.randn(32768, 64, generator=g).to(dev)
+    bf = torch.arange(16).repeat_interleave(2048).to(dev)
+    pf = torch.ops.torch_cluster.segment_ptr(bf, 16)
+    for cosine in (False, True):
+        tk = ms_of(lambda: cabi.knn_padded_nosync(xf, xf, 21, pf, pf, cosine))
+        ta = ms_of(lambda: pc.knn_graph(xf, 20, bf, cosine=cosine))
+        out["knn_graph_16x2048x64_k20_cosine" if cosine else "knn_graph_16x2048x64_k20"] = {
+            "kernel_ms": tk, "api_ms": ta, "queries_per_s": 32768 / (ta * 1e-3)}
+
+    # radius_graph on a clustered density: 64 clouds x 8192 points, r = 0.05
+    w = make_radius_mixture()
+    xr, br = w["x"].to(dev), w["batch"].to(dev)
+    for max_nn in (64, 8192):
+        e = pc.radius_graph(xr, w["r"], br, max_num_neighbors=max_nn)
+        ta = ms_of(lambda: pc.radius_graph(xr, w["r"], br, max_num_neighbors=max_nn))
+        rec = {"api_ms": ta, "edges": int(e.shape[1]), "edges_per_s": e.shape[1] / (ta * 1e-3),
+               "fp32_frac": 8.0 * w["pairs"] / (ta * 1e-3) / 1e12 / peak_tf}
+        if world > 1:
+            from pytorch_cluster_b200 import radius_sharded
+
+            ts = max_over_ranks(ms_of(lambda: radius_sharded(xr, xr, w["r"], br, br, max_num_neighbors=max_nn,
+                                                             batch_size=64, assemble=False)), world)
+            rec["sharded_no_assembly_ms"] = ts
+        out[f"radius_graph_64x8192x3_r0.05_max{max_nn}"] = rec
+    return out
+
+
 # ---- reference arm (CPU) ------------------------------------------------------------------------------
 
 def reference_knn_graph_cpu(x, k, batch, clouds):
@@ -223,13 +293,14 @@ def run_ours(args, rank, world, local_rank):
     def step_resident():
         return pc.knn_graph(x, k, batch)
 
-    out_host = {}
+    out_pinned = torch.empty(2, w["queries"] * k, dtype=torch.long).pin_memory()
 
     def step_e2e():
         dx = hx.to(dev, non_blocking=True)
         db = hb.to(dev, non_blocking=True)
         e = pc.knn_graph(dx, k, db)
-        out_host["e"] = e.cpu()
+        out_pinned.copy_(e, non_blocking=True)  # same shape: every node has k neighbours here
+        torch.cuda.current_stream().synchronize()
 
     e0 = step_resident()
     edges = e0.shape[1]
@@ -240,24 +311,26 @@ def run_ours(args, rank, world, local_rank):
 
         dist.barrier()
     torch.cuda.synchronize()
+    ptr = torch.ops.torch_cluster.segment_ptr(batch, w["clouds"])
     with ClockSampler(local_rank) as clocks:
         ms = timed_steps(step_resident, args.steps, args.warmup, flush)
         torch.cuda.synchronize()
-    ms = max_over_ranks(ms, world)
-    if world > 1:
-        dist.barrier()
-    ms_e2e = max_over_ranks(timed_steps(step_e2e, args.steps, args.warmup, flush), world)
-
-    # dominant kernel alone, through the C ABI (memset of one counter + one kernel launch)
-    ptr = torch.ops.torch_cluster.segment_ptr(batch, w["clouds"])
-    ms_kernel = timed_steps(lambda: _cabi.knn_padded_nosync(x, x, k + 1, ptr, ptr), args.steps, args.warmup, flush)
-    ms_kernel = max_over_ranks(ms_kernel, world)
+        ms = max_over_ranks(ms, world)
+        if world > 1:
+            dist.barrier()
+        ms_e2e = max_over_ranks(timed_steps(step_e2e, args.steps, args.warmup, flush), world)
+        # dominant kernel alone, through the C ABI (memset of one counter + one kernel launch)
+        ms_kernel = timed_steps(lambda: _cabi.knn_padded_nosync(x, x, k + 1, ptr, ptr), args.steps, args.warmup,
+                                flush)
+        ms_kernel = max_over_ranks(ms_kernel, world)
+        extra = {} if args.no_extra else extra_workloads(pc, _cabi, dev, flush, fp32_peak_tf(props, load_peaks()),
+                                                         world, rank)
 
     if rank != 0:
         return
     total_queries = w["queries"] * world
     sm_max = peaks.get("sm_max_mhz") or 1965.0
-    fp32_peak = props.multi_processor_count * FP32_LANES_PER_SM * 2 * sm_max * 1e6 / 1e12
+    fp32_peak = fp32_peak_tf(props, peaks)
     flops = 8.0 * w["pairs"]
     achieved = flops / (ms_kernel / args.steps * 1e-3) / 1e12
     line = {
@@ -274,7 +347,11 @@ def run_ours(args, rank, world, local_rank):
                      "peak": fp32_peak, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
                      "peak_source": f"nominal: {props.multi_processor_count} SMs x 128 lanes x 2 flop x "
                                     f"{sm_max:.0f} MHz (MEASURED_PEAKS.json holds no fp32 figure)",
-                     "flops_per_launch": flops, "ms_per_launch": ms_kernel / args.steps, "traffic": None},
+                     "flops_per_launch": flops, "ms_per_launch": ms_kernel / args.steps,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu, profiles/): the 1.6 MB
+                     # input is read once; the 44 MB of output mostly still sits in L2 when the kernel ends
+                     "traffic": KNN_LOWD_CFG2_DRAM_BYTES},
+        "extra": extra,
     }
     if not args.no_cpu_baseline:
         from oracle import reference_cpu as rc
@@ -298,6 +375,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

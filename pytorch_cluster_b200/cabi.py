@@ -37,24 +37,25 @@ def exclusive_scan(counts):
     return offsets
 
 
-def knn_padded_nosync(x, y, k, ptr_x=None, ptr_y=None, cosine=False):
-    """-> (edge_padded int64 [2, m*k], counts int32 [m], num_valid int64 [1]); nothing is read back."""
+def knn_padded_nosync(x, y, k, ptr_x=None, ptr_y=None, cosine=False, workspace=True):
+    """-> (edge_padded int64 [2, m*k], counts int32 [m], num_valid int64 [1]); nothing is read back.
+    workspace=False withholds the optional workspace, which selects the kernels that need none."""
     lib = _native.cabi()
     n, m, dim = x.shape[0], y.shape[0], x.shape[1]
     nseg = 1 if ptr_x is None else ptr_x.numel() - 1
     padded = torch.empty(2, m * k, dtype=torch.long, device=x.device)
     counts = torch.empty(m, dtype=torch.int32, device=x.device)
     nvalid = torch.empty(1, dtype=torch.long, device=x.device)
-    nbytes = lib.b200c_knn_workspace_bytes(n, m, dim, k, _dtype(x), int(cosine), nseg)
+    nbytes = lib.b200c_knn_workspace_bytes(n, m, dim, k, _dtype(x), int(cosine), nseg) if (workspace or cosine) else 0
     ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
     _native.check(lib.b200c_knn(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, k, _dtype(x),
                                 int(cosine), _p(padded), _p(counts), _p(nvalid), _p(ws), nbytes, _stream()))
     return padded, counts, nvalid
 
 
-def knn_padded(x, y, k, ptr_x=None, ptr_y=None, cosine=False):
+def knn_padded(x, y, k, ptr_x=None, ptr_y=None, cosine=False, workspace=True):
     """-> (edge_padded int64 [2, m*k], counts int32 [m], num_valid int)"""
-    padded, counts, nvalid = knn_padded_nosync(x, y, k, ptr_x, ptr_y, cosine)
+    padded, counts, nvalid = knn_padded_nosync(x, y, k, ptr_x, ptr_y, cosine, workspace)
     return padded, counts, int(nvalid.item())
 
 

@@ -349,6 +349,7 @@ knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, cons
   if (lane == 0) *my_cnt = 0;
   __syncwarp();
   const float ny = COSINE ? norms_y[q] : 1.f;
+  const bool vec4 = (dim & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;  // rows are whole float4s
 
   const int nc = cand_count[q];
   const bool exhaustive = *error_flag != 0 || nc > TC_CAP;
@@ -360,25 +361,37 @@ knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, cons
     uint32_t idx = 0;
     if (i < total) {
       idx = exhaustive ? (uint32_t)(x_lo + i) : (uint32_t)cand[q * TC_CAP + i];
-      const float4 *row = reinterpret_cast<const float4 *>(x + (size_t)idx * dim);
       float acc = 0.f;
-      for (int d4 = 0; d4 < (dim >> 2); ++d4) {
-        const float4 xv = row[d4];
-        const float4 qv = *reinterpret_cast<const float4 *>(my_q + 4 * d4);
-        if (COSINE) {
-          acc = __fmaf_rn(xv.x, qv.x, acc);
-          acc = __fmaf_rn(xv.y, qv.y, acc);
-          acc = __fmaf_rn(xv.z, qv.z, acc);
-          acc = __fmaf_rn(xv.w, qv.w, acc);
-        } else {
-          float df = xv.x - qv.x;
-          acc = __fmaf_rn(df, df, acc);
-          df = xv.y - qv.y;
-          acc = __fmaf_rn(df, df, acc);
-          df = xv.z - qv.z;
-          acc = __fmaf_rn(df, df, acc);
-          df = xv.w - qv.w;
-          acc = __fmaf_rn(df, df, acc);
+      if (vec4) {
+        const float4 *row = reinterpret_cast<const float4 *>(x + (size_t)idx * dim);
+        for (int d4 = 0; d4 < (dim >> 2); ++d4) {
+          const float4 xv = row[d4];
+          const float4 qv = *reinterpret_cast<const float4 *>(my_q + 4 * d4);
+          if (COSINE) {
+            acc = __fmaf_rn(xv.x, qv.x, acc);
+            acc = __fmaf_rn(xv.y, qv.y, acc);
+            acc = __fmaf_rn(xv.z, qv.z, acc);
+            acc = __fmaf_rn(xv.w, qv.w, acc);
+          } else {
+            float df = xv.x - qv.x;
+            acc = __fmaf_rn(df, df, acc);
+            df = xv.y - qv.y;
+            acc = __fmaf_rn(df, df, acc);
+            df = xv.z - qv.z;
+            acc = __fmaf_rn(df, df, acc);
+            df = xv.w - qv.w;
+            acc = __fmaf_rn(df, df, acc);
+          }
+        }
+      } else {
+        const float *row = x + (size_t)idx * dim;
+        for (int d = 0; d < dim; ++d) {
+          if (COSINE) {
+            acc = __fmaf_rn(row[d], my_q[d], acc);
+          } else {
+            const float df = row[d] - my_q[d];
+            acc = __fmaf_rn(df, df, acc);
+          }
         }
       }
       dist[0] = COSINE ? 1.f - acc / (norms_x[idx] * ny) : acc;
@@ -447,6 +460,24 @@ bool knn_tensor_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_seg
   return n / num_segments >= 32 * (int64_t)k;  // enough points per segment for k group minima, on average
 }
 
+// Exact re-rank of candidate lists ([m, 128] int32 + counts); shared with the low-dimensional screen.
+int launch_knn_rerank_f32(const KnnArgs &a, const int32_t *cand, const int32_t *cand_count, const int *error_flag,
+                          const float *norms_x, const float *norms_y) {
+  const int qstride = (a.dim + 3) & ~3;
+  const size_t rr_smem = (size_t)RR_WARPS * qstride * 4 + (size_t)RR_WARPS * 64 * sizeof(Key<float>) + RR_WARPS * 4;
+  const unsigned rr_ctas = (unsigned)((a.m + RR_WARPS - 1) / RR_WARPS);
+  if (a.cosine)
+    knn_rerank_kernel<true><<<rr_ctas, RR_WARPS * 32, rr_smem, a.stream>>>(
+        (const float *)a.x, (const float *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, norms_x,
+        norms_y, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid);
+  else
+    knn_rerank_kernel<false><<<rr_ctas, RR_WARPS * 32, rr_smem, a.stream>>>(
+        (const float *)a.x, (const float *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, nullptr,
+        nullptr, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid);
+  B200C_LAUNCH_CHECK("knn_rerank_kernel");
+  return B200C_OK;
+}
+
 int launch_knn_tensor_f32(const KnnArgs &a, void *workspace) {
   char *ws = (char *)workspace;
   float *sq_x = (float *)ws; ws += al256((size_t)a.n * 4);
@@ -490,19 +521,7 @@ int launch_knn_tensor_f32(const KnnArgs &a, void *workspace) {
   }
   B200C_LAUNCH_CHECK("knn_tensor_candidates_kernel");
 
-  const int qstride = (a.dim + 3) & ~3;
-  const size_t rr_smem = (size_t)RR_WARPS * qstride * 4 + (size_t)RR_WARPS * 64 * sizeof(Key<float>) + RR_WARPS * 4;
-  const unsigned rr_ctas = (unsigned)((a.m + RR_WARPS - 1) / RR_WARPS);
-  if (a.cosine)
-    knn_rerank_kernel<true><<<rr_ctas, RR_WARPS * 32, rr_smem, a.stream>>>(
-        (const float *)a.x, (const float *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, norms_x,
-        norms_y, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid);
-  else
-    knn_rerank_kernel<false><<<rr_ctas, RR_WARPS * 32, rr_smem, a.stream>>>(
-        (const float *)a.x, (const float *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, nullptr,
-        nullptr, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid);
-  B200C_LAUNCH_CHECK("knn_rerank_kernel");
-  return B200C_OK;
+  return launch_knn_rerank_f32(a, cand, cand_count, error_flag, norms_x, norms_y);
 }
 
 }  // namespace b200c

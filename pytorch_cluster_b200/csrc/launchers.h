@@ -52,5 +52,8 @@ int launch_row_norms_f64(const void *a, int64_t rows, int dim, void *out, cudaSt
 bool knn_tensor_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_segments, const void *x, const void *y);
 size_t knn_tensor_workspace_bytes(int64_t n, int64_t m, int dim, int cosine);
 int launch_knn_tensor_f32(const KnnArgs &a, void *workspace);
+int launch_knn_rerank_f32(const KnnArgs &a, const int32_t *cand, const int32_t *cand_count, const int *error_flag,
+                          const float *norms_x, const float *norms_y);
+
 
 }  // namespace b200c

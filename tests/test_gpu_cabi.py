@@ -33,6 +33,10 @@ def _check_knn(x, y, k, px=None, py=None, cosine=False):
     dpy = None if py is None else py.to(DEV)
     padded, counts, nvalid = _cabi.knn_padded(dx, dy, k, dpx, dpy, cosine)
     torch.cuda.synchronize()
+    # the same without the optional workspace: the kernels that screen or use tensor cores need it,
+    # so this exercises the plain exact kernels
+    plain, plain_counts, plain_valid = _cabi.knn_padded(dx, dy, k, dpx, dpy, cosine, workspace=False)
+    assert torch.equal(plain, padded) and torch.equal(plain_counts, counts) and plain_valid == nvalid
     want_col, _ = orc.knn_padded(x.numpy(), y.numpy(), k, None if px is None else px.numpy(),
                                  None if py is None else py.numpy(), cosine=cosine)
     m = y.shape[0]
