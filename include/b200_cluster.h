@@ -103,7 +103,9 @@ int b200c_exclusive_scan_static(const int32_t *counts, int64_t m, int64_t *offse
  * form already is the final edge_index; otherwise run b200c_exclusive_scan on
  * counts and b200c_knn_compact.
  *
- * workspace: b200c_knn_workspace_bytes(...) bytes (may be 0). */
+ * workspace: b200c_knn_workspace_bytes(...) bytes (may be 0).  Only the cosine distance needs
+ * one (the rows' norms); the full size additionally enables the tensor-core candidate path for
+ * fp32 features (32 <= dim <= 128, dim % 8 == 0, k <= 32), without it the exact kernels run. */
 size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t k,
                                  int dtype, int cosine, int64_t num_segments);
 int b200c_knn(const void *x, const void *y, const int64_t *ptr_x,
@@ -118,6 +120,20 @@ int b200c_knn_compact(const int64_t *edge_padded, const int32_t *counts,
                       const int64_t *offsets, int64_t m, int64_t k,
                       int64_t num_edges, int64_t *edge_index,
                       b200c_stream_t stream);
+
+/* The tail of knn_graph on the device — replaces the flow swap, the `row != col` mask, the boolean
+ * gathers and the stack of torch_cluster/knn.py:135-144.  From the padded kNN result of x against
+ * itself (edge_padded, counts as written by b200c_knn):
+ *   b200c_knn_graph_tail_count   kept[q] = valid slots of q, minus those equal to q when drop_self
+ *   (b200c_exclusive_scan of kept -> offsets, offsets[m] = E)
+ *   b200c_knn_graph_tail_write   edge_index int64 [2, E]: per query, in stored order, the kept
+ *                                neighbours; row 0 = neighbour, row 1 = query when source_to_target,
+ *                                else row 0 = query, row 1 = neighbour. */
+int b200c_knn_graph_tail_count(const int64_t *edge_padded, const int32_t *counts, int64_t m, int64_t k,
+                               int drop_self, int32_t *kept, b200c_stream_t stream);
+int b200c_knn_graph_tail_write(const int64_t *edge_padded, const int32_t *counts, const int64_t *offsets,
+                               int64_t m, int64_t k, int drop_self, int source_to_target,
+                               int64_t num_edges, int64_t *edge_index, b200c_stream_t stream);
 
 /* Fixed-radius search — replaces radius_kernel and its -1 padded output
  * (csrc/cuda/radius_cuda.cu:9-42, 75-95) by count -> exclusive scan -> fill.

@@ -56,11 +56,13 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_knn_workspace_bytes.restype = sz
     lib.b200c_knn.argtypes = [p, p, p, p, i64, i64, i64, i64, i64, i32, i32, p, p, p, p, sz, p]
     lib.b200c_knn_compact.argtypes = [p, p, p, i64, i64, i64, p, p]
+    lib.b200c_knn_graph_tail_count.argtypes = [p, p, i64, i64, i32, p, p]
+    lib.b200c_knn_graph_tail_write.argtypes = [p, p, p, i64, i64, i32, i32, i64, p, p]
     lib.b200c_radius_workspace_bytes.argtypes = [i64, i64, i64]
     lib.b200c_radius_workspace_bytes.restype = sz
     lib.b200c_radius_count.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, sz, p]
     lib.b200c_radius_fill.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, i64, p, p, sz, p]
-    for name in ("b200c_segment_ptr", "b200c_exclusive_scan", "b200c_exclusive_scan_static", "b200c_knn", "b200c_knn_compact",
+    for name in ("b200c_segment_ptr", "b200c_exclusive_scan", "b200c_exclusive_scan_static", "b200c_knn", "b200c_knn_compact", "b200c_knn_graph_tail_count", "b200c_knn_graph_tail_write",
                  "b200c_radius_count", "b200c_radius_fill"):
         getattr(lib, name).restype = i32
     _cabi = lib

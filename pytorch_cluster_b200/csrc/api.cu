@@ -86,7 +86,10 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
   if (m == 0) return B200C_OK;
 
   B200C_CHECK_ARG(dim <= 0x7fffffffLL / 4, "Input mismatch");
-  const size_t need = b200c_knn_workspace_bytes(n, m, dim, k, dtype, cosine, num_segments);
+  // required: the norms of the exact cosine kernel; the larger size b200c_knn_workspace_bytes may
+  // report also enables the tensor-core candidate path and is optional
+  const size_t elem_bytes = dtype == B200C_F64 ? 8 : 4;
+  const size_t need = cosine ? align256((size_t)n * elem_bytes) + align256((size_t)m * elem_bytes) : 0;
   if (need > 0 && (workspace == nullptr || workspace_bytes < need)) {
     set_error("kNN workspace too small: %zu < %zu", workspace_bytes, need);
     return B200C_ERR_WORKSPACE;

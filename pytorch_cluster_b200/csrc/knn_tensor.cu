@@ -136,7 +136,12 @@ struct TensorArgs {
 
 template <bool COSINE>
 __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(TensorArgs a) {
-  extern __shared__ __align__(1024) unsigned char smem[];
+  // The 128-byte swizzle works on absolute shared-memory address bits, so the operand tiles must
+  // start on a 1024-byte boundary.  The declared alignment of an extern array is shared by every
+  // kernel of the translation unit that names it, so the base is aligned by hand instead (the
+  // launch reserves 1024 bytes of slack).
+  extern __shared__ unsigned char smem_tensor_raw[];
+  unsigned char *smem = smem_tensor_raw + ((1024u - (smem_u32(smem_tensor_raw) & 1023u)) & 1023u);
   const int dim = a.dim;
   const uint32_t tile_bytes = (uint32_t)((dim + 31) >> 5) * 16384u;  // whole atoms of 32 features
   unsigned char *sQ = smem;
@@ -330,7 +335,8 @@ knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, cons
                   int32_t *__restrict__ counts, unsigned long long *__restrict__ num_valid) {
   using K = Key<float>;
   constexpr int KP = 32;
-  extern __shared__ __align__(16) unsigned char smem[];
+  extern __shared__ __align__(16) unsigned char smem_rerank[];
+  unsigned char *smem = smem_rerank;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // per warp: query row (dim floats, padded to 4), 2 * KP keys, queue fill
   const int qstride = (dim + 3) & ~3;

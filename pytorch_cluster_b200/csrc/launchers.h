@@ -55,5 +55,4 @@ int launch_knn_tensor_f32(const KnnArgs &a, void *workspace);
 int launch_knn_rerank_f32(const KnnArgs &a, const int32_t *cand, const int32_t *cand_count, const int *error_flag,
                           const float *norms_x, const float *norms_y);
 
-
 }  // namespace b200c

@@ -160,6 +160,45 @@ __global__ void knn_compact_kernel(const int64_t *__restrict__ col_padded, const
   }
 }
 
+// ---- knn_graph tail: drop self matches and padding, orient by flow -----------------------------------------
+// kept[q] = number of valid slots of query q whose neighbour is not q itself (all valid ones when
+// self loops are wanted).  One thread per query.
+__global__ void knn_graph_tail_count_kernel(const int64_t *__restrict__ col_padded, const int32_t *__restrict__ counts,
+                                            int64_t m, int k1, int drop_self, int32_t *__restrict__ kept) {
+  const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= m) return;
+  const int c = counts[q];
+  int n = c;
+  if (drop_self)
+    for (int e = 0; e < c; ++e) n -= col_padded[q * k1 + e] == q;
+  kept[q] = n;
+}
+
+// One warp per query: its kept neighbours, in their stored order, to offsets[q]... of the output;
+// row 0 holds the neighbour and row 1 the query for "source_to_target", the other way round otherwise.
+__global__ void knn_graph_tail_write_kernel(const int64_t *__restrict__ col_padded, const int32_t *__restrict__ counts,
+                                            const int64_t *__restrict__ offsets, int64_t m, int k1, int drop_self,
+                                            int source_to_target, int64_t *__restrict__ out0,
+                                            int64_t *__restrict__ out1) {
+  const int lane = threadIdx.x & 31;
+  const int64_t q = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (q >= m) return;
+  const int c = counts[q];
+  int64_t o = offsets[q];
+  for (int base = 0; base < c; base += 32) {
+    const int e = base + lane;
+    const int64_t nb = e < c ? col_padded[q * k1 + e] : -1;
+    const bool keep = e < c && !(drop_self && nb == q);
+    const unsigned mask = __ballot_sync(FULL_MASK, keep);
+    if (keep) {
+      const int64_t pos = o + __popc(mask & ((1u << lane) - 1u));
+      out0[pos] = source_to_target ? nb : q;
+      out1[pos] = source_to_target ? q : nb;
+    }
+    o += __popc(mask);
+  }
+}
+
 }  // namespace b200c
 
 using namespace b200c;
@@ -203,6 +242,31 @@ extern "C" int b200c_exclusive_scan(const int32_t *counts, int64_t m, int64_t *o
   B200C_LAUNCH_CHECK("scan_tile_offsets_kernel");
   scan_apply_kernel<<<(unsigned)tiles, SCAN_THREADS, 0, stream>>>(counts, m, tile_sums, offsets);
   B200C_LAUNCH_CHECK("scan_apply_kernel");
+  return B200C_OK;
+}
+
+extern "C" int b200c_knn_graph_tail_count(const int64_t *edge_padded, const int32_t *counts, int64_t m, int64_t k,
+                                          int drop_self, int32_t *kept, b200c_stream_t stream) {
+  B200C_CHECK_ARG(m >= 0 && k >= 1 && k <= B200C_MAX_K, "Input mismatch");
+  if (m == 0) return B200C_OK;
+  B200C_CHECK_ARG(edge_padded && counts && kept, "null pointer");
+  knn_graph_tail_count_kernel<<<(unsigned)((m + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      edge_padded + m * k, counts, m, (int)k, drop_self, kept);
+  B200C_LAUNCH_CHECK("knn_graph_tail_count_kernel");
+  return B200C_OK;
+}
+
+extern "C" int b200c_knn_graph_tail_write(const int64_t *edge_padded, const int32_t *counts, const int64_t *offsets,
+                                          int64_t m, int64_t k, int drop_self, int source_to_target,
+                                          int64_t num_edges, int64_t *edge_index, b200c_stream_t stream) {
+  B200C_CHECK_ARG(m >= 0 && k >= 1 && k <= B200C_MAX_K && num_edges >= 0, "Input mismatch");
+  if (m == 0 || num_edges == 0) return B200C_OK;
+  B200C_CHECK_ARG(edge_padded && counts && offsets && edge_index, "null pointer");
+  const int64_t threads = m * 32;
+  knn_graph_tail_write_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      edge_padded + m * k, counts, offsets, m, (int)k, drop_self, source_to_target, edge_index,
+      edge_index + num_edges);
+  B200C_LAUNCH_CHECK("knn_graph_tail_write_kernel");
   return B200C_OK;
 }
 

@@ -115,6 +115,48 @@ torch::Tensor knn(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor>
   return out;
 }
 
+// knn_graph in one operator: kNN of x in x, then self-match removal, padding removal and flow
+// orientation on the device (torch_cluster/knn.py:131-144), with a single host sync for the size.
+torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr, int64_t k, bool loop,
+                              bool source_to_target, bool cosine) {
+  const int64_t k1 = loop ? k : k + 1;
+  Prepared p = prepare(x, x, ptr, ptr);
+  TORCH_CHECK(k1 <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
+  TORCH_CHECK(k >= 1, "`k` needs to be positive");
+
+  c10::cuda::CUDAGuard guard(x.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const auto lopts = x.options().dtype(torch::kLong);
+  const auto iopts = x.options().dtype(torch::kInt);
+  const int64_t n = p.x.size(0), dim = p.x.size(1);
+  if (n == 0) return torch::empty({2, 0}, lopts);
+
+  auto padded = torch::empty({2, n * k1}, lopts);
+  auto counts = torch::empty({n}, iopts);
+  auto num_valid = torch::empty({1}, lopts);
+  const size_t ws_bytes = b200c_knn_workspace_bytes(n, n, dim, k1, p.dtype, cosine, p.num_segments);
+  auto ws = torch::empty({(int64_t)ws_bytes}, x.options().dtype(torch::kByte));
+  check_status(b200c_knn(p.x.data_ptr(), p.x.data_ptr(), p.px, p.px, p.num_segments, n, n, dim, k1, p.dtype,
+                         cosine ? 1 : 0, padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(),
+                         num_valid.data_ptr<int64_t>(), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                         stream.stream()));
+  auto kept = torch::empty({n}, iopts);
+  check_status(b200c_knn_graph_tail_count(padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(), n, k1,
+                                          loop ? 0 : 1, kept.data_ptr<int32_t>(), stream.stream()));
+  auto offsets = torch::empty({n + 1}, lopts);
+  const size_t scan_bytes = b200c_scan_workspace_bytes(n);
+  auto scan_ws = torch::empty({(int64_t)scan_bytes}, x.options().dtype(torch::kByte));
+  check_status(b200c_exclusive_scan(kept.data_ptr<int32_t>(), n, offsets.data_ptr<int64_t>(), scan_ws.data_ptr(),
+                                    scan_bytes, stream.stream()));
+  const int64_t total = offsets[n].item<int64_t>();  // the one host sync: the output size
+  auto out = torch::empty({2, total}, lopts);
+  check_status(b200c_knn_graph_tail_write(padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(),
+                                          offsets.data_ptr<int64_t>(), n, k1, loop ? 0 : 1,
+                                          source_to_target ? 1 : 0, total, out.data_ptr<int64_t>(),
+                                          stream.stream()));
+  return out;
+}
+
 torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
                      std::optional<torch::Tensor> ptr_y, double r, int64_t max_num_neighbors,
                      int64_t num_workers, bool ignore_same_index) {
@@ -169,4 +211,5 @@ torch::Tensor segment_ptr(torch::Tensor batch, int64_t num_segments) {
 static auto registry = torch::RegisterOperators()
                            .op("torch_cluster::knn", &knn)
                            .op("torch_cluster::radius", &radius)
-                           .op("torch_cluster::segment_ptr", &segment_ptr);
+                           .op("torch_cluster::segment_ptr", &segment_ptr)
+                           .op("torch_cluster::knn_graph_edges", &knn_graph_edges);

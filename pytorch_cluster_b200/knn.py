@@ -35,6 +35,22 @@ def _segment_ptrs(x: torch.Tensor, y: torch.Tensor, batch_x: Optional[torch.Tens
     return ptr_x, ptr_y
 
 
+def _graph_ptr(x: torch.Tensor, batch: Optional[torch.Tensor],
+               batch_size: Optional[int]) -> Optional[torch.Tensor]:
+    """Segment boundaries when x is searched in itself: one pointer vector serves both sides."""
+    num_segments = 1
+    if batch_size is None:
+        num_segments = _num_segments(x.size(0), batch)
+    else:
+        num_segments = batch_size
+    assert num_segments > 0
+    ptr: Optional[torch.Tensor] = None
+    if num_segments > 1:
+        assert batch is not None
+        ptr = torch.ops.torch_cluster.segment_ptr(batch, num_segments)
+    return ptr
+
+
 def knn(
     x: torch.Tensor,
     y: torch.Tensor,
@@ -77,16 +93,16 @@ def knn_graph(
 ) -> torch.Tensor:
     r"""Edges from every node to its :obj:`k` nearest nodes.
 
-    As the reference does (torch_cluster/knn.py:131-144): search k (+1 without self loops)
-    neighbours of x in x, orient by :obj:`flow`, and drop the ``row == col`` entries when
-    :obj:`loop` is false.
+    Same result as the reference's composition (torch_cluster/knn.py:131-144): the k (+1 without
+    self loops) nearest rows of x for every row of x, oriented by :obj:`flow`, with the
+    ``row == col`` entries dropped when :obj:`loop` is false — computed by one operator.
     """
     assert flow in ['source_to_target', 'target_to_source']
-    found = knn(x, x, k if loop else k + 1, batch, batch, cosine, num_workers, batch_size)
-    query, neighbour = found[0], found[1]
-    if not loop:
-        keep = query != neighbour
-        query, neighbour = query[keep], neighbour[keep]
-    if flow == 'source_to_target':
-        return torch.stack([neighbour, query], dim=0)
-    return torch.stack([query, neighbour], dim=0)
+    if x.numel() == 0:
+        return torch.empty(2, 0, dtype=torch.long, device=x.device)
+    if x.dim() == 1:
+        x = x.view(-1, 1)
+    x = x.contiguous()
+    ptr = _graph_ptr(x, batch, batch_size)
+    # one operator: search, self-match and padding removal, flow orientation (one host sync)
+    return torch.ops.torch_cluster.knn_graph_edges(x, ptr, k, loop, flow == 'source_to_target', cosine)

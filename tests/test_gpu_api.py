@@ -221,3 +221,28 @@ def test_api_edge_cases():
     xt = torch.rand(3, 20, device=DEV).t()  # non-contiguous input is made contiguous by the wrapper
     got = pc.knn(xt, xt, 2).cpu().numpy()
     assert np.array_equal(got, orc.knn_api(xt.cpu().numpy(), xt.cpu().numpy(), 2))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_knn_graph_fused_tail_equals_reference_composition(dtype):
+    """knn_graph runs as one operator; it must equal knn + flow swap + `row != col` mask + stack
+    (torch_cluster/knn.py:131-144), also where exact duplicates push a point's own index out of its
+    k + 1 nearest (then nothing is dropped for it) and where segments are shorter than k."""
+    import pytorch_cluster_b200 as pc
+
+    g = torch.Generator().manual_seed(9)
+    base = torch.rand(300, 3, generator=g, dtype=dtype)
+    x = torch.cat([base, base[:40], base[:40], base[:40], torch.rand(7, 3, generator=g, dtype=dtype)])
+    batch = torch.cat([torch.zeros(420, dtype=torch.long), torch.full((7,), 2, dtype=torch.long)])
+    for k in (1, 2, 5, 12):
+        for loop in (False, True):
+            for flow in ("source_to_target", "target_to_source"):
+                got = pc.knn_graph(x.to(DEV), k, batch.to(DEV), loop=loop, flow=flow).cpu().numpy()
+                want = orc.knn_graph_api(x.numpy(), k, batch.numpy(), loop, flow)
+                assert np.array_equal(got, want), (k, loop, flow)
+                found = pc.knn(x.to(DEV), x.to(DEV), k if loop else k + 1, batch.to(DEV), batch.to(DEV))
+                row, col = (found[1], found[0]) if flow == "source_to_target" else (found[0], found[1])
+                if not loop:
+                    keep = row != col
+                    row, col = row[keep], col[keep]
+                assert np.array_equal(got, torch.stack([row, col]).cpu().numpy())
