@@ -1,6 +1,7 @@
 """Benchmark of the neighbour-graph path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extra]
+    python bench.py --only NAME [--steps K]     (one workload through the C ABI, for profilers)
 
 Headline workload (``knn_graph_batched``): 32 clouds x 4096 points, 3-D fp32 ~ N(0,1), sorted
 batch vector, k = 20, loop = False — synthetic, seeded.  One step = one ``knn_graph`` call over
@@ -273,6 +274,44 @@ def run_reference(args, rank, world):
     print(json.dumps(line))
 
 
+# ---- single workloads for profilers --------------------------------------------------------------------------
+
+def run_only(args):
+    """`--only NAME`: K launches of one workload's kernels through the C ABI, nothing else (small
+    enough for an ncu capture).  Prints nothing but a completion line."""
+    import pytorch_cluster_b200  # noqa: F401  (registers the operators)
+    from pytorch_cluster_b200 import cabi
+
+    dev = torch.device("cuda", 0)
+    seg = torch.ops.torch_cluster.segment_ptr
+    name, steps = args.only, max(1, args.steps)
+    if name == "knn_graph_batched":            # the headline kernel: 32 x 4096 x 3, k = 20 (+1)
+        w = make_knn_graph_batched()
+        x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 32)
+        fn = lambda: cabi.knn_padded_nosync(x, x, 21, ptr, ptr)
+    elif name == "knn_bipartite_small":        # 2 of the 8 clouds of the large bipartite search
+        w = make_knn_bipartite(clouds=2)
+        x, y = w["x"].to(dev), w["y"].to(dev)
+        px, py = seg(w["batch_x"].to(dev), 2), seg(w["batch_y"].to(dev), 2)
+        fn = lambda: cabi.knn_padded_nosync(x, y, 32, px, py)
+    elif name == "knn_features":               # 16 x 2048 x 64, k = 20 (+1): tensor-core candidates + re-rank
+        g = torch.Generator().manual_seed(4)
+        x = torch.randn(32768, 64, generator=g).to(dev)
+        ptr = torch.arange(0, 32768 + 1, 2048, device=dev)
+        fn = lambda: cabi.knn_padded_nosync(x, x, 21, ptr, ptr, args.cosine)
+    elif name in ("radius_mixture_small", "radius_mixture_small_two_scans"):  # 16 of the 64 clouds
+        w = make_radius_mixture(clouds=16)
+        x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 16)
+        max_nn = 8192 if name.endswith("two_scans") else 64
+        fn = lambda: cabi.radius(x, x, w["r"], ptr, ptr, max_nn, True)
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    for _ in range(steps):
+        fn()
+    torch.cuda.synchronize()
+    print(f"done: {name} x {steps}")
+
+
 # ---- our arm ------------------------------------------------------------------------------------------------
 
 def run_ours(args, rank, world, local_rank):
@@ -341,7 +380,8 @@ def run_ours(args, rank, world, local_rank):
                                "loop=False", "l2": "256 MiB buffer rewritten between timed steps"},
         "e2e": {"value": total_queries * args.steps / (ms_e2e * 1e-3), "unit": "queries/s",
                 "h2d_bytes_per_step": hx.numel() * 4 + hb.numel() * 8, "d2h_bytes_per_step": 2 * edges * 8},
-        "gpu_launches": 3 * args.steps,
+        # per knn_graph call: segment_ptr, the kNN kernel, tail count, three scan kernels, tail write
+        "gpu_launches": 7 * args.steps,
         "clocks": clocks.summary(),
         "roofline": {"bound": "fp32", "kernel": "knn_lowd_kernel<float,3,32>", "achieved": achieved,
                      "peak": fp32_peak, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
@@ -376,10 +416,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--only", default=None, help="run one named workload through the C ABI (for profilers)")
+    ap.add_argument("--cosine", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.only:
+        run_only(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
