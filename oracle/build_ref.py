@@ -22,6 +22,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "ref_cluster_cpu.so")
+OUT_CUDA = os.path.join(OUT_DIR, "ref_cluster_cuda.so")
 
 
 def torch_flags():
@@ -73,6 +74,57 @@ def build(reference: str, force: bool = False, verbose: bool = True) -> str | No
     return OUT
 
 
+def build_cuda(reference: str, force: bool = False, verbose: bool = True) -> str | None:
+    """Compile the reference's unmodified CUDA kernels of this path
+    (``csrc/cuda/knn_cuda.cu``, ``csrc/cuda/radius_cuda.cu``) for sm_100a with nvcc, plus
+    ``oracle/ref_shim_cuda.cpp``, into ``oracle/_ref/ref_cluster_cuda.so``.  Returns the path,
+    or None when neither the reference checkout nor a previously built file exists."""
+    import shutil
+
+    csrc = os.path.join(reference, "csrc")
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.isdir(csrc) or not os.path.exists(nvcc):
+        return OUT_CUDA if os.path.exists(OUT_CUDA) else None
+    cu = [os.path.join(csrc, "cuda", "knn_cuda.cu"), os.path.join(csrc, "cuda", "radius_cuda.cu")]
+    shim = os.path.join(HERE, "ref_shim_cuda.cpp")
+    if not force and os.path.exists(OUT_CUDA) and all(
+        os.path.getmtime(OUT_CUDA) >= os.path.getmtime(s) for s in cu + [shim]
+    ):
+        return OUT_CUDA
+    os.makedirs(OUT_DIR, exist_ok=True)
+    cflags, ldflags = torch_flags()
+    cuda_home = os.path.dirname(os.path.dirname(nvcc))
+    cflags = cflags + [f"-I{cuda_home}/include"]
+    procs, objs = [], []
+    for s in cu:
+        o = os.path.join(OUT_DIR, os.path.basename(s) + ".o")
+        objs.append(o)
+        cmd = [nvcc, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a",
+               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-c", s, "-o", o, f"-I{csrc}"] + cflags + [
+                   # what torch.utils.cpp_extension adds to every nvcc command of a CUDAExtension
+                   "-D__CUDA_NO_HALF_OPERATORS__", "-D__CUDA_NO_HALF_CONVERSIONS__",
+                   "-D__CUDA_NO_BFLOAT16_CONVERSIONS__", "-D__CUDA_NO_HALF2_OPERATORS__"]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        procs.append(subprocess.Popen(cmd))
+    o = os.path.join(OUT_DIR, "ref_shim_cuda.cpp.o")
+    objs.append(o)
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-Wno-sign-compare", "-c", shim, "-o", o, f"-I{csrc}"] + cflags
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    procs.append(subprocess.Popen(cmd))
+    for p in procs:
+        if p.wait() != 0:
+            raise RuntimeError("compiling the reference CUDA path failed")
+    lib_dir = [f for f in ldflags if f.startswith("-L")][0][2:]
+    cmd = ["g++", "-shared", "-o", OUT_CUDA] + objs + ldflags + [
+        "-ltorch_cuda", "-lc10_cuda", f"-L{cuda_home}/lib64", "-lcudart"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.check_call(cmd)
+    return OUT_CUDA
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("REFERENCE_DIR", "/root/reference"))
@@ -80,4 +132,5 @@ if __name__ == "__main__":
     a = ap.parse_args()
     out = build(a.reference, a.force)
     print(out or "reference checkout not found; nothing built")
+    print(build_cuda(a.reference, a.force) or "reference CUDA path not built")
     sys.exit(0 if out else 1)

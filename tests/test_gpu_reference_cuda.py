@@ -1,0 +1,200 @@
+"""GPU parity against the reference's own CUDA kernels, compiled unmodified for sm_100a
+(``oracle/_ref/ref_cluster_cuda.so``): the product's operators must return the very same
+``edge_index`` tensors — values and order — as ``knn_cuda`` (csrc/cuda/knn_cuda.cu:86-135) and
+``radius_cuda`` (csrc/cuda/radius_cuda.cu:44-96) on the same device tensors.  Also records how long
+the reference's kernels take on this GPU beside the product's (printed, and written as JSON when
+``B200C_REPORT_DIR`` names a directory)."""
+import json
+import os
+
+import pytest
+import torch
+
+from oracle import reference_cuda as refc
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not refc.available(), reason="oracle/_ref/ref_cluster_cuda.so not built")]
+
+DEV = "cuda:0"
+
+
+def _ptr(clouds, per):
+    return torch.arange(clouds + 1, device=DEV, dtype=torch.long) * per
+
+
+def _ours_knn(x, y, px, py, k, cosine=False):
+    import pytorch_cluster_b200  # noqa: F401
+
+    return torch.ops.torch_cluster.knn(x, y, px, py, k, cosine, 1)
+
+
+def _ours_radius(x, y, px, py, r, max_nn, ignore_same):
+    import pytorch_cluster_b200  # noqa: F401
+
+    return torch.ops.torch_cluster.radius(x, y, px, py, r, max_nn, 1, ignore_same)
+
+
+def _same(a, b):
+    assert a.shape == b.shape, (a.shape, b.shape)
+    if not torch.equal(a, b):
+        bad = (a != b).any(0).nonzero().flatten()
+        raise AssertionError(f"{bad.numel()} differing edges, first at {int(bad[0])}: "
+                             f"{a[:, bad[0]].tolist()} vs {b[:, bad[0]].tolist()}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float, torch.double])
+@pytest.mark.parametrize("dim", [1, 2, 3, 5, 8, 11, 16])
+def test_knn_small_dims(dtype, dim):
+    g = torch.Generator().manual_seed(100 + dim)
+    x = torch.randn(3000, dim, generator=g).to(DEV, dtype)
+    y = torch.randn(700, dim, generator=g).to(DEV, dtype)
+    px = torch.tensor([0, 1000, 1000, 2500, 3000], device=DEV)
+    py = torch.tensor([0, 300, 350, 600, 700], device=DEV)
+    for k in (1, 7, 33, 100):
+        _same(_ours_knn(x, y, px, py, k), refc.knn(x, y, px, py, k))
+    _same(_ours_knn(x, y, None, None, 16), refc.knn(x, y, None, None, 16))
+
+
+def test_knn_ties_and_duplicates():
+    g = torch.Generator().manual_seed(7)
+    x = torch.randint(0, 4, (4096, 3), generator=g).float().to(DEV)  # heavy ties on a 4^3 lattice
+    px = _ptr(4, 1024)
+    for k in (5, 21, 64):
+        _same(_ours_knn(x, x, px, px, k), refc.knn(x, x, px, px, k))
+
+
+def test_knn_graph_batched_full_size():
+    """32 clouds x 4096 points, 3-D, op k = 21, fp32 and fp64."""
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(32 * 4096, 3, generator=g).to(DEV)
+    p = _ptr(32, 4096)
+    _same(_ours_knn(x, x, p, p, 21), refc.knn(x, x, p, p, 21))
+    xd = x.double()
+    _same(_ours_knn(xd, xd, p, p, 21), refc.knn(xd, xd, p, p, 21))
+
+
+def test_knn_bipartite_two_clouds():
+    """A quarter of the large bipartite configuration: 2 x (131072 points, 8192 queries), k = 32."""
+    g = torch.Generator().manual_seed(3)
+    x = (100 * torch.rand(2 * 131072, 3, generator=g)).to(DEV)
+    y = (100 * torch.rand(2 * 8192, 3, generator=g)).to(DEV)
+    px, py = _ptr(2, 131072), _ptr(2, 8192)
+    _same(_ours_knn(x, y, px, py, 32), refc.knn(x, y, px, py, 32))
+
+
+@pytest.mark.parametrize("cosine", [False, True])
+@pytest.mark.parametrize("dim", [32, 64, 128])
+def test_knn_feature_space_tensor_path(cosine, dim):
+    """16 clouds x 2048 points: the tensor-core candidate path against the reference's exact kernel."""
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(16 * 2048, dim, generator=g).to(DEV)
+    p = _ptr(16, 2048)
+    _same(_ours_knn(x, x, p, p, 21, cosine), refc.knn(x, x, p, p, 21, cosine))
+
+
+@pytest.mark.parametrize("cosine", [False, True])
+def test_knn_general_dim(cosine):
+    g = torch.Generator().manual_seed(14)
+    x = torch.randn(5000, 19, generator=g).to(DEV)
+    y = torch.randn(900, 19, generator=g).to(DEV)
+    px = torch.tensor([0, 2000, 5000], device=DEV)
+    py = torch.tensor([0, 500, 900], device=DEV)
+    for k in (3, 40):
+        _same(_ours_knn(x, y, px, py, k, cosine), refc.knn(x, y, px, py, k, cosine))
+
+
+def _mixture(clouds, points, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    centres = torch.rand(clouds, 32, 3, generator=g)
+    pick = torch.randint(0, 32, (clouds, points), generator=g)
+    x = torch.gather(centres, 1, pick.unsqueeze(-1).expand(-1, -1, 3)) + 0.02 * torch.randn(clouds, points, 3, generator=g)
+    bg = torch.rand(clouds, points, generator=g) < 0.2
+    x[bg] = torch.rand(int(bg.sum()), 3, generator=g)
+    return x.clamp_(0, 0.99999994).reshape(clouds * points, 3).contiguous().to(DEV)
+
+
+@pytest.mark.parametrize("max_nn", [1, 32, 64, 300])
+@pytest.mark.parametrize("ignore_same", [False, True])
+def test_radius_mixture(max_nn, ignore_same):
+    x = _mixture(8, 8192)
+    p = _ptr(8, 8192)
+    _same(_ours_radius(x, x, p, p, 0.05, max_nn, ignore_same), refc.radius(x, x, p, p, 0.05, max_nn, ignore_same))
+    xd = x.double()
+    _same(_ours_radius(xd, xd, p, p, 0.05, max_nn, ignore_same),
+          refc.radius(xd, xd, p, p, 0.05, max_nn, ignore_same))
+
+
+def test_radius_untruncated_and_bipartite():
+    x = _mixture(4, 8192)
+    p = _ptr(4, 8192)
+    _same(_ours_radius(x, x, p, p, 0.05, 8192, True), refc.radius(x, x, p, p, 0.05, 8192, True))
+    keep = torch.cat([torch.randperm(8192, generator=torch.Generator().manual_seed(9))[:2048].sort().values + 8192 * c
+                      for c in range(4)]).to(DEV)
+    y = x[keep].contiguous()
+    py = _ptr(4, 2048)
+    _same(_ours_radius(x, y, p, py, 0.05, 64, False), refc.radius(x, y, p, py, 0.05, 64, False))
+
+
+@pytest.mark.parametrize("dim", [1, 2, 6, 8, 12])
+def test_radius_dims(dim):
+    g = torch.Generator().manual_seed(200 + dim)
+    x = torch.rand(6000, dim, generator=g).to(DEV)
+    y = torch.rand(1500, dim, generator=g).to(DEV)
+    px = torch.tensor([0, 2500, 2500, 6000], device=DEV)
+    py = torch.tensor([0, 700, 800, 1500], device=DEV)
+    r = 0.03 if dim == 1 else 0.25
+    for max_nn in (16, 5000):
+        _same(_ours_radius(x, y, px, py, r, max_nn, False), refc.radius(x, y, px, py, r, max_nn, False))
+
+
+def _ms(fn, reps=3):
+    fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def test_time_beside_reference_kernels():
+    """Operator-level time (CUDA events, whole op call incl. its compaction) of the reference's CUDA
+    path and of this library on the same tensors.  A report, not a threshold — except that the
+    product must not be slower."""
+    rep = {}
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(32 * 4096, 3, generator=g).to(DEV)
+    p = _ptr(32, 4096)
+    rep["knn_32x4096x3_k21"] = (_ms(lambda: refc.knn(x, x, p, p, 21)), _ms(lambda: _ours_knn(x, x, p, p, 21)))
+    g = torch.Generator().manual_seed(3)
+    xb = (100 * torch.rand(8 * 131072, 3, generator=g)).to(DEV)
+    yb = (100 * torch.rand(8 * 8192, 3, generator=g)).to(DEV)
+    pxb, pyb = _ptr(8, 131072), _ptr(8, 8192)
+    rep["knn_8x131072x8192x3_k32"] = (_ms(lambda: refc.knn(xb, yb, pxb, pyb, 32), 1),
+                                      _ms(lambda: _ours_knn(xb, yb, pxb, pyb, 32)))
+    g = torch.Generator().manual_seed(4)
+    xf = torch.randn(16 * 2048, 64, generator=g).to(DEV)
+    pf = _ptr(16, 2048)
+    for cosine in (False, True):
+        rep[f"knn_16x2048x64_k21_cosine{int(cosine)}"] = (_ms(lambda: refc.knn(xf, xf, pf, pf, 21, cosine)),
+                                                         _ms(lambda: _ours_knn(xf, xf, pf, pf, 21, cosine)))
+    xr = _mixture(64, 8192)
+    pr = _ptr(64, 8192)
+    rep["radius_64x8192x3_r0.05_max64"] = (_ms(lambda: refc.radius(xr, xr, pr, pr, 0.05, 64, True)),
+                                           _ms(lambda: _ours_radius(xr, xr, pr, pr, 0.05, 64, True)))
+    # max_num_neighbors = 8192 on all 64 clouds would make the reference allocate 2 x 34 GB of padded
+    # output plus masks; it is timed on 8 clouds instead
+    xs, ps = xr[: 8 * 8192].contiguous(), _ptr(8, 8192)
+    rep["radius_8x8192x3_r0.05_max8192"] = (_ms(lambda: refc.radius(xs, xs, ps, ps, 0.05, 8192, True)),
+                                            _ms(lambda: _ours_radius(xs, xs, ps, ps, 0.05, 8192, True)))
+    out = {k: {"reference_cuda_ms": round(a, 4), "this_library_ms": round(b, 4), "ratio": round(a / b, 2)}
+           for k, (a, b) in rep.items()}
+    print(json.dumps(out, indent=1))
+    d = os.environ.get("B200C_REPORT_DIR")
+    if d and os.path.isdir(d):
+        with open(os.path.join(d, "reference_cuda_timings.json"), "w") as f:
+            json.dump(out, f, indent=1)
+    for k, v in out.items():
+        assert v["ratio"] >= 1.0, (k, v)
