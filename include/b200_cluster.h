@@ -37,7 +37,11 @@ enum {
   B200C_ERR_DEVICE = 5       /* the GPU is not an sm_100 device                    */
 };
 
-enum { B200C_F32 = 0, B200C_F64 = 1 };
+/* Data types of x and y.  The 16-bit types follow the reference's instantiations for c10::Half
+ * (knn, radius) and c10::BFloat16 (radius; csrc/cuda/knn_cuda.cu:125, csrc/cuda/radius_cuda.cu:84-85):
+ * every operation result is rounded to the 16-bit type, so results equal the reference's for
+ * such inputs and differ from a search on the widened values.  They need a workspace (below). */
+enum { B200C_F32 = 0, B200C_F64 = 1, B200C_F16 = 2, B200C_BF16 = 3 };
 
 /* Largest k accepted, as in the reference (csrc/cuda/knn_cuda.cu:98). */
 #define B200C_MAX_K 100
@@ -103,9 +107,10 @@ int b200c_exclusive_scan_static(const int32_t *counts, int64_t m, int64_t *offse
  * form already is the final edge_index; otherwise run b200c_exclusive_scan on
  * counts and b200c_knn_compact.
  *
- * workspace: b200c_knn_workspace_bytes(...) bytes (may be 0).  Only the cosine distance needs
- * one (the rows' norms); the full size additionally enables the tensor-core candidate path for
- * fp32 features (32 <= dim <= 128, dim % 8 == 0, k <= 32), without it the exact kernels run. */
+ * workspace: b200c_knn_workspace_bytes(...) bytes (may be 0).  The cosine distance needs one (the
+ * rows' norms) and so do the 16-bit types (float copies of x and y); for these the full reported
+ * size is required.  For fp32 features (32 <= dim <= 128, dim % 8 == 0, k <= 32) the full size
+ * additionally enables the tensor-core candidate path; without it the exact kernels run. */
 size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t k,
                                  int dtype, int cosine, int64_t num_segments);
 int b200c_knn(const void *x, const void *y, const int64_t *ptr_x,
@@ -148,13 +153,15 @@ int b200c_knn_graph_tail_write(const int64_t *edge_padded, const int32_t *counts
  * row 0 = q, row 1 = x index) — the truncation rule of
  * csrc/cuda/radius_cuda.cu:33-40.  offsets is the exclusive scan of counts.
  *
- * Workspace (optional): b200c_radius_workspace_bytes(m, dim, max_num_neighbors)
- * is non-zero when a one-pass mode applies (small neighbour caps): pass 1 then
- * also parks the hits in the workspace (m * max_num_neighbors int32) and pass 2
- * only copies them, instead of scanning the points a second time.  Give both
- * passes the same workspace, untouched in between; with NULL / too few bytes
- * both passes scan. */
-size_t b200c_radius_workspace_bytes(int64_t m, int64_t dim, int64_t max_num_neighbors);
+ * Workspace: b200c_radius_workspace_bytes(n, m, dim, max_num_neighbors, dtype).
+ * For fp32 / fp64 it is optional and non-zero when a one-pass mode applies (small
+ * neighbour caps): pass 1 then also parks the hits in the workspace
+ * (m * max_num_neighbors int32) and pass 2 only copies them, instead of scanning
+ * the points a second time; with NULL / too few bytes both passes scan.  For the
+ * 16-bit types it is required (pass 1 leaves float copies of x and y there for
+ * pass 2).  Give both passes the same workspace, untouched in between. */
+size_t b200c_radius_workspace_bytes(int64_t n, int64_t m, int64_t dim,
+                                    int64_t max_num_neighbors, int dtype);
 int b200c_radius_count(const void *x, const void *y, const int64_t *ptr_x,
                        const int64_t *ptr_y, int64_t num_segments, int64_t n,
                        int64_t m, int64_t dim, double r,

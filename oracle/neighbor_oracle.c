@@ -26,6 +26,19 @@
  * tail.  The file must be compiled with -ffp-contract=off so that only the
  * explicit fma()/fmaf() calls fuse.
  *
+ * 16-bit inputs (`*_r16`).  The reference instantiates the same kernels for
+ * c10::Half (knn_cuda.cu:125, radius_cuda.cu:84-85) and c10::BFloat16 (radius
+ * only).  Those types are not part of the reference checkout: they come from its
+ * dependency PyTorch (here 2.11.0; torch/headeronly/util/Half.h and BFloat16.h),
+ * whose published definition is: every arithmetic operator converts both
+ * operands to float, operates in float and narrows the result to the 16-bit type
+ * with round-to-nearest-even; comparisons convert to float; double op Half
+ * yields double.  The `*_r16` functions restate the kernels under that
+ * definition on float arrays holding 16-bit-representable values.  They are
+ * pinned on the GPU against the reference's own CUDA kernels compiled for
+ * sm_100a (tests/test_gpu_reference_cuda.py) and, on the CPU, by the reference's
+ * half-precision known-answer tests.
+ *
  * Parity pin: checked in tests/test_oracle.py against the reference's own
  * known-answer tests (test/test_knn.py, test/test_radius.py, README examples)
  * and against outputs of the reference's compiled CPU path (oracle/_ref, and
@@ -180,3 +193,115 @@ static int64_t segment_of(int64_t idx, const int64_t *ptr, int64_t num_segments)
 
 DEFINE_ORACLE(float, f32, fmaf, sqrtf)
 DEFINE_ORACLE(double, f64, fma, sqrt)
+
+
+/* ---- 16-bit inputs: float arithmetic, every result narrowed to fp16 (kind 1) or bf16 (kind 2) ---- */
+
+static inline float round_f16(float v) { return (float)(_Float16)v; }
+
+static inline float round_bf16(float v) {
+  uint32_t u;
+  memcpy(&u, &v, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) {
+    u = 0x7fc00000u; /* NaN stays NaN */
+  } else {
+    u += 0x7fffu + ((u >> 16) & 1u); /* round to nearest, ties to even */
+    u &= 0xffff0000u;
+  }
+  memcpy(&v, &u, 4);
+  return v;
+}
+
+static inline float r16(float v, int kind) { return kind == 1 ? round_f16(v) : round_bf16(v); }
+
+/* `acc += (a - b) * (a - b)` with Half / BFloat16 operands (knn_cuda.cu:61-64) */
+static inline float sqdist_r16(const float *a, const float *b, int64_t dim, int kind) {
+  float acc = 0;
+  for (int64_t d = 0; d < dim; d++) {
+    float diff = r16(a[d] - b[d], kind);
+    float prod = r16(diff * diff, kind);
+    acc = r16(acc + prod, kind);
+  }
+  return acc;
+}
+
+/* knn_cuda.cu:9-28, 55-59 with Half operands; `1. - q` is formed in double and narrowed
+ * through float (the 16-bit types construct from float) */
+static inline float cosdist_r16(const float *xr, const float *yr, int64_t dim, int kind) {
+  float dot = 0, nx = 0, ny = 0;
+  for (int64_t d = 0; d < dim; d++)
+    dot = r16(dot + r16(xr[d] * yr[d], kind), kind);
+  for (int64_t d = 0; d < dim; d++)
+    nx = r16(nx + r16(xr[d] * xr[d], kind), kind);
+  for (int64_t d = 0; d < dim; d++)
+    ny = r16(ny + r16(yr[d] * yr[d], kind), kind);
+  nx = r16(sqrtf(nx), kind);
+  ny = r16(sqrtf(ny), kind);
+  float den = r16(nx * ny, kind);
+  float q = r16(dot / den, kind);
+  return r16((float)(1. - (double)q), kind);
+}
+
+int64_t oracle_knn_r16(const float *x, const float *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                       int64_t num_segments, int64_t n, int64_t m, int64_t dim, int64_t k, int cosine,
+                       int kind, int64_t *out_col, float *out_dist) {
+  (void)n;
+  int64_t valid = 0;
+  const float init = r16(1e10f, kind); /* `best_dist[e] = 1e10` narrows: +inf for fp16 */
+#pragma omp parallel for schedule(dynamic, 64) reduction(+ : valid)
+  for (int64_t n_y = 0; n_y < m; n_y++) {
+    const int64_t b = segment_of(n_y, ptr_y, num_segments);
+    float *best_dist = out_dist + n_y * k;
+    int64_t *best_idx = out_col + n_y * k;
+    for (int64_t e = 0; e < k; e++) {
+      best_dist[e] = init;
+      best_idx[e] = -1;
+    }
+    for (int64_t n_x = ptr_x[b]; n_x < ptr_x[b + 1]; n_x++) {
+      float tmp = cosine ? cosdist_r16(x + n_x * dim, y + n_y * dim, dim, kind)
+                         : sqdist_r16(x + n_x * dim, y + n_y * dim, dim, kind);
+      if (!(best_dist[k - 1] > tmp))
+        continue;
+      int64_t e1 = 0;
+      while (!(best_dist[e1] > tmp))
+        e1++;
+      for (int64_t e2 = k - 1; e2 > e1; e2--) {
+        best_dist[e2] = best_dist[e2 - 1];
+        best_idx[e2] = best_idx[e2 - 1];
+      }
+      best_dist[e1] = tmp;
+      best_idx[e1] = n_x;
+    }
+    for (int64_t e = 0; e < k; e++)
+      valid += best_idx[e] >= 0;
+  }
+  return valid;
+}
+
+int64_t oracle_radius_r16(const float *x, const float *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                          int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
+                          int64_t max_num_neighbors, int ignore_same_index, int kind, int64_t *counts,
+                          const int64_t *offsets, int64_t *out_col) {
+  (void)n;
+  const float r2 = r16((float)(r * r), kind); /* radius_cuda.cu:90: double -> float -> 16-bit */
+  int64_t total = 0;
+#pragma omp parallel for schedule(dynamic, 64) reduction(+ : total)
+  for (int64_t n_y = 0; n_y < m; n_y++) {
+    const int64_t b = segment_of(n_y, ptr_y, num_segments);
+    int64_t count = 0;
+    for (int64_t n_x = ptr_x[b]; n_x < ptr_x[b + 1]; n_x++) {
+      if (count >= max_num_neighbors)
+        break;
+      float dist = sqdist_r16(x + n_x * dim, y + n_y * dim, dim, kind);
+      if (dist < r2 && !(ignore_same_index && n_y == n_x)) {
+        if (out_col)
+          out_col[offsets[n_y] + count] = n_x;
+        count++;
+      }
+    }
+    if (counts)
+      counts[n_y] = count;
+    total += count;
+  }
+  return total;
+}

@@ -33,6 +33,10 @@ def lib() -> ctypes.CDLL:
             f = getattr(_lib, f"oracle_radius_{sfx}")
             f.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, p]
             f.restype = i64
+        _lib.oracle_knn_r16.argtypes = [p, p, p, p, i64, i64, i64, i64, i64, i32, i32, p, p]
+        _lib.oracle_knn_r16.restype = i64
+        _lib.oracle_radius_r16.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, p]
+        _lib.oracle_radius_r16.restype = i64
     return _lib
 
 
@@ -64,33 +68,45 @@ def _prep(x, y, ptr_x, ptr_y):
     return x, y, ptr_x, ptr_y, sfx
 
 
-def knn_padded(x, y, k, ptr_x=None, ptr_y=None, cosine=False, fused=True):
+_KIND16 = {"f16": 1, "bf16": 2}
+
+
+def _fn(name, sfx, x, fused, round16):
+    """-> (C function, value of its policy argument).  ``round16`` ("f16" / "bf16") selects the
+    restatement for 16-bit inputs; x, y are then float32 arrays of 16-bit-representable values."""
+    if round16 is None:
+        return getattr(lib(), f"oracle_{name}_{sfx}"), int(fused)
+    assert x.dtype == np.float32
+    return getattr(lib(), f"oracle_{name}_r16"), _KIND16[round16]
+
+
+def knn_padded(x, y, k, ptr_x=None, ptr_y=None, cosine=False, fused=True, round16=None):
     """Per-query best lists: ``(col [M,k] int64 with -1 padding, dist [M,k])``."""
     x, y, ptr_x, ptr_y, sfx = _prep(x, y, ptr_x, ptr_y)
     m = y.shape[0]
     col = np.empty((m, k), dtype=np.int64)
     dist = np.empty((m, k), dtype=x.dtype)
-    getattr(lib(), f"oracle_knn_{sfx}")(
-        _ptr(x), _ptr(y), _ptr(ptr_x), _ptr(ptr_y), ptr_x.size - 1, x.shape[0], m,
-        x.shape[1], k, int(cosine), int(fused), _ptr(col), _ptr(dist))
+    f, policy = _fn("knn", sfx, x, fused, round16)
+    f(_ptr(x), _ptr(y), _ptr(ptr_x), _ptr(ptr_y), ptr_x.size - 1, x.shape[0], m,
+      x.shape[1], k, int(cosine), policy, _ptr(col), _ptr(dist))
     return col, dist
 
 
-def knn(x, y, k, ptr_x=None, ptr_y=None, cosine=False, fused=True) -> np.ndarray:
-    col, _ = knn_padded(x, y, k, ptr_x, ptr_y, cosine, fused)
+def knn(x, y, k, ptr_x=None, ptr_y=None, cosine=False, fused=True, round16=None) -> np.ndarray:
+    col, _ = knn_padded(x, y, k, ptr_x, ptr_y, cosine, fused, round16)
     row = np.repeat(np.arange(col.shape[0], dtype=np.int64), k).reshape(col.shape)
     mask = col != -1
     return np.stack([row[mask], col[mask]])
 
 
 def radius(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32,
-           ignore_same_index=False, fused=True) -> np.ndarray:
+           ignore_same_index=False, fused=True, round16=None) -> np.ndarray:
     x, y, ptr_x, ptr_y, sfx = _prep(x, y, ptr_x, ptr_y)
     m = y.shape[0]
-    f = getattr(lib(), f"oracle_radius_{sfx}")
+    f, policy = _fn("radius", sfx, x, fused, round16)
     counts = np.empty(m, dtype=np.int64)
     args = (_ptr(x), _ptr(y), _ptr(ptr_x), _ptr(ptr_y), ptr_x.size - 1, x.shape[0], m,
-            x.shape[1], float(r), int(max_num_neighbors), int(ignore_same_index), int(fused))
+            x.shape[1], float(r), int(max_num_neighbors), int(ignore_same_index), policy)
     total = f(*args, _ptr(counts), None, None)
     offsets = np.zeros(m + 1, dtype=np.int64)
     np.cumsum(counts, out=offsets[1:])

@@ -16,7 +16,7 @@ LIB_CABI = os.path.join(_PKG, "libb200cluster.so")
 LIB_OPS = os.path.join(_PKG, "_torch_ops.so")
 
 B200C_OK = 0
-B200C_F32, B200C_F64 = 0, 1
+B200C_F32, B200C_F64, B200C_F16, B200C_BF16 = 0, 1, 2, 3
 
 _cabi = None
 
@@ -58,7 +58,7 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_knn_compact.argtypes = [p, p, p, i64, i64, i64, p, p]
     lib.b200c_knn_graph_tail_count.argtypes = [p, p, i64, i64, i32, p, p]
     lib.b200c_knn_graph_tail_write.argtypes = [p, p, p, i64, i64, i32, i32, i64, p, p]
-    lib.b200c_radius_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.b200c_radius_workspace_bytes.argtypes = [i64, i64, i64, i64, i32]
     lib.b200c_radius_workspace_bytes.restype = sz
     lib.b200c_radius_count.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, sz, p]
     lib.b200c_radius_fill.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, i64, p, p, sz, p]

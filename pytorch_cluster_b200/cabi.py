@@ -17,7 +17,8 @@ def _stream():
 
 
 def _dtype(x):
-    return {torch.float32: _native.B200C_F32, torch.float64: _native.B200C_F64}[x.dtype]
+    return {torch.float32: _native.B200C_F32, torch.float64: _native.B200C_F64,
+            torch.float16: _native.B200C_F16, torch.bfloat16: _native.B200C_BF16}[x.dtype]
 
 
 def segment_ptr(batch, num_segments):
@@ -46,7 +47,7 @@ def knn_padded_nosync(x, y, k, ptr_x=None, ptr_y=None, cosine=False, workspace=T
     padded = torch.empty(2, m * k, dtype=torch.long, device=x.device)
     counts = torch.empty(m, dtype=torch.int32, device=x.device)
     nvalid = torch.empty(1, dtype=torch.long, device=x.device)
-    nbytes = lib.b200c_knn_workspace_bytes(n, m, dim, k, _dtype(x), int(cosine), nseg) if (workspace or cosine) else 0
+    nbytes = lib.b200c_knn_workspace_bytes(n, m, dim, k, _dtype(x), int(cosine), nseg) if (workspace or cosine or x.element_size() == 2) else 0
     ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
     _native.check(lib.b200c_knn(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, k, _dtype(x),
                                 int(cosine), _p(padded), _p(counts), _p(nvalid), _p(ws), nbytes, _stream()))
@@ -74,7 +75,8 @@ def knn(x, y, k, ptr_x=None, ptr_y=None, cosine=False):
 
 def _radius_workspace(x, m, dim, max_num_neighbors, one_pass):
     lib = _native.cabi()
-    nbytes = lib.b200c_radius_workspace_bytes(m, dim, max_num_neighbors) if one_pass else 0
+    nbytes = (lib.b200c_radius_workspace_bytes(x.shape[0], m, dim, max_num_neighbors, _dtype(x))
+              if (one_pass or x.element_size() == 2) else 0)
     ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
     return ws, nbytes
 

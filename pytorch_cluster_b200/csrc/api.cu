@@ -40,7 +40,8 @@ static int check_common(const void *x, const void *y, const int64_t *ptr_x, cons
   B200C_CHECK_ARG(x != nullptr && y != nullptr, "x and y must be CUDA tensors");
   B200C_CHECK_ARG(n >= 0 && m >= 0 && dim >= 1, "Input mismatch");
   B200C_CHECK_ARG(n <= 0x7fffffffLL && m <= 0x7fffffffLL, "more than 2^31-1 rows are not supported");
-  B200C_CHECK_ARG(dtype == B200C_F32 || dtype == B200C_F64, "unsupported dtype");
+  B200C_CHECK_ARG(dtype == B200C_F32 || dtype == B200C_F64 || dtype == B200C_F16 || dtype == B200C_BF16,
+                  "unsupported dtype");
   B200C_CHECK_ARG((ptr_x == nullptr) == (ptr_y == nullptr), "Input mismatch");
   B200C_CHECK_ARG(ptr_x == nullptr ? num_segments == 1 : (num_segments >= 1 && num_segments <= 0x7fffffffLL),
                   "Input mismatch");
@@ -56,12 +57,33 @@ extern "C" int b200c_version(void) { return 100; }
 extern "C" const char *b200c_last_error(void) { return g_error; }
 
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+static bool is16(int dtype) { return dtype == B200C_F16 || dtype == B200C_BF16; }
+
+// float copies of 16-bit x and y at the front of a workspace
+static size_t widen_bytes(int64_t n, int64_t m, int64_t dim, int dtype) {
+  return is16(dtype) ? align256((size_t)n * dim * 4) + align256((size_t)m * dim * 4) : 0;
+}
+
+static int widen_inputs(const void *&x, const void *&y, int64_t n, int64_t m, int64_t dim, int dtype,
+                        void *workspace, bool convert, cudaStream_t stream) {
+  float *x32 = (float *)workspace;
+  float *y32 = (float *)((char *)workspace + align256((size_t)n * dim * 4));
+  if (convert) {
+    int st = launch_widen16(x, n * dim, dtype, x32, stream);
+    if (st != B200C_OK) return st;
+    if ((st = launch_widen16(y, m * dim, dtype, y32, stream)) != B200C_OK) return st;
+  }
+  x = x32;
+  y = y32;
+  return B200C_OK;
+}
 
 extern "C" size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t k, int dtype, int cosine,
                                             int64_t num_segments) {
   const size_t elem = dtype == B200C_F64 ? 8 : 4;
-  // cosine: |row| of every x and y row
-  const size_t exact = cosine ? align256((size_t)n * elem) + align256((size_t)m * elem) : 0;
+  // 16-bit types: float copies; cosine: |row| of every x and y row
+  const size_t exact = widen_bytes(n, m, dim, dtype) +
+                       (cosine ? align256((size_t)n * elem) + align256((size_t)m * elem) : 0);
   // tensor-core candidate path: norms, candidate lists (and normalised copies for cosine)
   if (dtype == B200C_F32 && num_segments >= 1 &&
       knn_tensor_applicable(n, m, (int)dim, (int)k, num_segments, nullptr, nullptr)) {
@@ -89,13 +111,31 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
   // required: the norms of the exact cosine kernel; the larger size b200c_knn_workspace_bytes may
   // report also enables the tensor-core candidate path and is optional
   const size_t elem_bytes = dtype == B200C_F64 ? 8 : 4;
-  const size_t need = cosine ? align256((size_t)n * elem_bytes) + align256((size_t)m * elem_bytes) : 0;
+  const size_t wide = widen_bytes(n, m, dim, dtype);
+  const size_t need = wide + (cosine ? align256((size_t)n * elem_bytes) + align256((size_t)m * elem_bytes) : 0);
   if (need > 0 && (workspace == nullptr || workspace_bytes < need)) {
     set_error("kNN workspace too small: %zu < %zu", workspace_bytes, need);
     return B200C_ERR_WORKSPACE;
   }
   KnnArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, (int)k, cosine, nullptr, nullptr,
             edge_padded, edge_padded + m * k, counts, (unsigned long long *)num_valid, stream};
+  if (is16(dtype)) {
+    // exact general-dimension kernels on float copies, every operation rounded to the 16-bit type
+    if ((st = widen_inputs(a.x, a.y, n, m, dim, dtype, workspace, true, stream)) != B200C_OK) return st;
+    const bool h = dtype == B200C_F16;
+    if (cosine) {
+      char *ws = (char *)workspace + wide;
+      a.norms_x = ws;
+      a.norms_y = ws + align256((size_t)n * 4);
+      st = h ? launch_row_norms_f16(a.x, n, (int)dim, (void *)a.norms_x, stream)
+             : launch_row_norms_bf16(a.x, n, (int)dim, (void *)a.norms_x, stream);
+      if (st != B200C_OK) return st;
+      st = h ? launch_row_norms_f16(a.y, m, (int)dim, (void *)a.norms_y, stream)
+             : launch_row_norms_bf16(a.y, m, (int)dim, (void *)a.norms_y, stream);
+      if (st != B200C_OK) return st;
+    }
+    return h ? launch_knn_generic_f16(a) : launch_knn_generic_bf16(a);
+  }
   const bool f32 = dtype == B200C_F32;
   if (f32 && knn_tensor_applicable(n, m, (int)dim, (int)k, num_segments, x, y) &&
       workspace_bytes >= knn_tensor_workspace_bytes(n, m, (int)dim, cosine))
@@ -122,10 +162,16 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
 static constexpr int64_t RADIUS_DIRECT_MAX_NN = 256;
 static constexpr int64_t RADIUS_DIRECT_MAX_BYTES = 2ll << 30;
 
-extern "C" size_t b200c_radius_workspace_bytes(int64_t m, int64_t dim, int64_t max_num_neighbors) {
+static size_t radius_direct_bytes(int64_t m, int64_t dim, int64_t max_num_neighbors) {
   if (m <= 0 || dim < 1 || dim > 8 || max_num_neighbors < 1 || max_num_neighbors > RADIUS_DIRECT_MAX_NN) return 0;
   const int64_t bytes = m * max_num_neighbors * 4;
   return bytes <= RADIUS_DIRECT_MAX_BYTES ? (size_t)bytes : 0;
+}
+
+extern "C" size_t b200c_radius_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t max_num_neighbors,
+                                               int dtype) {
+  if (is16(dtype)) return n >= 0 && m >= 0 && dim >= 1 ? widen_bytes(n, m, dim, dtype) : 0;
+  return radius_direct_bytes(m, dim, max_num_neighbors);
 }
 
 static int radius_common(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
@@ -138,7 +184,19 @@ static int radius_common(const void *x, const void *y, const int64_t *ptr_x, con
   B200C_CHECK_ARG(max_num_neighbors >= 1, "max_num_neighbors must be positive");
   if ((st = check_device()) != B200C_OK) return st;
   if (m == 0) return B200C_OK;
-  const size_t direct_bytes = b200c_radius_workspace_bytes(m, dim, max_num_neighbors);
+  if (is16(dtype)) {
+    const size_t need = widen_bytes(n, m, dim, dtype);
+    if (workspace == nullptr || workspace_bytes < need) {
+      set_error("radius workspace too small for 16-bit inputs: %zu < %zu", workspace_bytes, need);
+      return B200C_ERR_WORKSPACE;
+    }
+    // the count pass converts; the fill pass finds the copies where the count pass left them
+    if ((st = widen_inputs(x, y, n, m, dim, dtype, workspace, !fill, stream)) != B200C_OK) return st;
+    RadiusArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, r, max_num_neighbors,
+                 ignore_same_index, counts, offsets, out_row, out_col, nullptr, stream};
+    return dtype == B200C_F16 ? launch_radius_generic_f16(a, fill) : launch_radius_generic_bf16(a, fill);
+  }
+  const size_t direct_bytes = radius_direct_bytes(m, dim, max_num_neighbors);
   int32_t *direct = (direct_bytes > 0 && workspace != nullptr && workspace_bytes >= direct_bytes)
                         ? (int32_t *)workspace
                         : nullptr;

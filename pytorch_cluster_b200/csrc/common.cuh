@@ -1,6 +1,8 @@
 // Shared device/host helpers of the sm_100a neighbour-graph kernels.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -244,6 +246,67 @@ __device__ __forceinline__ void cp_async_elem(T *smem_dst, const T *gmem_src) {
     cp_async_4(smem_dst, gmem_src);
   else
     cp_async_8(smem_dst, gmem_src);
+}
+
+// Arithmetic of 16-bit inputs.  The reference instantiates its kernels for c10::Half (and, for
+// radius, c10::BFloat16), whose operators compute in float and round every single result back to
+// the 16-bit type (torch/headeronly/util/Half.h: `operator+`, `operator*`, ... return
+// static_cast<float>(a) op static_cast<float>(b), narrowed by __float2half / __float2bfloat16,
+// round-to-nearest-even).  Here such inputs are widened to float once and every operation result is
+// passed through rnd16<RND>: RND 0 = none (float / double data), 1 = fp16, 2 = bf16.
+template <int RND, typename T>
+__device__ __forceinline__ T rnd16(T v) {
+  if constexpr (RND == 1) {
+    return __half2float(__float2half_rn(v));
+  } else if constexpr (RND == 2) {
+    return __bfloat162float(__float2bfloat16_rn(v));
+  } else {
+    return v;
+  }
+}
+
+// acc + diff^2 with diff = a - b, as the reference's `acc += (a - b) * (a - b)` evaluates it:
+// one fused multiply-add for float / double (nvcc contracts the expression), three separately
+// rounded operations for the 16-bit types.
+template <int RND, typename T>
+__device__ __forceinline__ T sq_accumulate(T a, T b, T acc) {
+  if constexpr (RND == 0) {
+    const T diff = a - b;
+    if constexpr (sizeof(T) == 4)
+      return __fmaf_rn(diff, diff, acc);
+    else
+      return __fma_rn(diff, diff, acc);
+  } else {
+    const float diff = rnd16<RND>(__fsub_rn(a, b));
+    const float prod = rnd16<RND>(__fmul_rn(diff, diff));
+    return rnd16<RND>(__fadd_rn(acc, prod));
+  }
+}
+
+// acc + a * b (`result += a * b`, csrc/cuda/knn_cuda.cu:13-16), same policy.
+template <int RND, typename T>
+__device__ __forceinline__ T dot_accumulate(T a, T b, T acc) {
+  if constexpr (RND == 0) {
+    if constexpr (sizeof(T) == 4)
+      return __fmaf_rn(a, b, acc);
+    else
+      return __fma_rn(a, b, acc);
+  } else {
+    return rnd16<RND>(__fadd_rn(acc, rnd16<RND>(__fmul_rn(a, b))));
+  }
+}
+
+// 1 - dot / (|x| * |y|) (csrc/cuda/knn_cuda.cu:55-59).  For the 16-bit types the product, the
+// quotient and the final difference (formed in double, narrowed through float) are each rounded.
+template <int RND, typename T>
+__device__ __forceinline__ T cosine_finish(T dot, T nx, T ny) {
+  if constexpr (RND == 0) {
+    return (T)1 - dot / (nx * ny);
+  } else {
+    const float den = rnd16<RND>(__fmul_rn(nx, ny));
+    const float q = rnd16<RND>(__fdiv_rn(dot, den));
+    return rnd16<RND>((float)(1.0 - (double)q));
+  }
 }
 
 template <typename T>

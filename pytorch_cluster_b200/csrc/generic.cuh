@@ -83,7 +83,8 @@ __device__ __forceinline__ T fma_rn(T a, T b, T c) {
 // MODE GEN_KNN:          out_row/out_col padded [m*k], counts, num_valid; `bound0` unused.
 // MODE GEN_RADIUS_COUNT: counts.   MODE GEN_RADIUS_FILL: offsets -> out_row/out_col.
 // COSINE only with GEN_KNN; norms_x / norms_y hold |row| as the reference computes it.
-template <typename T, int MODE, int KP, bool COSINE>
+// RND: rounding of every operation result for 16-bit inputs widened to float (see rnd16).
+template <typename T, int MODE, int KP, bool COSINE, int RND = 0>
 __global__ void __launch_bounds__(CTA_THREADS)
 generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *__restrict__ ptr_x,
                const int64_t *__restrict__ ptr_y, int num_segments, int64_t n, int64_t m, int dim, int k,
@@ -131,7 +132,7 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
     int limit[QW];
 #pragma unroll
     for (int qi = 0; qi < QW; ++qi) {
-      bound[qi] = MODE == GEN_KNN ? (T)1e10 : r2;
+      bound[qi] = MODE == GEN_KNN ? rnd16<RND>((T)1e10) : r2;
       ny[qi] = (T)1;
       cnt[qi] = 0;
       base[qi] = 0;
@@ -216,12 +217,10 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
               for (int dd = 0; dd < 4; ++dd)
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                  if constexpr (COSINE) {
-                    acc[s][qi][r] = fma_rn(xv[r][dd], qv[dd], acc[s][qi][r]);
-                  } else {
-                    const T diff = xv[r][dd] - qv[dd];
-                    acc[s][qi][r] = fma_rn(diff, diff, acc[s][qi][r]);
-                  }
+                  if constexpr (COSINE)
+                    acc[s][qi][r] = dot_accumulate<RND>(xv[r][dd], qv[dd], acc[s][qi][r]);
+                  else
+                    acc[s][qi][r] = sq_accumulate<RND>(xv[r][dd], qv[dd], acc[s][qi][r]);
                 }
             }
           }
@@ -248,7 +247,7 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
                 for (int r = 0; r < R; ++r) {
                   const int i = s * R + r;
                   T d = acc[s][qi][r];
-                  if constexpr (COSINE) d = (T)1 - d / (nxv[i] * ny[qi]);
+                  if constexpr (COSINE) d = cosine_finish<RND>(d, nxv[i], ny[qi]);
                   dist[i] = (idx0 + 32 * i) < x_hi ? d : pos_inf<T>();
                 }
               const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
@@ -309,10 +308,7 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
             int64_t c = tot;
             if (ignore_same && q >= x_lo && q < x_hi) {
               T a = 0;
-              for (int d = 0; d < dim; ++d) {
-                const T diff = x[q * dim + d] - y[q * dim + d];
-                a = fma_rn(diff, diff, a);
-              }
+              for (int d = 0; d < dim; ++d) a = sq_accumulate<RND>(x[q * dim + d], y[q * dim + d], a);
               if (a < r2) c -= 1;
             }
             counts[q] = (int32_t)(c < max_nn ? c : max_nn);
@@ -329,16 +325,16 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
 
 // |row| for the cosine distance: sqrt of the sequential fused sum of squares
 // (csrc/cuda/knn_cuda.cu:20-27).  One thread per row.
-template <typename T>
+template <typename T, int RND = 0>
 __global__ void row_norms_kernel(const T *__restrict__ a, int64_t rows, int dim, T *__restrict__ out) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows) return;
   T s = 0;
   for (int d = 0; d < dim; ++d) {
     const T v = a[i * dim + d];
-    s = fma_rn(v, v, s);
+    s = dot_accumulate<RND>(v, v, s);
   }
-  out[i] = sqrt(s);
+  out[i] = rnd16<RND>(sqrt(s));
 }
 
 }  // namespace b200c

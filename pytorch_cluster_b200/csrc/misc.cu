@@ -1,5 +1,6 @@
 // Small HBM-bound passes around the search kernels: segment pointers, the exclusive scan of the
 // per-query edge counts, and the compaction of padded kNN output.
+#include <type_traits>
 #include <mutex>
 
 #include "common.cuh"
@@ -197,6 +198,31 @@ __global__ void knn_graph_tail_write_kernel(const int64_t *__restrict__ col_padd
     }
     o += __popc(mask);
   }
+}
+
+// fp16 / bf16 -> float, exact (every 16-bit value is a float value).  Grid-stride, 2 elements per
+// 32-bit load where the element count allows it.
+template <typename H>
+__global__ void widen16_kernel(const H *__restrict__ src, int64_t elems, float *__restrict__ dst) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += stride) {
+    if constexpr (sizeof(H) == 2 && std::is_same<H, __half>::value)
+      dst[i] = __half2float(src[i]);
+    else
+      dst[i] = __bfloat162float(src[i]);
+  }
+}
+
+int launch_widen16(const void *src, int64_t elems, int dtype, float *dst, cudaStream_t stream) {
+  if (elems == 0) return B200C_OK;
+  const int64_t want = (elems + 255) / 256;
+  const unsigned grid = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  if (dtype == B200C_F16)
+    widen16_kernel<__half><<<grid, 256, 0, stream>>>((const __half *)src, elems, dst);
+  else
+    widen16_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16 *)src, elems, dst);
+  B200C_LAUNCH_CHECK("widen16_kernel");
+  return B200C_OK;
 }
 
 }  // namespace b200c

@@ -21,13 +21,18 @@ void check_status(int status) {
   TORCH_CHECK(status == B200C_OK, "b200_cluster: ", b200c_last_error());
 }
 
-// fp16 / bf16 inputs are widened to fp32 (every fp16/bf16 value is an fp32 value); the search
-// then runs with fp32 accumulation.
-torch::Tensor as_supported(const torch::Tensor &t) {
-  const auto st = t.scalar_type();
-  if (st == at::kHalf || st == at::kBFloat16) return t.to(at::kFloat);
-  TORCH_CHECK(st == at::kFloat || st == at::kDouble, "expected a floating point tensor, got ", st);
-  return t;
+// float, double, and the 16-bit types with the reference's rounding of every operation to the
+// 16-bit type (csrc/cuda/knn_cuda.cu:125, csrc/cuda/radius_cuda.cu:84-85).  kNN on bfloat16 is an
+// extension: the reference dispatches it for radius only.
+int dtype_code(const torch::Tensor &t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return B200C_F32;
+    case at::kDouble: return B200C_F64;
+    case at::kHalf: return B200C_F16;
+    case at::kBFloat16: return B200C_BF16;
+    default: TORCH_CHECK(false, "expected a floating point tensor, got ", t.scalar_type());
+  }
+  return -1;
 }
 
 struct Prepared {
@@ -50,9 +55,9 @@ Prepared prepare(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> 
   CHECK_INPUT(x.scalar_type() == y.scalar_type());
 
   Prepared p;
-  p.x = as_supported(x);
-  p.y = as_supported(y);
-  p.dtype = p.x.scalar_type() == at::kDouble ? B200C_F64 : B200C_F32;
+  p.x = x;
+  p.y = y;
+  p.dtype = dtype_code(x);
 
   if (ptr_x.has_value() || ptr_y.has_value()) {
     // a missing side defaults to one segment over all rows (csrc/cuda/knn_cuda.cu:100-112)
@@ -171,7 +176,7 @@ torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tens
 
   auto counts = torch::empty({m}, x.options().dtype(torch::kInt));
   // small neighbour caps: one scan that also parks the hits, then a copy (see b200_cluster.h)
-  const size_t ws_bytes = b200c_radius_workspace_bytes(m, dim, max_num_neighbors);
+  const size_t ws_bytes = b200c_radius_workspace_bytes(n, m, dim, max_num_neighbors, p.dtype);
   auto ws = torch::empty({(int64_t)ws_bytes}, x.options().dtype(torch::kByte));
   void *ws_ptr = ws_bytes ? ws.data_ptr() : nullptr;
   check_status(b200c_radius_count(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,

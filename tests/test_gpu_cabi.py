@@ -296,3 +296,82 @@ def test_argument_errors():
     st = lib.b200c_knn(x.data_ptr(), x.data_ptr(), None, None, 1, 10, 10, 3, 101, 0, 0, out.data_ptr(),
                        cnt.data_ptr(), nv.data_ptr(), None, 0, None)
     assert st == 1 and b"smaller than or equal to 100" in lib.b200c_last_error()
+
+
+# ---- 16-bit inputs: every operation rounded to fp16 / bf16, as the reference's c10::Half /
+# c10::BFloat16 instantiations compute (csrc/cuda/knn_cuda.cu:125, csrc/cuda/radius_cuda.cu:84-85) ----
+
+T16 = {"f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def _check_knn16(x, y, k, kind, px=None, py=None, cosine=False):
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    dx, dy = x.to(DEV), y.to(DEV)
+    dpx = None if px is None else px.to(DEV)
+    dpy = None if py is None else py.to(DEV)
+    padded, counts, nvalid = _cabi.knn_padded(dx, dy, k, dpx, dpy, cosine)
+    want_col, _ = orc.knn_padded(x.float().numpy(), y.float().numpy(), k, None if px is None else px.numpy(),
+                                 None if py is None else py.numpy(), cosine=cosine, round16=kind)
+    m = y.shape[0]
+    got_col = padded.cpu().numpy()[1].reshape(m, k)
+    bad = np.nonzero((got_col != want_col).any(axis=1))[0]
+    assert bad.size == 0, (f"{bad.size} of {m} queries differ; first {bad[:5]}: got {got_col[bad[:3]]} "
+                           f"want {want_col[bad[:3]]}")
+    assert nvalid == int((want_col >= 0).sum())
+    e = _cabi.knn(dx, dy, k, dpx, dpy, cosine).cpu().numpy()
+    assert np.array_equal(e, orc.knn(x.float().numpy(), y.float().numpy(), k, None if px is None else px.numpy(),
+                                     None if py is None else py.numpy(), cosine=cosine, round16=kind))
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("dim", [1, 2, 3, 5, 8, 13, 16, 40])
+def test_knn_16bit(dim, kind):
+    x, y = _data(300 + dim, 1800, 260, dim, torch.float32)
+    x, y = x.to(T16[kind]), y.to(T16[kind])
+    _check_knn16(x, y, 12, kind)
+    sx, sy = [500, 0, 9, 1291], [100, 10, 50, 100]
+    _check_knn16(x, y, 33, kind, _segments(sx), _segments(sy))   # a segment with fewer than k points
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("dim", [3, 24])
+def test_knn_16bit_cosine(dim, kind):
+    x, y = _data(330 + dim, 1500, 200, dim, torch.float32)
+    x, y = x.to(T16[kind]), y.to(T16[kind])
+    x[5] = 0  # a zero row: 0 / 0 = NaN, never selected
+    _check_knn16(x, y, 10, kind, cosine=True)
+
+
+def test_knn_16bit_overflow_and_large_k():
+    """fp16 distances overflow to +inf beyond 65504: such points are never selected
+    (`inf < inf` is false; the initial bound 1e10 narrows to +inf)."""
+    x, y = _data(77, 900, 64, 3, torch.float32, scale=120.0)
+    _check_knn16(x.half(), y.half(), 100, "f16")
+
+
+def _check_radius16(x, y, r, kind, px=None, py=None, max_nn=32, ignore_same=False):
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    dx, dy = x.to(DEV), y.to(DEV)
+    dpx = None if px is None else px.to(DEV)
+    dpy = None if py is None else py.to(DEV)
+    e = _cabi.radius(dx, dy, r, dpx, dpy, max_nn, ignore_same).cpu().numpy()
+    want = orc.radius(x.float().numpy(), y.float().numpy(), r, None if px is None else px.numpy(),
+                      None if py is None else py.numpy(), max_nn, ignore_same, round16=kind)
+    assert e.shape == want.shape, (e.shape, want.shape)
+    assert np.array_equal(e, want)
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("dim", [1, 3, 8, 20])
+def test_radius_16bit(dim, kind):
+    g = torch.Generator().manual_seed(400 + dim)
+    x = torch.rand(2500, dim, generator=g).to(T16[kind])
+    y = torch.rand(600, dim, generator=g).to(T16[kind])
+    r = 0.02 if dim == 1 else (0.2 if dim == 3 else 0.45 * dim ** 0.5)
+    _check_radius16(x, y, r, kind, max_nn=10000)
+    _check_radius16(x, y, r, kind, max_nn=7)
+    sx, sy = [1000, 0, 1500], [200, 100, 300]
+    _check_radius16(x, y, r, kind, _segments(sx), _segments(sy), max_nn=40)
+    _check_radius16(x, x, r, kind, max_nn=25, ignore_same=True)

@@ -198,3 +198,34 @@ def test_time_beside_reference_kernels():
             json.dump(out, f, indent=1)
     for k, v in out.items():
         assert v["ratio"] >= 1.0, (k, v)
+
+
+# ---- 16-bit inputs: the reference instantiates knn for c10::Half and radius for c10::Half and
+# c10::BFloat16; this library rounds every operation the same way ----
+
+@pytest.mark.parametrize("dim", [1, 3, 8, 19, 64])
+@pytest.mark.parametrize("cosine", [False, True])
+def test_knn_half(dim, cosine):
+    g = torch.Generator().manual_seed(500 + dim)
+    x = torch.randn(3000, dim, generator=g).to(DEV).half()
+    y = torch.randn(500, dim, generator=g).to(DEV).half()
+    px = torch.tensor([0, 1200, 1200, 3000], device=DEV)
+    py = torch.tensor([0, 200, 260, 500], device=DEV)
+    for k in (1, 9, 40):
+        _same(_ours_knn(x, y, px, py, k, cosine), refc.knn(x, y, px, py, k, cosine))
+    big = (x * 100).half()  # squared distances overflow fp16
+    _same(_ours_knn(big, big, px, px, 6, cosine), refc.knn(big, big, px, px, 6, cosine))
+
+
+@pytest.mark.parametrize("dtype", [torch.half, torch.bfloat16])
+@pytest.mark.parametrize("dim", [1, 3, 8, 19])
+def test_radius_16bit(dtype, dim):
+    g = torch.Generator().manual_seed(600 + dim)
+    x = torch.rand(5000, dim, generator=g).to(DEV).to(dtype)
+    y = torch.rand(900, dim, generator=g).to(DEV).to(dtype)
+    px = torch.tensor([0, 2000, 5000], device=DEV)
+    py = torch.tensor([0, 400, 900], device=DEV)
+    r = 0.02 if dim == 1 else (0.2 if dim == 3 else 0.42 * dim ** 0.5)
+    for max_nn in (5, 64, 5000):
+        _same(_ours_radius(x, y, px, py, r, max_nn, False), refc.radius(x, y, px, py, r, max_nn, False))
+    _same(_ours_radius(x, x, px, px, r, 32, True), refc.radius(x, x, px, px, r, 32, True))

@@ -183,3 +183,61 @@ def test_oracle_vs_reference_cpu_radius_live():
     for fused in (True, False):
         got = orc.radius(x.numpy(), y.numpy(), 0.08, max_num_neighbors=100000, fused=fused)
         assert_radius_equal(got, want)
+
+
+# ---- 16-bit restatement: pinned here against torch's own fp16 / bf16 tensor arithmetic (the same
+# c10::Half / c10::BFloat16 definition the reference's kernels are instantiated with) and the
+# reference's half-precision known-answer cases; on the GPU against the reference's CUDA kernels ----
+
+def _dist16(x16, y16):
+    """Per-operation rounded squared distances [m, n] computed with torch 16-bit tensors."""
+    d = torch.zeros(y16.shape[0], x16.shape[0], dtype=x16.dtype)
+    for j in range(x16.shape[1]):
+        diff = (x16[None, :, j].float() - y16[:, None, j].float()).to(x16.dtype)
+        prod = (diff.float() * diff.float()).to(x16.dtype)
+        d = (d.float() + prod.float()).to(x16.dtype)
+    return d
+
+
+@pytest.mark.parametrize("kind,dtype", [("f16", torch.float16), ("bf16", torch.bfloat16)])
+def test_oracle_16bit_matches_torch_16bit_arithmetic(kind, dtype):
+    g = torch.Generator().manual_seed(16)
+    x = (torch.randn(400, 3, generator=g) * 3).to(dtype)
+    y = (torch.randn(30, 3, generator=g) * 3).to(dtype)
+    d = _dist16(x, y)
+    want = []
+    for q in range(30):
+        cand = [i for i in range(400) if float(d[q, i]) < float("inf")]
+        want += [(q, i) for i in sorted(cand, key=lambda i: (float(d[q, i]), i))[:6]]
+    got = orc.knn(x.float().numpy(), y.float().numpy(), 6, round16=kind)
+    assert list(map(tuple, got.T.tolist())) == want
+    r = 1.3
+    r2 = float(torch.tensor(r * r, dtype=torch.float64).float().to(dtype))
+    want = [(q, i) for q in range(30) for i in range(400) if float(d[q, i]) < r2]
+    got = orc.radius(x.float().numpy(), y.float().numpy(), r, max_num_neighbors=4000, round16=kind)
+    assert list(map(tuple, got.T.tolist())) == want
+    got = orc.radius(x.float().numpy(), y.float().numpy(), r, max_num_neighbors=3, round16=kind)
+    trunc = []
+    for q in range(30):
+        trunc += [e for e in want if e[0] == q][:3]
+    assert list(map(tuple, got.T.tolist())) == trunc
+
+
+def test_oracle_16bit_reference_known_answers():
+    """test/test_knn.py:16-52 and test/test_radius.py:25-61 at half precision."""
+    x = np.array([[-1, -1], [-1, 1], [1, 1], [1, -1]] * 2, dtype=np.float32)
+    y = np.array([[1, 0], [-1, 0]], dtype=np.float32)
+    px, py = np.array([0, 4, 8]), np.array([0, 1, 2])
+    for kind in ("f16", "bf16"):
+        e = orc.knn(x, y, 2, round16=kind)
+        assert set(map(tuple, e.T.tolist())) == {(0, 2), (0, 3), (1, 0), (1, 1)}
+        e = orc.knn(x, y, 2, px, py, round16=kind)
+        assert set(map(tuple, e.T.tolist())) == {(0, 2), (0, 3), (1, 4), (1, 5)}
+        e = orc.knn(x, y, 2, px, py, cosine=True, round16=kind)
+        assert set(map(tuple, e.T.tolist())) == {(0, 2), (0, 3), (1, 4), (1, 5)}
+    yr = np.array([[0, 0], [0, 1]], dtype=np.float32)
+    for kind in ("f16", "bf16"):
+        e = orc.radius(x, yr, 2, max_num_neighbors=4, round16=kind)
+        assert set(map(tuple, e.T.tolist())) == {(0, 0), (0, 1), (0, 2), (0, 3), (1, 1), (1, 2), (1, 5), (1, 6)}
+        e = orc.radius(x, yr, 2, px, py, max_num_neighbors=4, round16=kind)
+        assert set(map(tuple, e.T.tolist())) == {(0, 0), (0, 1), (0, 2), (0, 3), (1, 5), (1, 6)}
