@@ -176,6 +176,39 @@ int b200c_radius_fill(const void *x, const void *y, const int64_t *ptr_x,
                       int64_t num_edges, int64_t *edge_index, void *workspace,
                       size_t workspace_bytes, b200c_stream_t stream);
 
+/* Nearest point assignment — replaces nearest_kernel + nearest_cuda
+ * (csrc/cuda/nearest_cuda.cu:9-61, 63-88).
+ *
+ * out[i] (int64 [n]) = the row of y, within the segment of x row i, with the smallest squared
+ * distance to x[i].  As in the reference only distances below 1e38 compete (none: out[i] = 0),
+ * NaN never wins, and among equal minima the reference's reduction order decides: the point with
+ * the smallest ((index - segment start) mod 1024, index).
+ * workspace: b200c_nearest_workspace_bytes(...) bytes, non-zero (and required) for the 16-bit
+ * types only. */
+size_t b200c_nearest_workspace_bytes(int64_t n, int64_t m, int64_t dim, int dtype);
+int b200c_nearest(const void *x, const void *y, const int64_t *ptr_x,
+                  const int64_t *ptr_y, int64_t num_segments, int64_t n, int64_t m,
+                  int64_t dim, int dtype, int64_t *out, void *workspace,
+                  size_t workspace_bytes, b200c_stream_t stream);
+
+/* Farthest point sampling — replaces fps_kernel and its launch in fps_cuda
+ * (csrc/cuda/fps_cuda.cu:9-68, 100-109).
+ *
+ * For every segment b (ptr [num_segments + 1]) writes out_ptr[b+1] - out_ptr[b] sample indices
+ * (global rows of src) at out[out_ptr[b]..]: the first is ptr[b] + start[b] (start == NULL: 0),
+ * each further one the point farthest from the samples so far, the running distance starting at
+ * 5e4 as in the reference; among equal maxima the point with the smallest
+ * ((index - segment start) mod 256, index) wins, which is what the reference's 256-thread
+ * reduction yields.  out_ptr is the caller's (the reference derives it from ratio on the host
+ * side, fps_cuda.cu:83-86).  Segments of up to 200 KB / ((dim + 1) * element size) points are
+ * held in shared memory for the whole call; larger ones run from global memory.
+ * workspace: b200c_fps_workspace_bytes(n, dim, dtype) bytes, required. */
+size_t b200c_fps_workspace_bytes(int64_t n, int64_t dim, int dtype);
+int b200c_fps(const void *src, const int64_t *ptr, const int64_t *out_ptr,
+              const int64_t *start, int64_t num_segments, int64_t n, int64_t dim,
+              int dtype, int64_t *out, void *workspace, size_t workspace_bytes,
+              b200c_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,7 +1,7 @@
 """Build recipe for ``oracle/_ref/ref_cluster_cpu.so`` (test infrastructure).
 
 Compiles the reference's unmodified CPU neighbour search
-(``csrc/cpu/knn_cpu.cpp``, ``csrc/cpu/radius_cpu.cpp`` with the vendored
+(``csrc/cpu/knn_cpu.cpp``, ``csrc/cpu/radius_cpu.cpp``, ``csrc/cpu/fps_cpu.cpp`` with the vendored
 nanoflann header under ``csrc/cpu/utils``) straight from the reference checkout
 with g++, together with ``oracle/ref_shim.cpp`` which registers the two
 functions as ``ref_cluster::knn_cpu`` / ``ref_cluster::radius_cpu``.  Flags
@@ -46,6 +46,7 @@ def build(reference: str, force: bool = False, verbose: bool = True) -> str | No
     srcs = [
         os.path.join(csrc, "cpu", "knn_cpu.cpp"),
         os.path.join(csrc, "cpu", "radius_cpu.cpp"),
+        os.path.join(csrc, "cpu", "fps_cpu.cpp"),
         os.path.join(HERE, "ref_shim.cpp"),
     ]
     if not force and os.path.exists(OUT) and all(
@@ -76,7 +77,7 @@ def build(reference: str, force: bool = False, verbose: bool = True) -> str | No
 
 def build_cuda(reference: str, force: bool = False, verbose: bool = True) -> str | None:
     """Compile the reference's unmodified CUDA kernels of this path
-    (``csrc/cuda/knn_cuda.cu``, ``csrc/cuda/radius_cuda.cu``) for sm_100a with nvcc, plus
+    (``csrc/cuda/knn_cuda.cu``, ``radius_cuda.cu``, ``nearest_cuda.cu``, ``fps_cuda.cu``) for sm_100a with nvcc, plus
     ``oracle/ref_shim_cuda.cpp``, into ``oracle/_ref/ref_cluster_cuda.so``.  Returns the path,
     or None when neither the reference checkout nor a previously built file exists."""
     import shutil
@@ -85,7 +86,7 @@ def build_cuda(reference: str, force: bool = False, verbose: bool = True) -> str
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.isdir(csrc) or not os.path.exists(nvcc):
         return OUT_CUDA if os.path.exists(OUT_CUDA) else None
-    cu = [os.path.join(csrc, "cuda", "knn_cuda.cu"), os.path.join(csrc, "cuda", "radius_cuda.cu")]
+    cu = [os.path.join(csrc, "cuda", f) for f in ("knn_cuda.cu", "radius_cuda.cu", "nearest_cuda.cu", "fps_cuda.cu")]
     shim = os.path.join(HERE, "ref_shim_cuda.cpp")
     if not force and os.path.exists(OUT_CUDA) and all(
         os.path.getmtime(OUT_CUDA) >= os.path.getmtime(s) for s in cu + [shim]

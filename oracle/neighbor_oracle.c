@@ -15,6 +15,9 @@
  *   - radius scan           csrc/cuda/radius_cuda.cu:26-41 (strict '<', first
  *                           max_num_neighbors hits in ascending x order)
  *   - r*r narrowing         csrc/cuda/radius_cuda.cu:90
+ *   - nearest               csrc/cuda/nearest_cuda.cu:9-61 (1024-thread stride and
+ *                           tree reduction: their tie order is restated, see below)
+ *   - farthest point sampling  csrc/cuda/fps_cuda.cu:9-68
  *
  * Rounding policy.  nvcc contracts `acc += d*d` into one fused multiply-add by
  * default, so the reference CUDA kernels accumulate acc = fma(d, d, acc) in the
@@ -305,3 +308,106 @@ int64_t oracle_radius_r16(const float *x, const float *y, const int64_t *ptr_x, 
   }
   return total;
 }
+
+
+/* ---- nearest and farthest point sampling ------------------------------------------------------
+ * Both reference kernels stride THREADS threads over a segment, keep each thread's first strict
+ * optimum and then reduce over threads keeping the lower thread on equal values.  Assuming each
+ * reduction round reads the values of the round before (the reference's shared-memory updates
+ * are not double buffered; values it may mix are equal-distance entries only), the winner among
+ * equal optima is the entry with the smallest ((index - segment start) mod THREADS, index).
+ * policy: 0 = float with fused multiply-add (nvcc's contraction), 1 = fp16, 2 = bf16 rounding of
+ * every operation; the double variants always fuse. */
+
+static inline float sqd_policy_f32(const float *a, const float *b, int64_t dim, int policy) {
+  if (policy != 0)
+    return sqdist_r16(a, b, dim, policy);
+  float acc = 0;
+  for (int64_t d = 0; d < dim; d++) {
+    float diff = a[d] - b[d];
+    acc = fmaf(diff, diff, acc);
+  }
+  return acc;
+}
+
+static inline double sqd_f64(const double *a, const double *b, int64_t dim) {
+  double acc = 0;
+  for (int64_t d = 0; d < dim; d++) {
+    double diff = a[d] - b[d];
+    acc = fma(diff, diff, acc);
+  }
+  return acc;
+}
+
+static inline int tie_before(int64_t i, int64_t j, int64_t lo, int64_t threads) {
+  int64_t a = (i - lo) % threads, b = (j - lo) % threads;
+  return a < b || (a == b && i < j);
+}
+
+#define DEFINE_NEAREST_FPS(T, SUFFIX, DIST, INIT_NEAREST, INIT_FPS)                               \
+  /* nearest_cuda.cu:9-61: out[n_x] = nearest y of the same segment */                           \
+  void oracle_nearest_##SUFFIX(const T *x, const T *y, const int64_t *ptr_x, const int64_t *ptr_y, \
+                               int64_t num_segments, int64_t n, int64_t dim, int policy,         \
+                               int64_t *out) {                                                   \
+    (void)policy;                                                                                \
+    _Pragma("omp parallel for schedule(dynamic, 64)")                                            \
+    for (int64_t n_x = 0; n_x < n; n_x++) {                                                      \
+      int64_t b = 0;                                                                             \
+      for (; b < num_segments; b++)                                                              \
+        if (n_x >= ptr_x[b] && n_x < ptr_x[b + 1])                                               \
+          break;                                                                                 \
+      const T init = INIT_NEAREST;                                                               \
+      T best = init;                                                                             \
+      int64_t best_idx = 0;                                                                      \
+      int found = 0;                                                                             \
+      for (int64_t n_y = ptr_y[b]; n_y < ptr_y[b + 1]; n_y++) {                                  \
+        T dist = DIST(x + n_x * dim, y + n_y * dim, dim, policy);                                \
+        if (!(dist < init))                                                                      \
+          continue;                                                                              \
+        if (!found || dist < best ||                                                             \
+            (dist == best && tie_before(n_y, best_idx, ptr_y[b], 1024))) {                       \
+          best = dist;                                                                           \
+          best_idx = n_y;                                                                        \
+          found = 1;                                                                             \
+        }                                                                                        \
+      }                                                                                          \
+      out[n_x] = best_idx;                                                                       \
+    }                                                                                            \
+  }                                                                                              \
+                                                                                                 \
+  /* fps_cuda.cu:9-68; start may be NULL (all zero); dist: scratch [n] */                        \
+  void oracle_fps_##SUFFIX(const T *src, const int64_t *ptr, const int64_t *out_ptr,             \
+                           const int64_t *start, int64_t num_segments, int64_t dim, int policy,  \
+                           T *dist, int64_t *out) {                                              \
+    (void)policy;                                                                                \
+    _Pragma("omp parallel for schedule(dynamic, 1)")                                             \
+    for (int64_t b = 0; b < num_segments; b++) {                                                 \
+      const int64_t lo = ptr[b], hi = ptr[b + 1];                                                \
+      if (hi <= lo || out_ptr[b + 1] <= out_ptr[b])                                              \
+        continue;                                                                                \
+      for (int64_t p = lo; p < hi; p++)                                                          \
+        dist[p] = INIT_FPS;                                                                      \
+      out[out_ptr[b]] = lo + (start ? start[b] : 0);                                             \
+      for (int64_t m = out_ptr[b] + 1; m < out_ptr[b + 1]; m++) {                                \
+        const int64_t old = out[m - 1];                                                          \
+        T best = (T)-1;                                                                          \
+        int64_t best_idx = 0;                                                                    \
+        for (int64_t p = lo; p < hi; p++) {                                                      \
+          T dd = DIST(src + old * dim, src + p * dim, dim, policy);                              \
+          /* min() of the CUDA math library: a NaN operand is ignored */                         \
+          dd = (dist[p] != dist[p]) ? dd : ((dd != dd) ? dist[p] : (dd < dist[p] ? dd : dist[p])); \
+          dist[p] = dd;                                                                          \
+          if (dd > best || (dd == best && dd > (T)-1 && tie_before(p, best_idx, lo, 256))) {     \
+            best = dd;                                                                           \
+            best_idx = p;                                                                        \
+          }                                                                                      \
+        }                                                                                        \
+        out[m] = best_idx;                                                                       \
+      }                                                                                          \
+    }                                                                                            \
+  }
+
+#define DIST_F64(a, b, dim, policy) sqd_f64(a, b, dim)
+DEFINE_NEAREST_FPS(float, f32, sqd_policy_f32, (policy ? r16(1e38f, policy) : 1e38f),
+                   (policy ? r16(5e4f, policy) : 5e4f))
+DEFINE_NEAREST_FPS(double, f64, DIST_F64, 1e38, 5e4)

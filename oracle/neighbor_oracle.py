@@ -33,6 +33,13 @@ def lib() -> ctypes.CDLL:
             f = getattr(_lib, f"oracle_radius_{sfx}")
             f.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, p]
             f.restype = i64
+        for sfx in ("f32", "f64"):
+            f = getattr(_lib, f"oracle_nearest_{sfx}")
+            f.argtypes = [p, p, p, p, i64, i64, i64, i32, p]
+            f.restype = None
+            f = getattr(_lib, f"oracle_fps_{sfx}")
+            f.argtypes = [p, p, p, p, i64, i64, i32, p, p]
+            f.restype = None
         _lib.oracle_knn_r16.argtypes = [p, p, p, p, i64, i64, i64, i64, i64, i32, i32, p, p]
         _lib.oracle_knn_r16.restype = i64
         _lib.oracle_radius_r16.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, p]
@@ -114,6 +121,34 @@ def radius(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32,
     f(*args, None, _ptr(offsets), _ptr(col))
     row = np.repeat(np.arange(m, dtype=np.int64), counts)
     return np.stack([row, col])
+
+
+def nearest(x, y, ptr_x=None, ptr_y=None, round16=None) -> np.ndarray:
+    """out[i] = nearest row of y for row i of x (csrc/cuda/nearest_cuda.cu)."""
+    x, y, ptr_x, ptr_y, sfx = _prep(x, y, ptr_x, ptr_y)
+    out = np.empty(x.shape[0], dtype=np.int64)
+    policy = 0 if round16 is None else _KIND16[round16]
+    assert policy == 0 or x.dtype == np.float32
+    getattr(lib(), f"oracle_nearest_{sfx}")(_ptr(x), _ptr(y), _ptr(ptr_x), _ptr(ptr_y), ptr_x.size - 1,
+                                            x.shape[0], x.shape[1], policy, _ptr(out))
+    return out
+
+
+def fps(src, ptr, out_ptr, start=None, round16=None) -> np.ndarray:
+    """Sample indices for given per-segment output boundaries (csrc/cuda/fps_cuda.cu:9-68)."""
+    src = np.ascontiguousarray(src)
+    assert src.dtype in (np.float32, np.float64) and src.ndim == 2
+    ptr = np.ascontiguousarray(ptr, dtype=np.int64)
+    out_ptr = np.ascontiguousarray(out_ptr, dtype=np.int64)
+    start = None if start is None else np.ascontiguousarray(start, dtype=np.int64)
+    out = np.zeros(int(out_ptr[-1]), dtype=np.int64)
+    dist = np.empty(src.shape[0], dtype=src.dtype)
+    policy = 0 if round16 is None else _KIND16[round16]
+    assert policy == 0 or src.dtype == np.float32
+    sfx = "f32" if src.dtype == np.float32 else "f64"
+    getattr(lib(), f"oracle_fps_{sfx}")(_ptr(src), _ptr(ptr), _ptr(out_ptr), _ptr(start), ptr.size - 1,
+                                        src.shape[1], policy, _ptr(dist), _ptr(out))
+    return out
 
 
 # ---- the Python-level functions of the reference, restated over the oracle ----

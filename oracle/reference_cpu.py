@@ -38,3 +38,8 @@ def radius(x, y, ptr_x, ptr_y, r, max_num_neighbors, num_workers=1, ignore_same_
     load()
     return torch.ops.ref_cluster.radius_cpu(x, y, ptr_x, ptr_y, r, max_num_neighbors,
                                             num_workers, ignore_same_index)
+
+
+def fps(src, ptr, ratio, random_start=False):
+    load()
+    return torch.ops.ref_cluster.fps_cpu(src, ptr, ratio, random_start)

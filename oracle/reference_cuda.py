@@ -37,3 +37,13 @@ def knn(x, y, ptr_x, ptr_y, k, cosine=False):
 def radius(x, y, ptr_x, ptr_y, r, max_num_neighbors, ignore_same_index=False):
     load()
     return torch.ops.ref_cluster_cuda.radius_cuda(x, y, ptr_x, ptr_y, r, max_num_neighbors, ignore_same_index)
+
+
+def nearest(x, y, ptr_x, ptr_y):
+    load()
+    return torch.ops.ref_cluster_cuda.nearest_cuda(x, y, ptr_x, ptr_y)
+
+
+def fps(src, ptr, ratio, random_start=False):
+    load()
+    return torch.ops.ref_cluster_cuda.fps_cuda(src, ptr, ratio, random_start)

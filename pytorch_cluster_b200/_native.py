@@ -62,6 +62,14 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_radius_workspace_bytes.restype = sz
     lib.b200c_radius_count.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, sz, p]
     lib.b200c_radius_fill.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, i64, p, p, sz, p]
+    lib.b200c_nearest_workspace_bytes.argtypes = [i64, i64, i64, i32]
+    lib.b200c_nearest_workspace_bytes.restype = sz
+    lib.b200c_nearest.argtypes = [p, p, p, p, i64, i64, i64, i64, i32, p, p, sz, p]
+    lib.b200c_nearest.restype = i32
+    lib.b200c_fps_workspace_bytes.argtypes = [i64, i64, i32]
+    lib.b200c_fps_workspace_bytes.restype = sz
+    lib.b200c_fps.argtypes = [p, p, p, p, i64, i64, i64, i32, p, p, sz, p]
+    lib.b200c_fps.restype = i32
     for name in ("b200c_segment_ptr", "b200c_exclusive_scan", "b200c_exclusive_scan_static", "b200c_knn", "b200c_knn_compact", "b200c_knn_graph_tail_count", "b200c_knn_graph_tail_write",
                  "b200c_radius_count", "b200c_radius_fill"):
         getattr(lib, name).restype = i32

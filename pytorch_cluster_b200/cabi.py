@@ -108,3 +108,29 @@ def radius(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_in
                                         _p(offsets), total, _p(out), _p(ws) if nbytes else None, nbytes,
                                         _stream()))
     return out
+
+
+def nearest(x, y, ptr_x=None, ptr_y=None):
+    """-> int64 [n]: for each row of x the nearest row of y of the same segment (b200c_nearest)."""
+    lib = _native.cabi()
+    n, m, dim = x.shape[0], y.shape[0], x.shape[1]
+    nseg = 1 if ptr_x is None else ptr_x.numel() - 1
+    out = torch.empty(n, dtype=torch.long, device=x.device)
+    nbytes = lib.b200c_nearest_workspace_bytes(n, m, dim, _dtype(x))
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+    _native.check(lib.b200c_nearest(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, _dtype(x), _p(out),
+                                    _p(ws) if nbytes else None, nbytes, _stream()))
+    return out
+
+
+def fps(src, ptr, out_ptr, start=None):
+    """-> int64 [out_ptr[-1]]: farthest point samples per segment (b200c_fps)."""
+    lib = _native.cabi()
+    n, dim = src.shape[0], src.shape[1]
+    total = int(out_ptr[-1].item())
+    out = torch.empty(total, dtype=torch.long, device=src.device)
+    nbytes = lib.b200c_fps_workspace_bytes(n, dim, _dtype(src))
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=src.device)
+    _native.check(lib.b200c_fps(_p(src), _p(ptr), _p(out_ptr), _p(start), ptr.numel() - 1, n, dim, _dtype(src),
+                                _p(out), _p(ws), nbytes, _stream()))
+    return out

@@ -231,3 +231,38 @@ extern "C" int b200c_radius_fill(const void *x, const void *y, const int64_t *pt
                        ignore_same_index, dtype, (int32_t *)counts, offsets, edge_index,
                        edge_index + num_edges, true, workspace, workspace_bytes, (cudaStream_t)stream);
 }
+
+// ---- nearest ------------------------------------------------------------------------------------------
+
+extern "C" size_t b200c_nearest_workspace_bytes(int64_t n, int64_t m, int64_t dim, int dtype) {
+  return n >= 0 && m >= 0 && dim >= 1 ? widen_bytes(n, m, dim, dtype) : 0;
+}
+
+extern "C" int b200c_nearest(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                             int64_t num_segments, int64_t n, int64_t m, int64_t dim, int dtype, int64_t *out,
+                             void *workspace, size_t workspace_bytes, b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int st = check_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, dtype);
+  if (st != B200C_OK) return st;
+  B200C_CHECK_ARG(out != nullptr || n == 0, "null output pointer");
+  B200C_CHECK_ARG(dim <= 0x7fffffffLL / 4, "Input mismatch");
+  if ((st = check_device()) != B200C_OK) return st;
+  if (n == 0) return B200C_OK;
+  if (is16(dtype)) {
+    const size_t need = widen_bytes(n, m, dim, dtype);
+    if (workspace == nullptr || workspace_bytes < need) {
+      set_error("nearest workspace too small for 16-bit inputs: %zu < %zu", workspace_bytes, need);
+      return B200C_ERR_WORKSPACE;
+    }
+    if ((st = widen_inputs(x, y, n, m, dim, dtype, workspace, true, stream)) != B200C_OK) return st;
+  }
+  // the kernel's "points" are y, its "queries" the rows of x
+  KnnArgs a{y, x, ptr_y, ptr_x, (int)num_segments, m, n, (int)dim, 1, 0, nullptr, nullptr,
+            nullptr, out, nullptr, nullptr, stream};
+  switch (dtype) {
+    case B200C_F32: return launch_nearest_generic_f32(a);
+    case B200C_F64: return launch_nearest_generic_f64(a);
+    case B200C_F16: return launch_nearest_generic_f16(a);
+    default: return launch_nearest_generic_bf16(a);
+  }
+}

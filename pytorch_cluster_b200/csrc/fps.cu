@@ -1,0 +1,201 @@
+// Farthest point sampling — replaces fps_kernel + the launch in fps_cuda
+// (csrc/cuda/fps_cuda.cu:9-68, 70-112).
+//
+// The algorithm is sequential per segment: sample m is the point whose distance to the samples
+// 0..m-1 is largest, so every sample costs one pass over the segment's running minimum distances
+// plus an arg-max reduction, and the reduction's latency bounds the step.  One CTA of 1024
+// threads owns a segment.  The reference re-reads the coordinates and the running distances from
+// global memory in every step; here both live in shared memory for the whole call when the
+// segment fits (up to ~14 000 three-dimensional fp32 points in 200 KB; one plane per feature, so
+// lane-strided reads are conflict free), and only larger segments fall back to global memory / L2
+// with the running distances in the caller's workspace.  A step is: 8 points per thread at 8192
+// points, a shuffle reduction per warp, one __syncthreads, and a second shuffle reduction that
+// every warp repeats on the 32 partial results (double buffered, so one barrier per step).
+//
+// Semantics kept (fps_cuda.cu:32-66): running distance starts at 5e4 and is min(previous, new)
+// with fmin semantics; new = sum over features of (old_d - p_d)^2 accumulated in order (fused for
+// float / double, every operation rounded for the 16-bit types); a candidate must be > -1 (NaN
+// never is; none: index 0); among equal maxima the reference's 256-thread stride and "keep the
+// lower thread on ties" reduction pick the smallest ((index - segment start) mod 256, index).
+#include "common.cuh"
+#include "launchers.h"
+
+namespace b200c {
+
+constexpr int FPS_THREADS = 1024;
+constexpr int FPS_REF_STRIDE = 256;  // THREADS of the reference kernel: defines its tie order
+constexpr size_t FPS_SMEM_BUDGET = 200 * 1024;
+
+template <typename T>
+__device__ __forceinline__ bool fps_better(T d, int64_t i, T bd, int64_t bi, int64_t seg_lo) {
+  if (d > bd) return true;
+  if (!(d == bd)) return false;
+  const int64_t a = (i - seg_lo) & (FPS_REF_STRIDE - 1), b = (bi - seg_lo) & (FPS_REF_STRIDE - 1);
+  return a < b || (a == b && i < bi);
+}
+
+template <typename T>
+__device__ __forceinline__ T fmin_t(T a, T b) {
+  if constexpr (sizeof(T) == 4)
+    return fminf(a, b);
+  else
+    return fmin(a, b);
+}
+
+template <typename T, int RND>
+__global__ void __launch_bounds__(FPS_THREADS)
+fps_kernel(const T *__restrict__ src, const int64_t *__restrict__ ptr, const int64_t *__restrict__ out_ptr,
+           const int64_t *__restrict__ start, int dim, T *__restrict__ dist_global, int64_t *__restrict__ out,
+           int64_t chip_capacity) {
+  extern __shared__ __align__(16) unsigned char smem_fps[];
+  __shared__ T part_d[2][32];
+  __shared__ int64_t part_i[2][32];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = blockIdx.x;
+  const int64_t seg_lo = ptr[b], seg_hi = ptr[b + 1];
+  const int64_t npts = seg_hi - seg_lo;
+  const int64_t o_lo = out_ptr[b], o_hi = out_ptr[b + 1];
+  if (npts <= 0 || o_hi <= o_lo) return;
+
+  // where coordinates and running distances live
+  const bool on_chip = npts <= chip_capacity;
+  const T *coords;
+  int64_t pstride, dstride;
+  T *dist;
+  if (on_chip) {
+    const int64_t plane = (npts + 3) / 4 * 4;
+    T *planes = reinterpret_cast<T *>(smem_fps);
+    dist = planes + (int64_t)dim * plane;
+    for (int64_t f = tid; f < npts * dim; f += FPS_THREADS) {
+      const int64_t p = f / dim;
+      const int d = (int)(f - p * dim);
+      planes[d * plane + p] = src[seg_lo * dim + f];
+    }
+    coords = planes;
+    pstride = 1;
+    dstride = plane;
+  } else {
+    coords = src + seg_lo * dim;
+    pstride = dim;
+    dstride = 1;
+    dist = dist_global + seg_lo;
+  }
+  const T init = rnd16<RND>((T)5e4);
+  for (int64_t p = tid; p < npts; p += FPS_THREADS) dist[p] = init;
+
+  int64_t old = seg_lo + (start != nullptr ? start[b] : 0);
+  if (tid == 0) out[o_lo] = old;
+  __syncthreads();
+
+  for (int64_t m = o_lo + 1; m < o_hi; ++m) {
+    const int buf = (int)(m & 1);
+    const T *q = coords + (old - seg_lo) * pstride;
+    T best = (T)-1;
+    int64_t best_idx = 0;
+    for (int64_t p = tid; p < npts; p += FPS_THREADS) {
+      const T *c = coords + p * pstride;
+      T dd = (T)0;
+      for (int d = 0; d < dim; ++d) dd = sq_accumulate<RND>(q[d * dstride], c[d * dstride], dd);
+      dd = fmin_t(dist[p], dd);
+      dist[p] = dd;
+      if (fps_better(dd, seg_lo + p, best, best_idx, seg_lo)) {
+        best = dd;
+        best_idx = seg_lo + p;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const T od = __shfl_xor_sync(FULL_MASK, best, o);
+      const int64_t oi = __shfl_xor_sync(FULL_MASK, best_idx, o);
+      if (fps_better(od, oi, best, best_idx, seg_lo)) {
+        best = od;
+        best_idx = oi;
+      }
+    }
+    if (lane == 0) {
+      part_d[buf][warp] = best;
+      part_i[buf][warp] = best_idx;
+    }
+    __syncthreads();
+    best = part_d[buf][lane];
+    best_idx = part_i[buf][lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const T od = __shfl_xor_sync(FULL_MASK, best, o);
+      const int64_t oi = __shfl_xor_sync(FULL_MASK, best_idx, o);
+      if (fps_better(od, oi, best, best_idx, seg_lo)) {
+        best = od;
+        best_idx = oi;
+      }
+    }
+    // no candidate above -1 anywhere (all distances NaN): the reference's untouched index 0
+    old = best > (T)-1 ? best_idx : 0;
+    if (tid == 0) out[m] = old;
+  }
+}
+
+template <typename T, int RND>
+static int launch_fps_t(const void *src, const int64_t *ptr, const int64_t *out_ptr, const int64_t *start,
+                        int64_t num_segments, int dim, void *dist, int64_t *out, cudaStream_t stream) {
+  auto kern = fps_kernel<T, RND>;
+  static bool configured = false;
+  if (!configured) {
+    B200C_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FPS_SMEM_BUDGET));
+    configured = true;
+  }
+  // points of (dim + 1) values each, planes padded to 4 elements
+  const int64_t capacity = (int64_t)(FPS_SMEM_BUDGET / sizeof(T) - 4 * (size_t)dim) / (dim + 1);
+  kern<<<(unsigned)num_segments, FPS_THREADS, FPS_SMEM_BUDGET, stream>>>(
+      (const T *)src, ptr, out_ptr, start, dim, (T *)dist, out, capacity > 0 ? capacity : 0);
+  B200C_LAUNCH_CHECK("fps_kernel");
+  return B200C_OK;
+}
+
+}  // namespace b200c
+
+using namespace b200c;
+
+static size_t fps_align256(size_t v) { return (v + 255) / 256 * 256; }
+
+extern "C" size_t b200c_fps_workspace_bytes(int64_t n, int64_t dim, int dtype) {
+  if (n < 0 || dim < 1) return 0;
+  const bool h = dtype == B200C_F16 || dtype == B200C_BF16;
+  const size_t elem = dtype == B200C_F64 ? 8 : 4;
+  return fps_align256((size_t)n * elem) + (h ? fps_align256((size_t)n * dim * 4) : 0);
+}
+
+extern "C" int b200c_fps(const void *src, const int64_t *ptr, const int64_t *out_ptr, const int64_t *start,
+                         int64_t num_segments, int64_t n, int64_t dim, int dtype, int64_t *out, void *workspace,
+                         size_t workspace_bytes, b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  B200C_CHECK_ARG(n >= 0 && dim >= 1 && dim <= 0x7fffffffLL / 4, "Input mismatch");
+  B200C_CHECK_ARG(num_segments >= 0 && num_segments <= 0x7fffffffLL, "Input mismatch");
+  B200C_CHECK_ARG(dtype >= B200C_F32 && dtype <= B200C_BF16, "unsupported dtype");
+  if (num_segments == 0 || n == 0) return B200C_OK;
+  B200C_CHECK_ARG(src && ptr && out_ptr && out, "null pointer");
+  int dev = 0, major = 0;
+  B200C_CUDA(cudaGetDevice(&dev));
+  B200C_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10) {
+    set_error("device %d has compute capability %d.x; this library is built for sm_100a only", dev, major);
+    return B200C_ERR_DEVICE;
+  }
+  const size_t need = b200c_fps_workspace_bytes(n, dim, dtype);
+  if (workspace == nullptr || workspace_bytes < need) {
+    set_error("fps workspace too small: %zu < %zu", workspace_bytes, need);
+    return B200C_ERR_WORKSPACE;
+  }
+  void *dist = workspace;
+  if (dtype == B200C_F16 || dtype == B200C_BF16) {
+    float *wide = (float *)((char *)workspace + fps_align256((size_t)n * 4));
+    int st = launch_widen16(src, n * dim, dtype, wide, stream);
+    if (st != B200C_OK) return st;
+    return dtype == B200C_F16
+               ? launch_fps_t<float, 1>(wide, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream)
+               : launch_fps_t<float, 2>(wide, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream);
+  }
+  return dtype == B200C_F32
+             ? launch_fps_t<float, 0>(src, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream)
+             : launch_fps_t<double, 0>(src, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream);
+}

@@ -17,7 +17,7 @@
 
 namespace b200c {
 
-enum GenMode { GEN_KNN = 0, GEN_RADIUS_COUNT = 1, GEN_RADIUS_FILL = 2 };
+enum GenMode { GEN_KNN = 0, GEN_RADIUS_COUNT = 1, GEN_RADIUS_FILL = 2, GEN_NEAREST = 3 };
 
 template <typename T>
 struct GenD {
@@ -80,7 +80,24 @@ __device__ __forceinline__ T fma_rn(T a, T b, T c) {
     return __fma_rn(a, b, c);
 }
 
+// The reference's nearest kernel (csrc/cuda/nearest_cuda.cu:31-60) strides 1024 threads over the
+// points of a segment; a thread keeps the first strict minimum of its stride and the tree
+// reduction keeps the lower thread on equal distances.  Its winner among equal minima is
+// therefore the point with the smallest ((index - segment start) mod 1024, index).
+constexpr int NEAREST_STRIDE = 1024;
+
+template <typename T>
+__device__ __forceinline__ bool nearest_better(T d, int64_t i, T bd, int64_t bi, int64_t seg_lo) {
+  if (d < bd) return true;
+  if (!(d == bd)) return false;
+  const int64_t a = (i - seg_lo) & (NEAREST_STRIDE - 1), b = (bi - seg_lo) & (NEAREST_STRIDE - 1);
+  return a < b || (a == b && i < bi);
+}
+
 // MODE GEN_KNN:          out_row/out_col padded [m*k], counts, num_valid; `bound0` unused.
+// MODE GEN_NEAREST:      out_col[q] = the nearest point of q's segment (0 when no point is closer
+//                        than 1e38, as in the reference); the kernel's "x" are the points searched
+//                        (the reference's y) and its "y" the rows assigned (the reference's x).
 // MODE GEN_RADIUS_COUNT: counts.   MODE GEN_RADIUS_FILL: offsets -> out_row/out_col.
 // COSINE only with GEN_KNN; norms_x / norms_y hold |row| as the reference computes it.
 // RND: rounding of every operation result for 16-bit inputs widened to float (see rnd16).
@@ -132,7 +149,7 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
     int limit[QW];
 #pragma unroll
     for (int qi = 0; qi < QW; ++qi) {
-      bound[qi] = MODE == GEN_KNN ? rnd16<RND>((T)1e10) : r2;
+      bound[qi] = MODE == GEN_KNN ? rnd16<RND>((T)1e10) : (MODE == GEN_NEAREST ? rnd16<RND>((T)1e38) : r2);
       ny[qi] = (T)1;
       cnt[qi] = 0;
       base[qi] = 0;
@@ -165,6 +182,15 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
     if (nsteps > 0) {
       const int npts0 = nx < G::XC ? (int)nx : G::XC;
       stage_block<T>(stage, x, y, x_lo, npts0, 0, dim, q_lo, q_hi, tid);
+    }
+
+    // nearest: every lane's best so far per query; `bound` holds the distance, admissible only below 1e38
+    int64_t near_idx[QW];
+    bool near_found[QW];
+#pragma unroll
+    for (int qi = 0; qi < QW; ++qi) {
+      near_idx[qi] = 0;
+      near_found[qi] = false;
     }
 
     T acc[NSUB][QW][R];
@@ -254,6 +280,18 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
               if constexpr (MODE == GEN_RADIUS_COUNT) {
 #pragma unroll
                 for (int i = 0; i < NR; ++i) cnt[qi] += dist[i] < bound[qi] ? 1 : 0;
+              } else if constexpr (MODE == GEN_NEAREST) {
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                  // strict "<" against the initial 1e38 (nearest_cuda.cu:31, 41), the full order after
+                  const bool take = near_found[qi] ? nearest_better(dist[i], idx0 + 32 * i, bound[qi], near_idx[qi], x_lo)
+                                                   : dist[i] < bound[qi];
+                  if (take) {
+                    bound[qi] = dist[i];
+                    near_idx[qi] = idx0 + 32 * i;
+                    near_found[qi] = true;
+                  }
+                }
               } else {
                 const T dmin = min_of(dist);
                 if (__any_sync(FULL_MASK, dmin < bound[qi])) {
@@ -300,6 +338,22 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
             counts[q] = valid;
             my_valid += valid;
           }
+        } else if constexpr (MODE == GEN_NEAREST) {
+          T bd = bound[qi];
+          int64_t bi = near_idx[qi];
+          bool bf = near_found[qi];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            const T od = __shfl_xor_sync(FULL_MASK, bd, o);
+            const int64_t oi = __shfl_xor_sync(FULL_MASK, bi, o);
+            const bool of = __shfl_xor_sync(FULL_MASK, (int)bf, o) != 0;
+            if (of && (!bf || nearest_better(od, oi, bd, bi, x_lo))) {
+              bd = od;
+              bi = oi;
+              bf = true;
+            }
+          }
+          if (lane == 0) out_col[q] = bf ? bi : 0;
         } else if constexpr (MODE == GEN_RADIUS_COUNT) {
           int tot = cnt[qi];
 #pragma unroll

@@ -7,4 +7,5 @@ int launch_radius_generic_bf16(const RadiusArgs &a, bool fill) { return launch_r
 int launch_row_norms_bf16(const void *a, int64_t rows, int dim, void *out, cudaStream_t s) {
   return launch_row_norms_t<float, 2>(a, rows, dim, out, s);
 }
+int launch_nearest_generic_bf16(const KnnArgs &a) { return launch_nearest_generic<float, 2>(a); }
 }  // namespace b200c

@@ -7,4 +7,5 @@ int launch_radius_generic_f16(const RadiusArgs &a, bool fill) { return launch_ra
 int launch_row_norms_f16(const void *a, int64_t rows, int dim, void *out, cudaStream_t s) {
   return launch_row_norms_t<float, 1>(a, rows, dim, out, s);
 }
+int launch_nearest_generic_f16(const KnnArgs &a) { return launch_nearest_generic<float, 1>(a); }
 }  // namespace b200c

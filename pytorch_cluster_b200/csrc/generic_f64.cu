@@ -5,4 +5,5 @@ int launch_radius_generic_f64(const RadiusArgs &a, bool fill) { return launch_ra
 int launch_row_norms_f64(const void *a, int64_t rows, int dim, void *out, cudaStream_t s) {
   return launch_row_norms_t<double>(a, rows, dim, out, s);
 }
+int launch_nearest_generic_f64(const KnnArgs &a) { return launch_nearest_generic<double, 0>(a); }
 }  // namespace b200c

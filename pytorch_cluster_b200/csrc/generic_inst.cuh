@@ -60,6 +60,12 @@ static int launch_radius_generic(const RadiusArgs &a, bool fill) {
               : launch_generic_one<T, GEN_RADIUS_COUNT, 0, false, RND>(nullptr, &a);
 }
 
+// nearest: a.x / a.ptr_x describe the points searched, a.y / a.ptr_y the rows assigned; a.out_col [a.m]
+template <typename T, int RND = 0>
+static int launch_nearest_generic(const KnnArgs &a) {
+  return launch_generic_one<T, GEN_NEAREST, 0, false, RND>(&a, nullptr);
+}
+
 template <typename T, int RND = 0>
 static int launch_row_norms_t(const void *a, int64_t rows, int dim, void *out, cudaStream_t stream) {
   if (rows == 0) return B200C_OK;

@@ -211,10 +211,80 @@ torch::Tensor segment_ptr(torch::Tensor batch, int64_t num_segments) {
   return ptr;
 }
 
+// nearest: torch_cluster::nearest of csrc/nearest.cpp:22-36; host side of csrc/cuda/nearest_cuda.cu:63-88.
+torch::Tensor nearest(torch::Tensor x, torch::Tensor y, torch::Tensor ptr_x, torch::Tensor ptr_y) {
+  CHECK_CUDA(x);
+  CHECK_CUDA(y);
+  CHECK_CUDA(ptr_x);
+  CHECK_CUDA(ptr_y);
+  c10::cuda::CUDAGuard guard(x.device());
+  x = x.view({x.size(0), -1}).contiguous();
+  y = y.view({y.size(0), -1}).contiguous();
+  CHECK_INPUT(x.size(1) == y.size(1));
+  CHECK_INPUT(x.scalar_type() == y.scalar_type());
+  CHECK_INPUT(ptr_x.dim() == 1 && ptr_y.dim() == 1 && ptr_x.numel() == ptr_y.numel() && ptr_x.numel() >= 2);
+  TORCH_CHECK(ptr_x.scalar_type() == at::kLong && ptr_y.scalar_type() == at::kLong,
+              "ptr_x and ptr_y must be int64 tensors");
+  ptr_x = ptr_x.contiguous();
+  ptr_y = ptr_y.contiguous();
+  const int dtype = dtype_code(x);
+  const int64_t n = x.size(0), m = y.size(0), dim = x.size(1);
+  auto out = torch::empty({n}, ptr_x.options());
+  if (n == 0) return out;
+  const size_t ws_bytes = b200c_nearest_workspace_bytes(n, m, dim, dtype);
+  auto ws = torch::empty({(int64_t)ws_bytes}, x.options().dtype(torch::kByte));
+  check_status(b200c_nearest(x.data_ptr(), y.data_ptr(), ptr_x.data_ptr<int64_t>(), ptr_y.data_ptr<int64_t>(),
+                             ptr_x.numel() - 1, n, m, dim, dtype, out.data_ptr<int64_t>(),
+                             ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                             at::cuda::getCurrentCUDAStream().stream()));
+  return out;
+}
+
+// fps: torch_cluster::fps of csrc/fps.cpp:22-36; host side of csrc/cuda/fps_cuda.cu:70-112.  The
+// per-segment sample counts are formed exactly as there (degree in ratio's dtype, times ratio,
+// ceil, cumulative sum); one host read gives the output size.
+torch::Tensor fps(torch::Tensor src, torch::Tensor ptr, torch::Tensor ratio, bool random_start) {
+  CHECK_CUDA(src);
+  CHECK_CUDA(ptr);
+  CHECK_CUDA(ratio);
+  CHECK_INPUT(ptr.dim() == 1);
+  TORCH_CHECK(ptr.scalar_type() == at::kLong, "ptr must be an int64 tensor");
+  c10::cuda::CUDAGuard guard(src.device());
+  src = src.view({src.size(0), -1}).contiguous();
+  ptr = ptr.contiguous();
+  const int64_t batch_size = ptr.numel() - 1;
+  const int dtype = dtype_code(src);
+
+  auto deg = ptr.narrow(0, 1, batch_size) - ptr.narrow(0, 0, batch_size);
+  auto out_ptr = deg.toType(ratio.scalar_type()) * ratio;
+  out_ptr = out_ptr.ceil().toType(torch::kLong).cumsum(0);
+  out_ptr = torch::cat({torch::zeros({1}, ptr.options()), out_ptr}, 0).contiguous();
+
+  torch::Tensor start;
+  const int64_t *start_ptr = nullptr;
+  if (random_start) {
+    start = torch::rand(batch_size, src.options());
+    start = (start * deg.toType(ratio.scalar_type())).toType(torch::kLong).contiguous();
+    start_ptr = start.data_ptr<int64_t>();
+  }
+  const int64_t total = batch_size > 0 ? out_ptr[-1].item<int64_t>() : 0;  // the one host sync
+  auto out = torch::empty({total}, ptr.options());
+  if (total == 0) return out;
+  const int64_t n = src.size(0), dim = src.size(1);
+  const size_t ws_bytes = b200c_fps_workspace_bytes(n, dim, dtype);
+  auto ws = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kByte));
+  check_status(b200c_fps(src.data_ptr(), ptr.data_ptr<int64_t>(), out_ptr.data_ptr<int64_t>(), start_ptr,
+                         batch_size, n, dim, dtype, out.data_ptr<int64_t>(), ws.data_ptr(), ws_bytes,
+                         at::cuda::getCurrentCUDAStream().stream()));
+  return out;
+}
+
 }  // namespace
 
 static auto registry = torch::RegisterOperators()
                            .op("torch_cluster::knn", &knn)
                            .op("torch_cluster::radius", &radius)
                            .op("torch_cluster::segment_ptr", &segment_ptr)
-                           .op("torch_cluster::knn_graph_edges", &knn_graph_edges);
+                           .op("torch_cluster::knn_graph_edges", &knn_graph_edges)
+                           .op("torch_cluster::nearest", &nearest)
+                           .op("torch_cluster::fps", &fps);

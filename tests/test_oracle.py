@@ -241,3 +241,74 @@ def test_oracle_16bit_reference_known_answers():
         assert set(map(tuple, e.T.tolist())) == {(0, 0), (0, 1), (0, 2), (0, 3), (1, 1), (1, 2), (1, 5), (1, 6)}
         e = orc.radius(x, yr, 2, px, py, max_num_neighbors=4, round16=kind)
         assert set(map(tuple, e.T.tolist())) == {(0, 0), (0, 1), (0, 2), (0, 3), (1, 5), (1, 6)}
+
+
+# ---- nearest and farthest point sampling ------------------------------------------------------------
+
+SQ8 = [[-1, -1], [-1, 1], [1, 1], [1, -1], [-2, -2], [-2, 2], [2, 2], [2, -2]]
+
+
+def _fps_out_ptr(ptr, ratio, dtype=torch.float32):
+    """Per-segment sample boundaries as csrc/cuda/fps_cuda.cu:83-86 forms them."""
+    ptr = torch.as_tensor(ptr)
+    deg = ptr[1:] - ptr[:-1]
+    cnt = (deg.to(dtype) * torch.as_tensor(ratio, dtype=dtype)).ceil().long().cumsum(0)
+    return torch.cat([torch.zeros(1, dtype=torch.long), cnt]).numpy()
+
+
+def test_oracle_nearest_known_answers():
+    """test/test_nearest.py:11-36."""
+    x = np.array(SQ8, dtype=np.float32)
+    y = np.array([[-1, 0], [1, 0], [-2, 0], [2, 0]], dtype=np.float32)
+    out = orc.nearest(x, y, np.array([0, 4, 8]), np.array([0, 2, 4]))
+    assert out.tolist() == [0, 0, 1, 1, 2, 2, 3, 3]
+    assert orc.nearest(x, y).tolist() == [0, 0, 1, 1, 2, 2, 3, 3]
+    assert orc.nearest(x.astype(np.float64), y.astype(np.float64)).tolist() == [0, 0, 1, 1, 2, 2, 3, 3]
+    assert orc.nearest(x, y, round16="f16").tolist() == [0, 0, 1, 1, 2, 2, 3, 3]
+
+
+def test_oracle_nearest_tie_order_follows_the_reference_reduction():
+    """Equal minima: the reference's 1024-thread stride prefers the smaller (offset mod 1024)."""
+    y = np.full((3000, 2), 5.0, dtype=np.float32)
+    y[[2, 1025, 2050], :] = 0.0          # three points at distance 0 from the query
+    x = np.zeros((1, 2), dtype=np.float32)
+    assert orc.nearest(x, y).tolist() == [1025]      # offsets mod 1024: 2, 1, 2
+    y[1025, :] = 5.0
+    assert orc.nearest(x, y).tolist() == [2]         # (2, 2) before (2, 2050)
+    # nothing below 1e38: index 0 as the kernel leaves it
+    y[:] = np.inf
+    assert orc.nearest(x, y).tolist() == [0]
+
+
+def test_oracle_fps_known_answers():
+    """test/test_fps.py:16-62 with random_start=False."""
+    x = np.array(SQ8, dtype=np.float32)
+    assert orc.fps(x, [0, 4, 8], _fps_out_ptr([0, 4, 8], 0.5)).tolist() == [0, 2, 4, 6]
+    assert orc.fps(x, [0, 4, 8], _fps_out_ptr([0, 4, 8], [0.5, 0.5])).tolist() == [0, 2, 4, 6]
+    assert sorted(orc.fps(x, [0, 8], _fps_out_ptr([0, 8], 0.5)).tolist()) == [0, 5, 6, 7]
+    assert sorted(orc.fps(x.astype(np.float64), [0, 8], _fps_out_ptr([0, 8], 0.5)).tolist()) == [0, 5, 6, 7]
+    assert sorted(orc.fps(x, [0, 8], _fps_out_ptr([0, 8], 0.5), round16="f16").tolist()) == [0, 5, 6, 7]
+
+
+def test_oracle_fps_matches_reference_cpu_path():
+    """csrc/cpu/fps_cpu.cpp on random clouds (no equal distances, so its first-maximum rule and
+    unfused arithmetic pick the same points)."""
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(3 * 700, 3, generator=g)
+    ptr = torch.tensor([0, 700, 1400, 2100])
+    for ratio in (0.5, 0.1):
+        want = refcpu.fps(x, ptr, torch.tensor(ratio), False)
+        got = orc.fps(x.numpy(), ptr.numpy(), _fps_out_ptr(ptr, ratio))
+        assert got.tolist() == want.tolist()
+    xd = x.double()
+    want = refcpu.fps(xd, ptr, torch.tensor(0.25, dtype=torch.float64), False)
+    assert orc.fps(xd.numpy(), ptr.numpy(), _fps_out_ptr(ptr, 0.25, torch.float64)).tolist() == want.tolist()
+
+
+def test_oracle_fps_tie_order_follows_the_reference_reduction():
+    """All points beyond the 5e4 cap tie; the reference's 256-thread stride prefers the smaller
+    (offset mod 256), then the lower index."""
+    x = np.zeros((600, 1), dtype=np.float32)
+    x[[3, 258, 515], 0] = 1000.0         # squared distance 1e6 -> clamped to 5e4, three-way tie
+    out = orc.fps(x, [0, 600], np.array([0, 3]))
+    assert out.tolist()[:2] == [0, 258]  # offsets mod 256: 3, 2, 3
