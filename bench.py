@@ -228,6 +228,17 @@ def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank):
                                                              batch_size=64, assemble=False)), world)
             rec["sharded_no_assembly_ms"] = ts
         out[f"radius_graph_64x8192x3_r0.05_max{max_nn}"] = rec
+
+    # the operators either side of the path: farthest point sampling (25 % of every cloud, first
+    # point first), then assignment of every point to its nearest sample
+    t = ms_of(lambda: pc.fps(xr, br, ratio=0.25, random_start=False, batch_size=64))
+    samples = pc.fps(xr, br, ratio=0.25, random_start=False, batch_size=64)
+    out["fps_64x8192x3_ratio0.25"] = {"api_ms": t, "samples": int(samples.numel()),
+                                      "samples_per_s": samples.numel() / (t * 1e-3)}
+    ys, bs = xr[samples].contiguous(), br[samples].contiguous()
+    t = ms_of(lambda: pc.nearest(xr, ys, br, bs))
+    out["nearest_64x8192_to_2048x3"] = {"api_ms": t, "rows_per_s": xr.shape[0] / (t * 1e-3),
+                                        "fp32_frac": 8.0 * 64 * 8192 * 2048 / (t * 1e-3) / 1e12 / peak_tf}
     return out
 
 

@@ -260,8 +260,8 @@ extern "C" int b200c_nearest(const void *x, const void *y, const int64_t *ptr_x,
   KnnArgs a{y, x, ptr_y, ptr_x, (int)num_segments, m, n, (int)dim, 1, 0, nullptr, nullptr,
             nullptr, out, nullptr, nullptr, stream};
   switch (dtype) {
-    case B200C_F32: return launch_nearest_generic_f32(a);
-    case B200C_F64: return launch_nearest_generic_f64(a);
+    case B200C_F32: return dim <= 8 ? launch_nearest_lowd_f32(a) : launch_nearest_generic_f32(a);
+    case B200C_F64: return dim <= 8 ? launch_nearest_lowd_f64(a) : launch_nearest_generic_f64(a);
     case B200C_F16: return launch_nearest_generic_f16(a);
     default: return launch_nearest_generic_bf16(a);
   }

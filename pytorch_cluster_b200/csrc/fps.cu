@@ -8,9 +8,13 @@
 // global memory in every step; here both live in shared memory for the whole call when the
 // segment fits (up to ~14 000 three-dimensional fp32 points in 200 KB; one plane per feature, so
 // lane-strided reads are conflict free), and only larger segments fall back to global memory / L2
-// with the running distances in the caller's workspace.  A step is: 8 points per thread at 8192
-// points, a shuffle reduction per warp, one __syncthreads, and a second shuffle reduction that
-// every warp repeats on the 32 partial results (double buffered, so one barrier per step).
+// with the running distances in the caller's workspace.  For fp32 points of up to 8 features a
+// segment of up to 8192 (DIM <= 3) or 4096 points additionally keeps its coordinates and running
+// distances in registers (thread t owns points t, t + 1024, ...; shared memory only serves the
+// broadcast of the newest sample's coordinates), candidates travel as 64-bit keys
+// (distance bits << 32 | inverted tie rank) and a step is: 3 broadcast loads, 8 distance updates
+// per thread, two REDUX instructions per warp, one __syncthreads, and the same two REDUX again
+// on the 32 partial keys in every warp (double buffered, so one barrier per step).
 //
 // Semantics kept (fps_cuda.cu:32-66): running distance starts at 5e4 and is min(previous, new)
 // with fmin semantics; new = sum over features of (old_d - p_d)^2 accumulated in order (fused for
@@ -42,8 +46,19 @@ __device__ __forceinline__ T fmin_t(T a, T b) {
     return fmin(a, b);
 }
 
-template <typename T, int RND>
-__global__ void __launch_bounds__(FPS_THREADS)
+// Maximum of 64-bit keys over a warp as two 32-bit REDUX steps: high words first, then the low
+// words of the lanes that hold the maximal high word.
+__device__ __forceinline__ void warp_max_key(uint32_t &hi, uint32_t &lo) {
+  const uint32_t mh = __reduce_max_sync(FULL_MASK, hi);
+  const uint32_t ml = __reduce_max_sync(FULL_MASK, hi == mh ? lo : 0u);
+  hi = mh;
+  lo = ml;
+}
+
+// DIM > 0: compile-time feature count with the register-resident path for segments of up to
+// FPS_THREADS * PT points (fp32 without 16-bit rounding only); DIM == 0: run-time feature count.
+template <typename T, int RND, int DIM, int PT>
+__global__ void __launch_bounds__(FPS_THREADS, 1)
 fps_kernel(const T *__restrict__ src, const int64_t *__restrict__ ptr, const int64_t *__restrict__ out_ptr,
            const int64_t *__restrict__ start, int dim, T *__restrict__ dist_global, int64_t *__restrict__ out,
            int64_t chip_capacity) {
@@ -57,6 +72,64 @@ fps_kernel(const T *__restrict__ src, const int64_t *__restrict__ ptr, const int
   const int64_t npts = seg_hi - seg_lo;
   const int64_t o_lo = out_ptr[b], o_hi = out_ptr[b + 1];
   if (npts <= 0 || o_hi <= o_lo) return;
+
+  if constexpr (DIM > 0 && RND == 0 && sizeof(T) == 4) {
+    if (npts <= (int64_t)FPS_THREADS * PT) {
+      __shared__ uint2 part_key[2][32];
+      const int n = (int)npts;
+      const int plane = (n + 3) / 4 * 4;
+      float *planes = reinterpret_cast<float *>(smem_fps);
+      for (int f = tid; f < n * DIM; f += FPS_THREADS) {
+        const int p = f / DIM, d = f - p * DIM;
+        planes[d * plane + p] = src[seg_lo * DIM + f];
+      }
+      __syncthreads();
+      float c[PT][DIM], dmin[PT];
+      uint32_t inv_tie[PT];  // 0xffffffff - ((offset mod 256) << 24 | offset); 0 marks "no point"
+#pragma unroll
+      for (int j = 0; j < PT; ++j) {
+        const int rel = tid + j * FPS_THREADS;
+        const bool valid = rel < n;
+#pragma unroll
+        for (int d = 0; d < DIM; ++d) c[j][d] = valid ? planes[d * plane + rel] : 0.f;
+        dmin[j] = 5e4f;
+        inv_tie[j] = valid ? 0xffffffffu - ((uint32_t)(rel & (FPS_REF_STRIDE - 1)) << 24 | (uint32_t)rel) : 0u;
+      }
+      int old_rel = (int)(start != nullptr ? start[b] : 0);
+      if (tid == 0) out[o_lo] = seg_lo + old_rel;
+      for (int64_t m = o_lo + 1; m < o_hi; ++m) {
+        const int buf = (int)(m & 1);
+        float q[DIM];
+#pragma unroll
+        for (int d = 0; d < DIM; ++d) q[d] = planes[d * plane + old_rel];
+        uint32_t hi = 0u, lo = 0u;
+#pragma unroll
+        for (int j = 0; j < PT; ++j) {
+          float dd = 0.f;
+#pragma unroll
+          for (int d = 0; d < DIM; ++d) dd = sq_accumulate<0>(q[d], c[j][d], dd);
+          dd = fminf(dmin[j], dd);
+          dmin[j] = dd;
+          // dd >= 0 here (a NaN sum is dropped by fminf), so its bit pattern orders like its value
+          const uint32_t bits = inv_tie[j] != 0u ? __float_as_uint(dd) : 0u;
+          if (bits > hi || (bits == hi && inv_tie[j] > lo)) {
+            hi = bits;
+            lo = inv_tie[j];
+          }
+        }
+        warp_max_key(hi, lo);
+        if (lane == 0) part_key[buf][warp] = make_uint2(hi, lo);
+        __syncthreads();
+        const uint2 pk = part_key[buf][lane];
+        hi = pk.x;
+        lo = pk.y;
+        warp_max_key(hi, lo);
+        old_rel = (int)((0xffffffffu - lo) & 0x00ffffffu);
+        if (tid == 0) out[m] = seg_lo + old_rel;
+      }
+      return;
+    }
+  }
 
   // where coordinates and running distances live
   const bool on_chip = npts <= chip_capacity;
@@ -135,10 +208,10 @@ fps_kernel(const T *__restrict__ src, const int64_t *__restrict__ ptr, const int
   }
 }
 
-template <typename T, int RND>
+template <typename T, int RND, int DIM = 0, int PT = 1>
 static int launch_fps_t(const void *src, const int64_t *ptr, const int64_t *out_ptr, const int64_t *start,
                         int64_t num_segments, int dim, void *dist, int64_t *out, cudaStream_t stream) {
-  auto kern = fps_kernel<T, RND>;
+  auto kern = fps_kernel<T, RND, DIM, PT>;
   static bool configured = false;
   if (!configured) {
     B200C_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FPS_SMEM_BUDGET));
@@ -195,7 +268,17 @@ extern "C" int b200c_fps(const void *src, const int64_t *ptr, const int64_t *out
                ? launch_fps_t<float, 1>(wide, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream)
                : launch_fps_t<float, 2>(wide, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream);
   }
-  return dtype == B200C_F32
-             ? launch_fps_t<float, 0>(src, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream)
-             : launch_fps_t<double, 0>(src, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream);
+  if (dtype == B200C_F64)
+    return launch_fps_t<double, 0>(src, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream);
+  switch (dim) {
+    case 1: return launch_fps_t<float, 0, 1, 8>(src, ptr, out_ptr, start, num_segments, 1, dist, out, stream);
+    case 2: return launch_fps_t<float, 0, 2, 8>(src, ptr, out_ptr, start, num_segments, 2, dist, out, stream);
+    case 3: return launch_fps_t<float, 0, 3, 8>(src, ptr, out_ptr, start, num_segments, 3, dist, out, stream);
+    case 4: return launch_fps_t<float, 0, 4, 4>(src, ptr, out_ptr, start, num_segments, 4, dist, out, stream);
+    case 5: return launch_fps_t<float, 0, 5, 4>(src, ptr, out_ptr, start, num_segments, 5, dist, out, stream);
+    case 6: return launch_fps_t<float, 0, 6, 4>(src, ptr, out_ptr, start, num_segments, 6, dist, out, stream);
+    case 7: return launch_fps_t<float, 0, 7, 4>(src, ptr, out_ptr, start, num_segments, 7, dist, out, stream);
+    case 8: return launch_fps_t<float, 0, 8, 4>(src, ptr, out_ptr, start, num_segments, 8, dist, out, stream);
+  }
+  return launch_fps_t<float, 0>(src, ptr, out_ptr, start, num_segments, (int)dim, dist, out, stream);
 }

@@ -52,6 +52,8 @@ int launch_radius_generic_f16(const RadiusArgs &a, bool fill);
 int launch_radius_generic_bf16(const RadiusArgs &a, bool fill);
 int launch_row_norms_f16(const void *a, int64_t rows, int dim, void *out, cudaStream_t s);
 int launch_row_norms_bf16(const void *a, int64_t rows, int dim, void *out, cudaStream_t s);
+int launch_nearest_lowd_f32(const KnnArgs &a);
+int launch_nearest_lowd_f64(const KnnArgs &a);
 int launch_nearest_generic_f32(const KnnArgs &a);
 int launch_nearest_generic_f64(const KnnArgs &a);
 int launch_nearest_generic_f16(const KnnArgs &a);

@@ -189,6 +189,16 @@ def test_time_beside_reference_kernels():
     xs, ps = xr[: 8 * 8192].contiguous(), _ptr(8, 8192)
     rep["radius_8x8192x3_r0.05_max8192"] = (_ms(lambda: refc.radius(xs, xs, ps, ps, 0.05, 8192, True)),
                                             _ms(lambda: _ours_radius(xs, xs, ps, ps, 0.05, 8192, True)))
+    # nearest: every point of the 64 clouds to the closest of 2048 samples of its cloud; fps: 25 % of
+    # every cloud, first point first
+    from pytorch_cluster_b200 import cabi  # noqa: F401  (loads the operators)
+    ys = torch.cat([xr[c * 8192: c * 8192 + 2048] for c in range(64)]).contiguous()
+    pys = _ptr(64, 2048)
+    rep["nearest_64x8192_to_2048x3"] = (_ms(lambda: refc.nearest(xr, ys, pr, pys)),
+                                        _ms(lambda: torch.ops.torch_cluster.nearest(xr, ys, pr, pys)))
+    ratio = torch.tensor(0.25, device=DEV)
+    rep["fps_64x8192x3_ratio0.25"] = (_ms(lambda: refc.fps(xr, pr, ratio, False), 1),
+                                      _ms(lambda: torch.ops.torch_cluster.fps(xr, pr, ratio, False)))
     out = {k: {"reference_cuda_ms": round(a, 4), "this_library_ms": round(b, 4), "ratio": round(a / b, 2)}
            for k, (a, b) in rep.items()}
     print(json.dumps(out, indent=1))
