@@ -1,23 +1,25 @@
 // Feature-space kNN (fp32, 32 <= D <= 128, D % 8 == 0, k <= 32): tensor-core candidates, exact re-rank.
 //
-// Stage 1, knn_tensor_candidates_kernel — tcgen05 / TMEM.  A CTA owns 128 query rows.  The query
-// tile and, one after the other, 128-point tiles of the queries' segment are laid out in shared
+// Stage 1, knn_tensor_candidates_kernel — tcgen05 / TMEM.  A CTA of 512 threads owns 128 query rows.
+// The query tile and a ring of two 128-point tiles of the queries' segment are laid out in shared
 // memory in the K-major, 128-byte-swizzled operand layout of the 5th-generation tensor cores (rows
 // of 32 tf32 values = 128 bytes, 16-byte chunk c of row r stored at chunk c ^ (r & 7); cp.async, 16
-// bytes per copy, coalesced on the global side and conflict-free on the shared side; the copy of
-// the next tile runs while the current one is read back); one thread issues D / 8
-// `tcgen05.mma.cta_group::1.kind::tf32` instructions (M = 128, N = 128, K = 8) that accumulate
-// S = Q X^T into 128 columns of tensor memory, `tcgen05.commit` signals an mbarrier, and every
-// thread reads back its own query's row with `tcgen05.ld.32x32b`.  From S the approximate distance
-// a = |x|^2 - 2 S + |q|^2 (or 1 - S on pre-normalised rows for cosine) costs one FFMA per pair.
-// The segment is swept twice:
-//   pass A keeps, per query, the minimum of a over each group of consecutive points (at most 64
-//          groups).  The k-th smallest of those minima, T, is an upper bound of the k-th smallest
+// bytes per copy, coalesced on the global side and conflict-free on the shared side).  One thread
+// issues D / 8 `tcgen05.mma.cta_group::1.kind::tf32` instructions (M = 128, N = 128, K = 8) per tile
+// that accumulate S = Q X^T into one of two 128-column accumulators in tensor memory;
+// `tcgen05.commit` signals that accumulator's mbarrier.  The loop is software-pipelined: while the
+// tensor core works on tile s, the threads read back tile s - 1 from the other accumulator with
+// `tcgen05.ld.32x32b` (four threads per query row, 32 columns each) and the copies of tile s + 1
+// are in flight.  From S the approximate distance a = |x|^2 - 2 S + |q|^2 (or 1 - S on
+// pre-normalised rows for cosine) costs one FFMA per pair.  The segment is swept twice:
+//   pass A keeps, per query, the minimum of a over groups of points (at most 64 groups, 16 per
+//          thread).  The k-th smallest of those minima, T, is an upper bound of the k-th smallest
 //          approximate distance: k different points lie at or below it.
-//   pass B records every point with a <= T + 2 E as a candidate of that query (thread-owned list,
-//          no atomics), E being a bound of |a - d_exact| for tf32 operands (each truncated to 10
-//          mantissa bits: |dS| <= 2^-9 |x||q|).  If d_k is the exact k-th distance, then
-//          d_k <= T + E, so every true neighbour (d <= d_k) has a <= T + 2 E: no neighbour is lost.
+//   pass B records every point with a <= T + 2 E as a candidate of that query (two lists per
+//          query, each filled by one thread from the front and by another from the back), E being a bound of |a - d_exact| for
+//          tf32 operands (each truncated to 10 mantissa bits: |dS| <= 2^-9 |x||q|).  If d_k is the
+//          exact k-th distance, then d_k <= T + E, so every true neighbour (d <= d_k) has
+//          a <= T + 2 E: no neighbour is lost.
 // Stage 2, knn_rerank_kernel — one warp per query evaluates its candidates exactly as the
 // reference does (sequential fused multiply-adds over ascending features,
 // csrc/cuda/knn_cuda.cu:9-28, 55-64) and selects the k best by (distance, index) with the
@@ -35,9 +37,12 @@ namespace b200c {
 
 constexpr int TC_M = 128;        // queries per CTA = TMEM lanes
 constexpr int TC_N = 128;        // points per tile = TMEM columns
-constexpr int TC_GMAX = 64;      // group minima kept per query
-constexpr int TC_CAP = 128;      // candidates kept per query
-constexpr int TC_THREADS = 128;
+constexpr int TC_PARTS = 4;      // threads per query row: each reads back 32 of a tile's 128 columns
+constexpr int TC_COLS = TC_N / TC_PARTS;
+constexpr int TC_GH = 16;        // group minima kept per thread: 64 per query
+constexpr int TC_CAP = 128;      // candidates kept per query: two lists of 64, each filled from both ends
+constexpr int TC_THREADS = TC_M * TC_PARTS;
+constexpr int TC_SQX_SLOTS = 3;
 constexpr int TC_SPIN_LIMIT = 1 << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -61,11 +66,33 @@ __device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src
 // Rows [row0, row0 + 128) of src ([*, dim] row-major) into the swizzled operand layout: features
 // [32 a, 32 a + 32) of all rows form "atom" a (128 rows x 128 bytes = 16 KiB); inside an atom the
 // 16-byte chunk c of row r sits at r * 128 + ((c ^ (r & 7)) * 16).  Rows >= row_end are zero.
+// Consecutive threads copy consecutive chunks of a row (coalesced 16-byte loads).  When the
+// number of chunks per row divides the thread count (dim = 32, 64, 128) a thread keeps its chunk
+// and walks down the rows in steps that are multiples of 8, so its swizzle term is constant and
+// the addresses advance by constants; other dims pay an integer division per copy.
 __device__ __forceinline__ void stage_operand(unsigned char *dst, const float *__restrict__ src, int64_t row0,
                                               int64_t row_end, int dim, int tid) {
   const int chunks = dim >> 2;  // 16-byte chunks per row
+  if ((chunks & (chunks - 1)) == 0) {
+    const int ch = tid & (chunks - 1);
+    const int r0 = tid / chunks;            // chunks is a power of two: a shift
+    const int rstep = TC_THREADS / chunks;  // 32, 16 or 8
+    unsigned char *d = dst + (ch >> 3) * 16384 + r0 * 128 + (((ch & 7) ^ (r0 & 7)) << 4);
+    const float *g = src + (row0 + r0) * dim + ch * 4;
+    int64_t row = row0 + r0;
+    for (int r = r0; r < TC_M; r += rstep) {
+      if (row < row_end)
+        cp_async_16(d, g);
+      else
+        *reinterpret_cast<float4 *>(d) = make_float4(0.f, 0.f, 0.f, 0.f);
+      d += rstep * 128;
+      g += (int64_t)rstep * dim;
+      row += rstep;
+    }
+    return;
+  }
   for (int p = tid; p < TC_M * chunks; p += TC_THREADS) {
-    const int row = p / chunks, ch = p - row * chunks;  // consecutive threads: consecutive chunks of a row
+    const int row = p / chunks, ch = p - row * chunks;
     unsigned char *d = dst + (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
     const int64_t g = row0 + row;
     if (g < row_end)
@@ -130,7 +157,7 @@ struct TensorArgs {
   int64_t n, m;
   int dim, k;
   int32_t *cand;               // [m, TC_CAP]
-  int32_t *cand_count;         // [m]; > TC_CAP marks an overflow
+  int32_t *cand_count;         // [m]; four 8-bit counts: list A front, A back, list B front, B back
   int *error_flag;
 };
 
@@ -145,29 +172,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
   const int dim = a.dim;
   const uint32_t tile_bytes = (uint32_t)((dim + 31) >> 5) * 16384u;  // whole atoms of 32 features
   unsigned char *sQ = smem;
-  unsigned char *sX = smem + tile_bytes;
-  float *s_sqx = reinterpret_cast<float *>(smem + 2 * tile_bytes);  // |x|^2 of the current and the next tile
-  float *gmin = s_sqx + 2 * TC_N;                                   // [TC_M][TC_GMAX + 1]
-  __shared__ __align__(8) uint64_t mbar;
+  unsigned char *sX = smem + tile_bytes;                             // ring of two point tiles
+  float *s_sqx = reinterpret_cast<float *>(smem + 3 * tile_bytes);   // |x|^2 per column, ring of three tiles
+  float *gmin = s_sqx + TC_SQX_SLOTS * TC_N;                         // [TC_GH][TC_THREADS] group minima
+  __shared__ __align__(8) uint64_t mbar[2];
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  if (tid == 0) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar)));
+  const int row = tid & (TC_M - 1);  // the query this thread reads back (TMEM lane)
+  const int part = tid >> 7;         // which 32 of a tile's 128 columns it reads
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[1])));
+  }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
-                 "r"(TC_N));
+                 "r"(2 * TC_N));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_base_s;
-  const uint32_t my_taddr = tmem + ((uint32_t)(warp * 32) << 16);
+  // a warp reaches the 32 TMEM lanes of its quarter (warp index mod 4)
+  const uint32_t my_taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(part * TC_COLS);
   // D = f32, A = B = tf32, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TC_N >> 3) << 17) |
                          ((uint32_t)(TC_M >> 4) << 24);
-  uint32_t phase = 0;
-  bool failed = false;
+  uint32_t phase0 = 0u, phase1 = 0u;  // parity of the next completion of each accumulator's mbarrier
+  bool ok = true, failed = false;
 
   const int64_t tile_lo = (int64_t)blockIdx.x * TC_M;
   const int64_t tile_hi = tile_lo + TC_M < a.m ? tile_lo + TC_M : a.m;
@@ -183,18 +216,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
     if (q_lo >= q_hi) continue;
     segment_points(a.ptr_x, a.n, b, x_lo, x_hi);
     const int64_t nx = x_hi > x_lo ? x_hi - x_lo : 0;
-    const int64_t q = q_lo + tid;
+    const int64_t q = q_lo + row;
     const bool have_q = q < q_hi;
-    if (nx == 0) {
-      if (have_q) a.cand_count[q] = 0;
-      continue;
-    }
+    if (nx == 0) continue;  // the candidate counts were zeroed before the launch
 
-    // groups of `gs` consecutive points (a multiple of 32), at most TC_GMAX of them
-    const int64_t per = (nx + TC_GMAX - 1) / TC_GMAX;
-    const int gs = (int)((per + 31) / 32 * 32);
-    const int ngroups = (int)((nx + gs - 1) / gs);
+    // A thread meets 32 columns of every tile; it groups that stream into at most TC_GH groups of
+    // `gs` columns (a multiple of 32).  The four threads of a query hold at most 64 group minima.
     const int ntiles = (int)((nx + TC_N - 1) / TC_N);
+    const int64_t own = (int64_t)ntiles * TC_COLS;
+    const int gs = (int)(((own + TC_GH - 1) / TC_GH + 31) / 32 * 32);
 
     // Everything is compared in "shifted" form a' = bias_x + scale * S, i.e. the approximate distance
     // minus the query's own constant (|q|^2 for L2, 1 for cosine): bias_x = |x|^2 or 0, +inf for
@@ -205,121 +235,160 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
       const float qsq = a.sq_y[q];
       err = 0.00390625f * 1.05f * sqrtf(qsq) * xmax + 4e-6f * (xmax * xmax + qsq);
     }
-    float *my_gmin = gmin + tid * (TC_GMAX + 1);
 
+    // Software pipeline over the 2 * ntiles steps (pass A then pass B over the same tiles): in
+    // iteration s the tensor core works on step s while the threads read back step s - 1 and the
+    // copies of step s + 1 are in flight.  Point tile of step s: ring slot s & 1; accumulator:
+    // TMEM columns (s & 1) * 128 ..; |x|^2 of its columns: slot s % 3.
+    const int nsteps = 2 * ntiles;
     stage_operand(sQ, a.ya, q_lo, q_hi, dim, tid);  // joins the first point tile's copy group
+    stage_operand(sX, a.xa, x_lo, x_hi, dim, tid);
+    if (tid < TC_N) s_sqx[tid] = x_lo + tid < x_hi ? (COSINE ? 0.f : a.sq_x[x_lo + tid]) : pos_inf<float>();
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
 
-    float thr = 0.f;
-    int ncand = 0;
-    for (int pass = 0; pass < 2 && !failed; ++pass) {
-      float run_min = pos_inf<float>();
-      int group = 0, in_group = 0;
-      // first tile of the pass (the query tile's copies, issued above, join this group in pass A)
-      stage_operand(sX, a.xa, x_lo, x_hi, dim, tid);
-      s_sqx[tid] = x_lo + tid < x_hi ? (COSINE ? 0.f : a.sq_x[x_lo + tid]) : pos_inf<float>();
-      asm volatile("cp.async.commit_group;\n" ::: "memory");
-      for (int t = 0; t < ntiles && !failed; ++t) {
-        const int64_t p0 = x_lo + (int64_t)t * TC_N;
+    float thr = 0.f, run_min = pos_inf<float>();
+    int group = 0, in_group = 0, ncand = 0;
+    for (int s = 0; s <= nsteps; ++s) {
+      if (s < nsteps) {
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();  // tile t is in place; everyone has finished reading the accumulator of tile t - 1
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      // step s is in place; everyone has finished reading the accumulator of step s - 2; and one
+      // decision for the whole CTA if some wait ran out
+      if (__syncthreads_or(!ok)) {
+        failed = true;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (s < nsteps && tid == 0) {
+        const uint32_t sx = smem_u32(sX) + (uint32_t)(s & 1) * tile_bytes;
+        const uint32_t acc = tmem + (uint32_t)(s & 1) * TC_N;
+        for (int ks = 0; ks < (dim >> 3); ++ks) {
+          const uint32_t off = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
+          const uint64_t da = umma_desc_sw128(smem_u32(sQ) + off);
+          const uint64_t db = umma_desc_sw128(sx + off);
+          const uint32_t accumulate = ks > 0 ? 1u : 0u;
+          asm volatile(
+              "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+              "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+              ::"r"(acc), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+              : "memory");
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                     ::"r"(smem_u32(&mbar[s & 1]))
+                     : "memory");
+      }
+      if (s >= 1) {
+        const int pb = (s - 1) & 1;
+        // step s - 1 is complete: its tile may be overwritten.  One answer per warp: the read-back
+        // below is a warp-wide instruction
+        ok = __all_sync(FULL_MASK, mbar_wait(&mbar[pb], pb ? phase1 : phase0));
+        if (pb)
+          phase1 ^= 1u;
+        else
+          phase0 ^= 1u;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (tid == 0) {
-          for (int ks = 0; ks < (dim >> 3); ++ks) {
-            const uint32_t off = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
-            const uint64_t da = umma_desc_sw128(smem_u32(sQ) + off);
-            const uint64_t db = umma_desc_sw128(smem_u32(sX) + off);
-            const uint32_t accumulate = ks > 0 ? 1u : 0u;
-            asm volatile(
-                "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-                ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-                : "memory");
-          }
-          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                       ::"r"(smem_u32(&mbar))
-                       : "memory");
-        }
-        const bool arrived = mbar_wait(&mbar, phase);
-        if (__syncthreads_or(!arrived)) {  // the same decision for the whole CTA
-          failed = true;
-          break;
-        }
-        phase ^= 1u;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // the tensor core is done with sX: fetch the next tile while this one is read back
-        if (t + 1 < ntiles) {
-          const int64_t p1 = p0 + TC_N;
-          stage_operand(sX, a.xa, p1, x_hi, dim, tid);
-          s_sqx[((t + 1) & 1) * TC_N + tid] = p1 + tid < x_hi ? (COSINE ? 0.f : a.sq_x[p1 + tid]) : pos_inf<float>();
-          asm volatile("cp.async.commit_group;\n" ::: "memory");
-        }
-        const float *sqx = s_sqx + (t & 1) * TC_N;
-
-        const int valid = (x_hi - p0) < TC_N ? (int)(x_hi - p0) : TC_N;
-#pragma unroll 1
-        for (int c0 = 0; c0 < TC_N; c0 += 32) {
-          uint32_t v[32];
-          tmem_load32(my_taddr + c0, v);
-          if (c0 >= valid) continue;  // uniform: a block past the segment's end
+      }
+      if (s + 1 < nsteps && ok) {
+        const int t1 = s + 1 < ntiles ? s + 1 : s + 1 - ntiles;
+        const int64_t p1 = x_lo + (int64_t)t1 * TC_N;
+        stage_operand(sX + (uint32_t)((s + 1) & 1) * tile_bytes, a.xa, p1, x_hi, dim, tid);
+        if (tid < TC_N)
+          s_sqx[((s + 1) % TC_SQX_SLOTS) * TC_N + tid] =
+              p1 + tid < x_hi ? (COSINE ? 0.f : a.sq_x[p1 + tid]) : pos_inf<float>();
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+      }
+      if (s >= 1 && ok) {
+        // read back step s - 1: this thread's 32 columns of its query's row
+        const int e = s - 1;
+        const int pass = e >= ntiles ? 1 : 0;
+        const int t = e - pass * ntiles;
+        const int64_t p0 = x_lo + (int64_t)t * TC_N + part * TC_COLS;
+        const float *sqx = s_sqx + (e % TC_SQX_SLOTS) * TC_N + part * TC_COLS;
+        uint32_t v[32];
+        tmem_load32(my_taddr + (uint32_t)(e & 1) * TC_N, v);
+        constexpr int c0 = 0;
+        if (p0 < x_hi) {  // else: a block past the segment's end
           if (pass == 0) {
-            float m = run_min;
+            // four independent chains, so that the minimum does not wait on itself
+            float m0 = run_min, m1 = pos_inf<float>(), m2 = m1, m3 = m1;
 #pragma unroll
             for (int j4 = 0; j4 < 8; ++j4) {
               const float4 bx = *reinterpret_cast<const float4 *>(sqx + c0 + 4 * j4);
-              m = fminf(m, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 0]), bx.x));
-              m = fminf(m, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 1]), bx.y));
-              m = fminf(m, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 2]), bx.z));
-              m = fminf(m, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 3]), bx.w));
+              m0 = fminf(m0, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 0]), bx.x));
+              m1 = fminf(m1, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 1]), bx.y));
+              m2 = fminf(m2, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 2]), bx.z));
+              m3 = fminf(m3, __fmaf_rn(scale, __uint_as_float(v[4 * j4 + 3]), bx.w));
             }
-            run_min = m;
+            run_min = fminf(fminf(m0, m1), fminf(m2, m3));
             in_group += 32;
-            if (in_group >= gs) {  // groups are multiples of 32 points and start at the segment's first point
-              my_gmin[group++] = run_min;
+            if (in_group >= gs) {
+              gmin[group * TC_THREADS + tid] = run_min;
+              ++group;
               run_min = pos_inf<float>();
               in_group = 0;
             }
           } else {
+            // one bit per column that passes, without branches; the few set bits are walked after
+            uint32_t hits = 0u;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float ap = __fmaf_rn(scale, __uint_as_float(v[j]), sqx[c0 + j]);
-              if (ap <= thr) {  // rare
-                if (ncand < TC_CAP && have_q) a.cand[q * TC_CAP + ncand] = (int32_t)(p0 + c0 + j);
-                ++ncand;
-              }
+            for (int j4 = 0; j4 < 8; ++j4) {
+              const float4 bx = *reinterpret_cast<const float4 *>(sqx + c0 + 4 * j4);
+              hits |= (__fmaf_rn(scale, __uint_as_float(v[4 * j4 + 0]), bx.x) <= thr ? 1u : 0u) << (4 * j4 + 0);
+              hits |= (__fmaf_rn(scale, __uint_as_float(v[4 * j4 + 1]), bx.y) <= thr ? 1u : 0u) << (4 * j4 + 1);
+              hits |= (__fmaf_rn(scale, __uint_as_float(v[4 * j4 + 2]), bx.z) <= thr ? 1u : 0u) << (4 * j4 + 2);
+              hits |= (__fmaf_rn(scale, __uint_as_float(v[4 * j4 + 3]), bx.w) <= thr ? 1u : 0u) << (4 * j4 + 3);
+            }
+            while (hits != 0u) {
+              const int j = __ffs(hits) - 1;
+              hits &= hits - 1u;
+              // threads 0 and 1 of a query share the first half of its list, 2 and 3 the second;
+              // one fills its half from the front, the other from the back: no atomics, no
+              // waiting on the stores
+              if (ncand < TC_CAP / 2 && have_q)
+                a.cand[q * TC_CAP + (part >> 1) * (TC_CAP / 2) + ((part & 1) ? TC_CAP / 2 - 1 - ncand : ncand)] =
+                    (int32_t)(p0 + c0 + j);
+              ++ncand;
             }
           }
         }
       }
-      if (pass == 0 && !failed) {
-        if (in_group > 0) my_gmin[group++] = run_min;
-        // k-th smallest of this query's group minima: k different points lie at or below it
-        if (group >= a.k) {
-          float g[TC_GMAX];
+      if (s == ntiles) {
+        // pass A is read back: the k-th smallest of the query's group minima (this thread's and
+        // its partner's) bounds the k-th smallest approximate distance — k different points lie
+        // at or below it
+        if (in_group > 0) gmin[(group++) * TC_THREADS + tid] = run_min;
+        for (int g = group; g < TC_GH; ++g) gmin[g * TC_THREADS + tid] = pos_inf<float>();
+        __syncthreads();
+        float g64[TC_PARTS * TC_GH];
 #pragma unroll
-          for (int i = 0; i < TC_GMAX; ++i) g[i] = i < group ? my_gmin[i] : pos_inf<float>();
-          sort64(g);
-          float kth = g[0];
+        for (int p = 0; p < TC_PARTS; ++p)
 #pragma unroll
-          for (int i = 1; i < 32; ++i) kth = (i == a.k - 1) ? g[i] : kth;  // k <= 32
-          thr = kth + 2.f * err;
-          if (!(thr < 3.0e38f)) thr = 3.0e38f;  // NaN or infinite: keep every real column (padding is +inf)
-        } else {
-          thr = 3.0e38f;  // fewer groups than k (short segment): keep every real column (padding is +inf)
-        }
-        (void)ngroups;
+          for (int i = 0; i < TC_GH; ++i) g64[p * TC_GH + i] = gmin[i * TC_THREADS + p * TC_M + row];
+        sort64(g64);
+        float kth = g64[0];
+#pragma unroll
+        for (int i = 1; i < 32; ++i) kth = (i == a.k - 1) ? g64[i] : kth;  // k <= 32
+        thr = kth + 2.f * err;
+        // NaN, infinite, or fewer than k non-empty groups (their minima are +inf): keep every real
+        // column; padding columns are +inf and still fail the comparison
+        if (!(thr < 3.0e38f)) thr = 3.0e38f;
       }
-      __syncthreads();  // all read-backs of this pass are done before its buffers are restaged
     }
-    if (have_q && !failed) a.cand_count[q] = ncand;
-    __syncthreads();
+    // the four counts of a query in one word (zeroed before the launch), 8 bits each; a count
+    // beyond a list's capacity is stored as capacity + 1, so that the pair's sum still says "overflow"
+    if (have_q && !failed) {
+      const int c = ncand < TC_CAP / 2 + 1 ? ncand : TC_CAP / 2 + 1;
+      atomicAdd(&a.cand_count[q], c << (8 * part));
+    }
+    __syncthreads();  // every read-back of this segment is done before the buffers are restaged
   }
   if (failed && tid == 0) *a.error_flag = 1;
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_N));
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * TC_N));
 }
 
 // ---- exact re-rank: one warp per query ---------------------------------------------------------------------
@@ -357,8 +426,11 @@ knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, cons
   const float ny = COSINE ? norms_y[q] : 1.f;
   const bool vec4 = (dim & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;  // rows are whole float4s
 
-  const int nc = cand_count[q];
-  const bool exhaustive = *error_flag != 0 || nc > TC_CAP;
+  // candidate row: two lists of TC_CAP / 2 slots, each filled from its front and from its back
+  const int packed = cand_count[q];
+  const int c0 = packed & 0xff, c1 = (packed >> 8) & 0xff, c2 = (packed >> 16) & 0xff, c3 = (packed >> 24) & 0xff;
+  const int nc = c0 + c1 + c2 + c3;
+  const bool exhaustive = *error_flag != 0 || c0 + c1 > TC_CAP / 2 || c2 + c3 > TC_CAP / 2;
   const int64_t total = exhaustive ? (x_hi > x_lo ? x_hi - x_lo : 0) : nc;
   float bound = 1e10f;
   for (int64_t base = 0; base < total; base += 32) {
@@ -366,7 +438,14 @@ knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, cons
     float dist[1] = {pos_inf<float>()};
     uint32_t idx = 0;
     if (i < total) {
-      idx = exhaustive ? (uint32_t)(x_lo + i) : (uint32_t)cand[q * TC_CAP + i];
+      int slot = (int)i;
+      if (i >= c0 + c1 + c2)
+        slot = TC_CAP - 1 - ((int)i - c0 - c1 - c2);
+      else if (i >= c0 + c1)
+        slot = TC_CAP / 2 + ((int)i - c0 - c1);
+      else if (i >= c0)
+        slot = TC_CAP / 2 - 1 - ((int)i - c0);
+      idx = exhaustive ? (uint32_t)(x_lo + i) : (uint32_t)cand[q * TC_CAP + slot];
       float acc = 0.f;
       if (vec4) {
         const float4 *row = reinterpret_cast<const float4 *>(x + (size_t)idx * dim);
@@ -446,8 +525,9 @@ __global__ void tensor_prep_kernel(const float *__restrict__ a, int64_t rows, in
     for (int d = 0; d < dim; ++d) normalised[i * dim + d] = a[i * dim + d] / nrm;
 }
 
+// query tile + ring of two point tiles + |x|^2 ring + group minima + alignment slack
 size_t knn_tensor_smem_bytes(int dim) {
-  return 2 * (size_t)((dim + 31) / 32) * 16384 + 2 * TC_N * 4 + (size_t)TC_M * (TC_GMAX + 1) * 4 + 1024;
+  return 3 * (size_t)((dim + 31) / 32) * 16384 + (size_t)TC_SQX_SLOTS * TC_N * 4 + (size_t)TC_GH * TC_THREADS * 4 + 1024;
 }
 
 static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
@@ -500,18 +580,29 @@ int launch_knn_tensor_f32(const KnnArgs &a, void *workspace) {
     yhat = (float *)ws; ws += al256((size_t)a.m * a.dim * 4);
   }
   B200C_CUDA(cudaMemsetAsync(xmax, 0, 256, a.stream));
+  B200C_CUDA(cudaMemsetAsync(cand_count, 0, (size_t)a.m * 4, a.stream));  // the two threads of a query add their counts
   const int threads = 128;
   tensor_prep_kernel<<<(unsigned)((a.n + threads - 1) / threads), threads, 0, a.stream>>>(
       (const float *)a.x, a.n, a.dim, sq_x, (unsigned *)xmax, xhat);
   B200C_LAUNCH_CHECK("tensor_prep_kernel");
-  tensor_prep_kernel<<<(unsigned)((a.m + threads - 1) / threads), threads, 0, a.stream>>>(
-      (const float *)a.y, a.m, a.dim, sq_y, nullptr, yhat);
-  B200C_LAUNCH_CHECK("tensor_prep_kernel");
+  const bool self = a.x == a.y && a.n == a.m;  // x searched in itself (knn_graph): one set of norms serves both
+  if (self) {
+    sq_y = sq_x;
+    yhat = xhat;
+  } else {
+    tensor_prep_kernel<<<(unsigned)((a.m + threads - 1) / threads), threads, 0, a.stream>>>(
+        (const float *)a.y, a.m, a.dim, sq_y, nullptr, yhat);
+    B200C_LAUNCH_CHECK("tensor_prep_kernel");
+  }
   if (a.cosine) {
     int st = launch_row_norms_f32(a.x, a.n, a.dim, norms_x, a.stream);
     if (st != B200C_OK) return st;
-    st = launch_row_norms_f32(a.y, a.m, a.dim, norms_y, a.stream);
-    if (st != B200C_OK) return st;
+    if (self) {
+      norms_y = norms_x;
+    } else {
+      st = launch_row_norms_f32(a.y, a.m, a.dim, norms_y, a.stream);
+      if (st != B200C_OK) return st;
+    }
   }
 
   TensorArgs t{a.cosine ? xhat : (const float *)a.x, a.cosine ? yhat : (const float *)a.y, sq_x, sq_y, xmax,
