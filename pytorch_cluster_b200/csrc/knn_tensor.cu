@@ -148,6 +148,21 @@ __device__ __forceinline__ void sort64(float (&v)[64]) {
   }
 }
 
+// Group minima of a CTA: 64 per query row, row r's entry c stored at r * 64 + (c ^ (r & 31)), so that
+// both the writers (consecutive rows, same c) and the readers (one row, consecutive c) hit 32
+// different banks.
+__device__ __forceinline__ int gmin_slot(int row, int c) { return row * 64 + (c ^ (row & 31)); }
+
+// Ascending merge of a bitonic sequence of 32-bit values held one per lane.
+__device__ __forceinline__ uint32_t warp_bitonic_merge32_u32(uint32_t v, int lane) {
+#pragma unroll
+  for (int stride = 16; stride > 0; stride >>= 1) {
+    const uint32_t o = __shfl_xor_sync(FULL_MASK, v, stride);
+    v = ((o < v) == ((lane & stride) == 0)) ? o : v;
+  }
+  return v;
+}
+
 struct TensorArgs {
   const float *xa, *ya;        // operands of the product: x, y (L2) or their normalised copies (cosine)
   const float *sq_x, *sq_y;    // L2: |row|^2 ; cosine: unused
@@ -174,7 +189,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
   unsigned char *sQ = smem;
   unsigned char *sX = smem + tile_bytes;                             // ring of two point tiles
   float *s_sqx = reinterpret_cast<float *>(smem + 3 * tile_bytes);   // |x|^2 per column, ring of three tiles
-  float *gmin = s_sqx + TC_SQX_SLOTS * TC_N;                         // [TC_GH][TC_THREADS] group minima
+  float *gmin = s_sqx + TC_SQX_SLOTS * TC_N;                         // [TC_M][64] group minima, see gmin_slot
   __shared__ __align__(8) uint64_t mbar[2];
   __shared__ uint32_t tmem_base_s;
 
@@ -324,7 +339,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
             run_min = fminf(fminf(m0, m1), fminf(m2, m3));
             in_group += 32;
             if (in_group >= gs) {
-              gmin[group * TC_THREADS + tid] = run_min;
+              gmin[gmin_slot(row, part * TC_GH + group)] = run_min;
               ++group;
               run_min = pos_inf<float>();
               in_group = 0;
@@ -358,18 +373,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
         // pass A is read back: the k-th smallest of the query's group minima (this thread's and
         // its partner's) bounds the k-th smallest approximate distance — k different points lie
         // at or below it
-        if (in_group > 0) gmin[(group++) * TC_THREADS + tid] = run_min;
-        for (int g = group; g < TC_GH; ++g) gmin[g * TC_THREADS + tid] = pos_inf<float>();
+        if (in_group > 0) gmin[gmin_slot(row, part * TC_GH + group++)] = run_min;
+        for (int g = group; g < TC_GH; ++g) gmin[gmin_slot(row, part * TC_GH + g)] = pos_inf<float>();
         __syncthreads();
-        float g64[TC_PARTS * TC_GH];
-#pragma unroll
-        for (int p = 0; p < TC_PARTS; ++p)
-#pragma unroll
-          for (int i = 0; i < TC_GH; ++i) g64[p * TC_GH + i] = gmin[i * TC_THREADS + p * TC_M + row];
-        sort64(g64);
-        float kth = g64[0];
-#pragma unroll
-        for (int i = 1; i < 32; ++i) kth = (i == a.k - 1) ? g64[i] : kth;  // k <= 32
+        // every warp selects for 8 rows: 64 values as two per lane, two warp sorts, the 32 smallest
+        // of both by one bitonic merge (k <= 32), compared as order-preserving integers
+        const int lane = tid & 31;
+        for (int r = warp * (TC_M / (TC_THREADS / 32)); r < (warp + 1) * (TC_M / (TC_THREADS / 32)); ++r) {
+          uint32_t lo = warp_sort32_u32(ordered_bits(gmin[gmin_slot(r, lane)]), lane);
+          const uint32_t hi = warp_sort32_u32(ordered_bits(gmin[gmin_slot(r, lane + 32)]), lane);
+          const uint32_t rev = __shfl_sync(FULL_MASK, hi, 31 - lane);
+          lo = warp_bitonic_merge32_u32(rev < lo ? rev : lo, lane);
+          const uint32_t kb = __shfl_sync(FULL_MASK, lo, a.k - 1);
+          if (lane == 0) gmin[r * 64] = from_ordered_bits(kb);  // the row's minima are consumed: reuse its first word
+        }
+        __syncthreads();
+        const float kth = gmin[row * 64];
         thr = kth + 2.f * err;
         // NaN, infinite, or fewer than k non-empty groups (their minima are +inf): keep every real
         // column; padding columns are +inf and still fail the comparison
@@ -432,54 +451,96 @@ knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, cons
   const int nc = c0 + c1 + c2 + c3;
   const bool exhaustive = *error_flag != 0 || c0 + c1 > TC_CAP / 2 || c2 + c3 > TC_CAP / 2;
   const int64_t total = exhaustive ? (x_hi > x_lo ? x_hi - x_lo : 0) : nc;
+  // exact distance of point `idx` to the query, with the reference's operation order
+  auto exact_dist = [&](uint32_t idx) -> float {
+    float acc = 0.f;
+    if (vec4) {
+      const float4 *row = reinterpret_cast<const float4 *>(x + (size_t)idx * dim);
+      for (int d4 = 0; d4 < (dim >> 2); ++d4) {
+        const float4 xv = row[d4];
+        const float4 qv = *reinterpret_cast<const float4 *>(my_q + 4 * d4);
+        if (COSINE) {
+          acc = __fmaf_rn(xv.x, qv.x, acc);
+          acc = __fmaf_rn(xv.y, qv.y, acc);
+          acc = __fmaf_rn(xv.z, qv.z, acc);
+          acc = __fmaf_rn(xv.w, qv.w, acc);
+        } else {
+          float df = xv.x - qv.x;
+          acc = __fmaf_rn(df, df, acc);
+          df = xv.y - qv.y;
+          acc = __fmaf_rn(df, df, acc);
+          df = xv.z - qv.z;
+          acc = __fmaf_rn(df, df, acc);
+          df = xv.w - qv.w;
+          acc = __fmaf_rn(df, df, acc);
+        }
+      }
+    } else {
+      const float *row = x + (size_t)idx * dim;
+      for (int d = 0; d < dim; ++d) {
+        if (COSINE) {
+          acc = __fmaf_rn(row[d], my_q[d], acc);
+        } else {
+          const float df = row[d] - my_q[d];
+          acc = __fmaf_rn(df, df, acc);
+        }
+      }
+    }
+    return COSINE ? 1.f - acc / (norms_x[idx] * ny) : acc;
+  };
+  auto cand_at = [&](int i) -> uint32_t {
+    int slot = i;
+    if (i >= c0 + c1 + c2)
+      slot = TC_CAP - 1 - (i - c0 - c1 - c2);
+    else if (i >= c0 + c1)
+      slot = TC_CAP / 2 + (i - c0 - c1);
+    else if (i >= c0)
+      slot = TC_CAP / 2 - 1 - (i - c0);
+    return (uint32_t)cand[q * TC_CAP + slot];
+  };
+
+  if (!exhaustive && total <= 64) {
+    // The usual case, at most two candidates per lane: two warp sorts and a merge in registers,
+    // without the queue in shared memory.  Only distances below 1e10 are admissible, as everywhere.
+    K k0 = K::empty(), k1 = K::empty();
+    if (lane < total) {
+      const uint32_t idx = cand_at(lane);
+      const float d = exact_dist(idx);
+      if (d < 1e10f) k0 = K::make(d, idx);
+    }
+    if (lane + 32 < total) {
+      const uint32_t idx = cand_at(lane + 32);
+      const float d = exact_dist(idx);
+      if (d < 1e10f) k1 = K::make(d, idx);
+    }
+    k0 = warp_sort32(k0, lane);
+    if (total > 32) {
+      k1 = warp_sort32(k1, lane);
+      // the 32 smallest of both: element i of one against element 31 - i of the other is bitonic
+      k0 = key_min(k0, k1.shfl(31 - lane));
+      k0 = warp_bitonic_merge32(k0, lane);
+    }
+    const bool okk = lane < k && !k0.is_empty();
+    if (lane < k) {
+      out_row[q * k + lane] = q;
+      out_col[q * k + lane] = okk ? (int64_t)k0.index() : (int64_t)-1;
+    }
+    const int valid = __popc(__ballot_sync(FULL_MASK, okk));
+    if (lane == 0) {
+      counts[q] = valid;
+      if (valid) atomicAdd(num_valid, (unsigned long long)valid);
+    }
+    return;
+  }
+
   float bound = 1e10f;
   for (int64_t base = 0; base < total; base += 32) {
     const int64_t i = base + lane;
     float dist[1] = {pos_inf<float>()};
     uint32_t idx = 0;
     if (i < total) {
-      int slot = (int)i;
-      if (i >= c0 + c1 + c2)
-        slot = TC_CAP - 1 - ((int)i - c0 - c1 - c2);
-      else if (i >= c0 + c1)
-        slot = TC_CAP / 2 + ((int)i - c0 - c1);
-      else if (i >= c0)
-        slot = TC_CAP / 2 - 1 - ((int)i - c0);
-      idx = exhaustive ? (uint32_t)(x_lo + i) : (uint32_t)cand[q * TC_CAP + slot];
-      float acc = 0.f;
-      if (vec4) {
-        const float4 *row = reinterpret_cast<const float4 *>(x + (size_t)idx * dim);
-        for (int d4 = 0; d4 < (dim >> 2); ++d4) {
-          const float4 xv = row[d4];
-          const float4 qv = *reinterpret_cast<const float4 *>(my_q + 4 * d4);
-          if (COSINE) {
-            acc = __fmaf_rn(xv.x, qv.x, acc);
-            acc = __fmaf_rn(xv.y, qv.y, acc);
-            acc = __fmaf_rn(xv.z, qv.z, acc);
-            acc = __fmaf_rn(xv.w, qv.w, acc);
-          } else {
-            float df = xv.x - qv.x;
-            acc = __fmaf_rn(df, df, acc);
-            df = xv.y - qv.y;
-            acc = __fmaf_rn(df, df, acc);
-            df = xv.z - qv.z;
-            acc = __fmaf_rn(df, df, acc);
-            df = xv.w - qv.w;
-            acc = __fmaf_rn(df, df, acc);
-          }
-        }
-      } else {
-        const float *row = x + (size_t)idx * dim;
-        for (int d = 0; d < dim; ++d) {
-          if (COSINE) {
-            acc = __fmaf_rn(row[d], my_q[d], acc);
-          } else {
-            const float df = row[d] - my_q[d];
-            acc = __fmaf_rn(df, df, acc);
-          }
-        }
-      }
-      dist[0] = COSINE ? 1.f - acc / (norms_x[idx] * ny) : acc;
+      idx = exhaustive ? (uint32_t)(x_lo + i) : cand_at((int)i);
+      dist[0] = exact_dist(idx);
     }
     if (__any_sync(FULL_MASK, dist[0] < bound)) {
       // candidate r = 0 of lane l is offered with index idx0 + 32 * 0; pass the lane's own index
