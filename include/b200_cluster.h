@@ -140,6 +140,21 @@ int b200c_knn_graph_tail_write(const int64_t *edge_padded, const int32_t *counts
                                int64_t m, int64_t k, int drop_self, int source_to_target,
                                int64_t num_edges, int64_t *edge_index, b200c_stream_t stream);
 
+/* knn_graph with loop = False in one kernel, for fp32 / fp64 points of up to 8 features — the
+ * search for k + 1 neighbours of every row of x in x, the `row != col` mask and the flow swap of
+ * torch_cluster/knn.py:131-144 without the padded intermediate.
+ *
+ * edge_index is int64 [2, n * k].  A query whose k + 1 nearest points exist and include itself
+ * writes its k other neighbours, in order, at slots q*k..; row 0 = neighbour and row 1 = query
+ * when source_to_target, else the other way round.  *irregular (one int32, device) receives the
+ * number of queries that do not have that shape (segments of fewer than k + 1 points; rows
+ * pushed out of their own list by k + 1 exact duplicates); their slots are left unwritten.  When
+ * it is 0 the result is final, otherwise run b200c_knn and the tail entry points instead.
+ * Returns B200C_ERR_UNSUPPORTED for more than 8 features and for the 16-bit types. */
+int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n,
+                    int64_t dim, int64_t k, int dtype, int source_to_target,
+                    int64_t *edge_index, int32_t *irregular, b200c_stream_t stream);
+
 /* Fixed-radius search — replaces radius_kernel and its -1 padded output
  * (csrc/cuda/radius_cuda.cu:9-42, 75-95) by count -> exclusive scan -> fill.
  *

@@ -134,3 +134,15 @@ def fps(src, ptr, out_ptr, start=None):
     _native.check(lib.b200c_fps(_p(src), _p(ptr), _p(out_ptr), _p(start), ptr.numel() - 1, n, dim, _dtype(src),
                                 _p(out), _p(ws), nbytes, _stream()))
     return out
+
+
+def knn_graph(x, k, ptr=None, source_to_target=True):
+    """-> (edge_index int64 [2, n*k], irregular int): b200c_knn_graph; edge_index is final iff irregular == 0."""
+    lib = _native.cabi()
+    n, dim = x.shape
+    nseg = 1 if ptr is None else ptr.numel() - 1
+    out = torch.empty(2, n * k, dtype=torch.long, device=x.device)
+    irregular = torch.empty(1, dtype=torch.int32, device=x.device)
+    _native.check(lib.b200c_knn_graph(_p(x), _p(ptr), nseg, n, dim, k, _dtype(x), int(source_to_target), _p(out),
+                                      _p(irregular), _stream()))
+    return out, int(irregular.item())

@@ -157,6 +157,31 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
   return f32 ? launch_knn_generic_f32(a) : launch_knn_generic_f64(a);
 }
 
+// knn_graph of low-dimensional points in one kernel: see b200_cluster.h
+extern "C" int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
+                               int64_t k, int dtype, int source_to_target, int64_t *edge_index, int32_t *irregular,
+                               b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int st = check_common(x, x, ptr, ptr, num_segments, n, n, dim, dtype);
+  if (st != B200C_OK) return st;
+  B200C_CHECK_ARG(k >= 1, "`k` needs to be positive");
+  B200C_CHECK_ARG(k + 1 <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
+  B200C_CHECK_ARG(irregular != nullptr && (edge_index != nullptr || n == 0), "null output pointer");
+  if (dim > 8 || is16(dtype)) {
+    set_error("b200c_knn_graph covers fp32 / fp64 points of up to 8 features; use b200c_knn and the tail entry points");
+    return B200C_ERR_UNSUPPORTED;
+  }
+  if ((st = check_device()) != B200C_OK) return st;
+  B200C_CUDA(cudaMemsetAsync(irregular, 0, sizeof(int32_t), stream));
+  if (n == 0) return B200C_OK;
+  KnnArgs a{x, x, ptr, ptr, (int)num_segments, n, n, (int)dim, (int)(k + 1), 0, nullptr, nullptr,
+            nullptr, nullptr, nullptr, nullptr, stream};
+  a.graph_out = edge_index;
+  a.graph_s2t = source_to_target;
+  a.graph_irregular = (int *)irregular;
+  return dtype == B200C_F32 ? launch_knn_lowd_f32(a) : launch_knn_lowd_f64(a);
+}
+
 // One-pass mode keeps a row of max_num_neighbors int32 slots per query; it is used when that
 // scratch is modest, i.e. for the small neighbour caps that are typical in practice.
 static constexpr int64_t RADIUS_DIRECT_MAX_NN = 256;

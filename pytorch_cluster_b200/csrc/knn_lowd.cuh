@@ -30,7 +30,8 @@ __global__ void __launch_bounds__(CTA_THREADS, KP == 32 ? 3 : 2)
 knn_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *__restrict__ ptr_x,
                 const int64_t *__restrict__ ptr_y, int num_segments, int64_t n, int64_t m, int k,
                 int64_t *__restrict__ out_row, int64_t *__restrict__ out_col,
-                int32_t *__restrict__ counts, unsigned long long *__restrict__ num_valid) {
+                int32_t *__restrict__ counts, unsigned long long *__restrict__ num_valid,
+                int64_t *__restrict__ graph_out, int graph_s2t, int *__restrict__ graph_irregular) {
   using Cfg = KnnLowD<T, DIM, KP>;
   using C = LowD<T, DIM>;
   using K = Key<T>;
@@ -51,7 +52,7 @@ knn_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t 
   const int64_t tile_hi = tile_lo + TQ < m ? tile_lo + TQ : m;
   const int b_first = segment_of(ptr_y, num_segments, tile_lo);
   const int b_last = segment_of(ptr_y, num_segments, tile_hi - 1);
-  int my_valid = 0;
+  int my_valid = 0, my_irregular = 0;
 
   for (int b = b_first; b <= b_last; ++b) {
     int64_t y_lo, y_hi, x_lo, x_hi;
@@ -121,6 +122,12 @@ knn_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t 
     // final merge and output
     for (int qi = 0; qi < nq; ++qi) {
       const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
+      if (graph_out != nullptr) {
+        if (!knn_finish_graph<T, KP>(my_keys + qi * (KP + Cfg::QCAP), my_cnt[qi], k, q, m, graph_out, graph_s2t != 0,
+                                     lane))
+          ++my_irregular;
+        continue;
+      }
       const int valid = knn_finish<T, KP>(my_keys + qi * (KP + Cfg::QCAP), my_cnt[qi], k, q, out_row, out_col, lane);
       if (lane == 0) {
         counts[q] = valid;
@@ -131,6 +138,7 @@ knn_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t 
   }
 
   if (lane == 0 && my_valid) atomicAdd(num_valid, (unsigned long long)my_valid);
+  if (lane == 0 && my_irregular) atomicAdd(graph_irregular, my_irregular);
 }
 
 }  // namespace b200c

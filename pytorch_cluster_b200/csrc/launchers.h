@@ -19,6 +19,12 @@ struct KnnArgs {
   int32_t *counts;
   unsigned long long *num_valid;
   cudaStream_t stream;
+  // graph mode of the low-dimensional kernel (x searched in itself, k = neighbours + 1): final
+  // [2, m * (k - 1)] edge rows without the self matches, and a count of queries that do not fit
+  // that shape; the padded outputs above are then unused
+  int64_t *graph_out = nullptr;
+  int graph_s2t = 0;
+  int *graph_irregular = nullptr;
 };
 
 struct RadiusArgs {

@@ -136,6 +136,16 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
   const int64_t n = p.x.size(0), dim = p.x.size(1);
   if (n == 0) return torch::empty({2, 0}, lopts);
 
+  if (!loop && !cosine && dim <= 8 && (p.dtype == B200C_F32 || p.dtype == B200C_F64)) {
+    // the usual shape (every row finds itself and k others) comes out of one kernel; anything
+    // else is detected there and takes the general route below
+    auto out = torch::empty({2, n * k}, lopts);
+    auto irregular = torch::empty({1}, iopts);
+    check_status(b200c_knn_graph(p.x.data_ptr(), p.px, p.num_segments, n, dim, k, p.dtype, source_to_target ? 1 : 0,
+                                 out.data_ptr<int64_t>(), irregular.data_ptr<int32_t>(), stream.stream()));
+    if (irregular.item<int32_t>() == 0) return out;  // the one host sync
+  }
+
   auto padded = torch::empty({2, n * k1}, lopts);
   auto counts = torch::empty({n}, iopts);
   auto num_valid = torch::empty({1}, lopts);

@@ -375,3 +375,48 @@ def test_radius_16bit(dim, kind):
     sx, sy = [1000, 0, 1500], [200, 100, 300]
     _check_radius16(x, y, r, kind, _segments(sx), _segments(sy), max_nn=40)
     _check_radius16(x, x, r, kind, max_nn=25, ignore_same=True)
+
+
+# ---- knn_graph in one kernel (b200c_knn_graph) --------------------------------------------------------
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+@pytest.mark.parametrize("s2t", [True, False])
+@pytest.mark.parametrize("k", [1, 6, 20, 31, 32, 63, 99])
+def test_knn_graph_one_kernel(k, s2t, dt):
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    sizes = [700, 150, 1300]
+    x, _ = _data(40 + k, sum(sizes), 1, 3, DT[dt])
+    ptr = _segments(sizes)
+    got, irregular = _cabi.knn_graph(x.to(DEV), k, ptr.to(DEV), s2t)
+    assert irregular == 0
+    batch = np.repeat(np.arange(3), sizes)
+    want = orc.knn_graph_api(x.numpy(), k, batch, loop=False, flow="source_to_target" if s2t else "target_to_source")
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_knn_graph_one_kernel_reports_irregular_queries():
+    """Segments with fewer than k + 1 points, and rows pushed out of their own list by duplicates,
+    are counted (and left to the general path), the rest is still written."""
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    sizes = [5, 400]
+    x, _ = _data(3, sum(sizes), 1, 2, torch.float32)
+    got, irregular = _cabi.knn_graph(x.to(DEV), 8, _segments(sizes).to(DEV), True)
+    assert irregular == 5
+    want = orc.knn_graph_api(x.numpy(), 8, np.repeat(np.arange(2), sizes), loop=False)
+    keep = want[1] >= 5  # edges of the regular segment
+    assert np.array_equal(got.cpu().numpy()[:, 5 * 8:], want[:, keep])
+    # 12 copies of one point, k = 4: a copy with a high index is not among its own 5 nearest
+    x = torch.zeros(12, 3)
+    _, irregular = _cabi.knn_graph(x.to(DEV), 4, None, True)
+    assert irregular == 12 - 5
+
+
+def test_knn_graph_one_kernel_unsupported_shapes():
+    from pytorch_cluster_b200 import _native, cabi as _cabi
+
+    x = torch.randn(100, 9).to(DEV)
+    with pytest.raises(RuntimeError):
+        _cabi.knn_graph(x, 4)
+    assert "8 features" in _native.cabi().b200c_last_error().decode()
