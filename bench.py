@@ -315,6 +315,20 @@ def run_only(args):
         x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 16)
         max_nn = 8192 if name.endswith("two_scans") else 64
         fn = lambda: cabi.radius(x, x, w["r"], ptr, ptr, max_nn, True)
+    elif name == "knn_graph_one_kernel":       # the headline call's kernel in its graph-output mode
+        w = make_knn_graph_batched()
+        x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 32)
+        fn = lambda: cabi.knn_graph(x, 20, ptr, True)
+    elif name in ("fps_small", "nearest_small"):  # 16 of the 64 clouds; 25 % samples, then assignment
+        w = make_radius_mixture(clouds=16)
+        x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 16)
+        out_ptr = torch.arange(17, device=dev) * 2048
+        samples = cabi.fps(x, ptr, out_ptr)
+        if name == "fps_small":
+            fn = lambda: cabi.fps(x, ptr, out_ptr)
+        else:
+            y = x[samples].contiguous()
+            fn = lambda: cabi.nearest(x, y, ptr, out_ptr)
     else:
         raise SystemExit(f"unknown workload {name}")
     for _ in range(steps):

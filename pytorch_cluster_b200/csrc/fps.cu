@@ -84,8 +84,9 @@ fps_kernel(const T *__restrict__ src, const int64_t *__restrict__ ptr, const int
         planes[d * plane + p] = src[seg_lo * DIM + f];
       }
       __syncthreads();
+      // keys: distance bits << 32 | 0xffffffff - ((offset mod 256) << 24 | offset); 0 = "no point"
       float c[PT][DIM], dmin[PT];
-      uint32_t inv_tie[PT];  // 0xffffffff - ((offset mod 256) << 24 | offset); 0 marks "no point"
+      uint32_t valid_mask = 0u;
 #pragma unroll
       for (int j = 0; j < PT; ++j) {
         const int rel = tid + j * FPS_THREADS;
@@ -93,7 +94,7 @@ fps_kernel(const T *__restrict__ src, const int64_t *__restrict__ ptr, const int
 #pragma unroll
         for (int d = 0; d < DIM; ++d) c[j][d] = valid ? planes[d * plane + rel] : 0.f;
         dmin[j] = 5e4f;
-        inv_tie[j] = valid ? 0xffffffffu - ((uint32_t)(rel & (FPS_REF_STRIDE - 1)) << 24 | (uint32_t)rel) : 0u;
+        valid_mask |= valid ? 1u << j : 0u;
       }
       int old_rel = (int)(start != nullptr ? start[b] : 0);
       if (tid == 0) out[o_lo] = seg_lo + old_rel;
@@ -102,7 +103,12 @@ fps_kernel(const T *__restrict__ src, const int64_t *__restrict__ ptr, const int
         float q[DIM];
 #pragma unroll
         for (int d = 0; d < DIM; ++d) q[d] = planes[d * plane + old_rel];
-        uint32_t hi = 0u, lo = 0u;
+        // A thread's points t, t + 1024, ... share (offset mod 256), so among them the reference's
+        // order of equal distances is the index order: keep the first strict maximum, without
+        // branches.  Slots past the segment's end come last and hold bits 0, so they never replace
+        // a real point.
+        uint32_t hi = 0u;
+        int jbest = 0;
 #pragma unroll
         for (int j = 0; j < PT; ++j) {
           float dd = 0.f;
@@ -111,12 +117,12 @@ fps_kernel(const T *__restrict__ src, const int64_t *__restrict__ ptr, const int
           dd = fminf(dmin[j], dd);
           dmin[j] = dd;
           // dd >= 0 here (a NaN sum is dropped by fminf), so its bit pattern orders like its value
-          const uint32_t bits = inv_tie[j] != 0u ? __float_as_uint(dd) : 0u;
-          if (bits > hi || (bits == hi && inv_tie[j] > lo)) {
-            hi = bits;
-            lo = inv_tie[j];
-          }
+          const uint32_t bits = valid_mask & (1u << j) ? __float_as_uint(dd) : 0u;
+          jbest = bits > hi ? j : jbest;
+          hi = bits > hi ? bits : hi;
         }
+        const int rel_best = tid + jbest * FPS_THREADS;
+        uint32_t lo = tid < n ? 0xffffffffu - ((uint32_t)(rel_best & (FPS_REF_STRIDE - 1)) << 24 | (uint32_t)rel_best) : 0u;
         warp_max_key(hi, lo);
         if (lane == 0) part_key[buf][warp] = make_uint2(hi, lo);
         __syncthreads();
