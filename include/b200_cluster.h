@@ -155,6 +155,17 @@ int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_segments, int
                     int64_t dim, int64_t k, int dtype, int source_to_target,
                     int64_t *edge_index, int32_t *irregular, b200c_stream_t stream);
 
+/* The same for a part of a larger point set, so that a host can cut one knn_graph call into
+ * groups of whole segments and overlap their copies with the search of the next group: x, ptr,
+ * n describe the part (ptr starts at 0), index_base (the part's first row in the whole set) is
+ * added to every index written, edge_row0 points to the part's first slot in row 0 of the whole
+ * edge_index and row_stride is the distance to the same slot of row 1 (the whole set's n * k).
+ * No counterpart in the reference, which has no host-buffer path. */
+int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n,
+                         int64_t dim, int64_t k, int dtype, int source_to_target,
+                         int64_t index_base, int64_t *edge_row0, int64_t row_stride,
+                         int32_t *irregular, b200c_stream_t stream);
+
 /* Fixed-radius search — replaces radius_kernel and its -1 padded output
  * (csrc/cuda/radius_cuda.cu:9-42, 75-95) by count -> exclusive scan -> fill.
  *

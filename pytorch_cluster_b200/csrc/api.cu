@@ -158,15 +158,17 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
 }
 
 // knn_graph of low-dimensional points in one kernel: see b200_cluster.h
-extern "C" int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
-                               int64_t k, int dtype, int source_to_target, int64_t *edge_index, int32_t *irregular,
-                               b200c_stream_t stream_) {
+extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
+                                    int64_t k, int dtype, int source_to_target, int64_t index_base,
+                                    int64_t *edge_row0, int64_t row_stride, int32_t *irregular,
+                                    b200c_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   int st = check_common(x, x, ptr, ptr, num_segments, n, n, dim, dtype);
   if (st != B200C_OK) return st;
   B200C_CHECK_ARG(k >= 1, "`k` needs to be positive");
   B200C_CHECK_ARG(k + 1 <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
-  B200C_CHECK_ARG(irregular != nullptr && (edge_index != nullptr || n == 0), "null output pointer");
+  B200C_CHECK_ARG(irregular != nullptr && (edge_row0 != nullptr || n == 0), "null output pointer");
+  B200C_CHECK_ARG(index_base >= 0 && row_stride >= n * k, "Input mismatch");
   if (dim > 8 || is16(dtype)) {
     set_error("b200c_knn_graph covers fp32 / fp64 points of up to 8 features; use b200c_knn and the tail entry points");
     return B200C_ERR_UNSUPPORTED;
@@ -176,10 +178,19 @@ extern "C" int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_se
   if (n == 0) return B200C_OK;
   KnnArgs a{x, x, ptr, ptr, (int)num_segments, n, n, (int)dim, (int)(k + 1), 0, nullptr, nullptr,
             nullptr, nullptr, nullptr, nullptr, stream};
-  a.graph_out = edge_index;
+  a.graph_out = edge_row0;
+  a.graph_row_stride = row_stride;
+  a.graph_index_base = index_base;
   a.graph_s2t = source_to_target;
   a.graph_irregular = (int *)irregular;
   return dtype == B200C_F32 ? launch_knn_lowd_f32(a) : launch_knn_lowd_f64(a);
+}
+
+extern "C" int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
+                               int64_t k, int dtype, int source_to_target, int64_t *edge_index, int32_t *irregular,
+                               b200c_stream_t stream) {
+  return b200c_knn_graph_part(x, ptr, num_segments, n, dim, k, dtype, source_to_target, 0, edge_index, n * k,
+                              irregular, stream);
 }
 
 // One-pass mode keeps a row of max_num_neighbors int32 slots per query; it is used when that

@@ -31,7 +31,8 @@ knn_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t 
                 const int64_t *__restrict__ ptr_y, int num_segments, int64_t n, int64_t m, int k,
                 int64_t *__restrict__ out_row, int64_t *__restrict__ out_col,
                 int32_t *__restrict__ counts, unsigned long long *__restrict__ num_valid,
-                int64_t *__restrict__ graph_out, int graph_s2t, int *__restrict__ graph_irregular) {
+                int64_t *__restrict__ graph_out, int64_t graph_row_stride, int64_t graph_index_base, int graph_s2t,
+                int *__restrict__ graph_irregular) {
   using Cfg = KnnLowD<T, DIM, KP>;
   using C = LowD<T, DIM>;
   using K = Key<T>;
@@ -123,8 +124,8 @@ knn_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t 
     for (int qi = 0; qi < nq; ++qi) {
       const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
       if (graph_out != nullptr) {
-        if (!knn_finish_graph<T, KP>(my_keys + qi * (KP + Cfg::QCAP), my_cnt[qi], k, q, m, graph_out, graph_s2t != 0,
-                                     lane))
+        if (!knn_finish_graph<T, KP>(my_keys + qi * (KP + Cfg::QCAP), my_cnt[qi], k, q, graph_row_stride,
+                                     graph_index_base, graph_out, graph_s2t != 0, lane))
           ++my_irregular;
         continue;
       }

@@ -23,7 +23,8 @@ static int launch_knn_lowd_one(const KnnArgs &a) {
   }
   kern<<<(unsigned)tiles, CTA_THREADS, Cfg::SMEM_BYTES, a.stream>>>(
       (const T *)a.x, (const T *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.k, a.out_row,
-      a.out_col, a.counts, a.num_valid, a.graph_out, a.graph_s2t, a.graph_irregular);
+      a.out_col, a.counts, a.num_valid, a.graph_out, a.graph_row_stride, a.graph_index_base, a.graph_s2t,
+      a.graph_irregular);
   B200C_LAUNCH_CHECK("knn_lowd_kernel");
   return B200C_OK;
 }

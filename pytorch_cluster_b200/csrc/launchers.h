@@ -22,7 +22,9 @@ struct KnnArgs {
   // graph mode of the low-dimensional kernel (x searched in itself, k = neighbours + 1): final
   // [2, m * (k - 1)] edge rows without the self matches, and a count of queries that do not fit
   // that shape; the padded outputs above are then unused
-  int64_t *graph_out = nullptr;
+  int64_t *graph_out = nullptr;     // row 0 of this call's slots
+  int64_t graph_row_stride = 0;     // distance from a slot of row 0 to the same slot of row 1
+  int64_t graph_index_base = 0;     // added to every index written (rows of a part of a larger x)
   int graph_s2t = 0;
   int *graph_irregular = nullptr;
 };

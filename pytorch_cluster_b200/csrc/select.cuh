@@ -169,14 +169,15 @@ __device__ __forceinline__ int knn_finish(Key<T> *keys, int cnt, int k, int64_t 
 }
 
 // knn_graph output of one query (row q) whose k1 = k + 1 best points include q itself: the k other
-// ones, in order, at slots q*k .. q*k+k-1 of the final [2, m*k] edge rows (row 0 = neighbour,
-// row 1 = query when s2t, else the other way round) — the `row != col` mask and the flow swap of
+// ones, in order, at slots q*k .. q*k+k-1 of the two edge rows (row 0 = neighbour, row 1 = query
+// when s2t, else the other way round; the rows lie row_stride apart; index_base is added to both) — the `row != col` mask and the flow swap of
 // torch_cluster/knn.py:135-144 applied while the list is still in shared memory.  Returns false
 // (and writes nothing) when the query has fewer than k1 points or q is not among them; such
 // queries need the general path.
 template <typename T, int KP>
-__device__ __forceinline__ bool knn_finish_graph(Key<T> *keys, int cnt, int k1, int64_t q, int64_t m,
-                                                 int64_t *__restrict__ graph_out, bool s2t, int lane) {
+__device__ __forceinline__ bool knn_finish_graph(Key<T> *keys, int cnt, int k1, int64_t q, int64_t row_stride,
+                                                 int64_t index_base, int64_t *__restrict__ graph_out, bool s2t,
+                                                 int lane) {
   if (cnt > 0) knn_merge<T, KP>(keys, cnt, k1, lane);
   int valid = 0, selfpos = -1;
   for (int e0 = 0; e0 < k1; e0 += 32) {
@@ -189,13 +190,13 @@ __device__ __forceinline__ bool knn_finish_graph(Key<T> *keys, int cnt, int k1, 
   }
   if (valid != k1 || selfpos < 0) return false;
   const int64_t k = k1 - 1;
-  int64_t *row_nb = s2t ? graph_out : graph_out + m * k;
-  int64_t *row_q = s2t ? graph_out + m * k : graph_out;
+  int64_t *row_nb = s2t ? graph_out : graph_out + row_stride;
+  int64_t *row_q = s2t ? graph_out + row_stride : graph_out;
   for (int e = lane; e < k1; e += 32) {
     if (e == selfpos) continue;
     const int64_t slot = q * k + e - (e > selfpos ? 1 : 0);
-    row_nb[slot] = (int64_t)keys[e].index();
-    row_q[slot] = q;
+    row_nb[slot] = index_base + (int64_t)keys[e].index();
+    row_q[slot] = index_base + q;
   }
   return true;
 }

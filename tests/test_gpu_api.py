@@ -246,3 +246,32 @@ def test_knn_graph_fused_tail_equals_reference_composition(dtype):
                     keep = row != col
                     row, col = row[keep], col[keep]
                 assert np.array_equal(got, torch.stack([row, col]).cpu().numpy())
+
+
+# ---- host-buffer entry point -----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float, torch.double])
+@pytest.mark.parametrize("flow", ["source_to_target", "target_to_source"])
+def test_knn_graph_host_equals_device_call(dtype, flow):
+    from pytorch_cluster_b200 import knn_graph, knn_graph_host
+
+    g = torch.Generator().manual_seed(77)
+    sizes = [900, 300, 1, 2000, 650, 40, 1200]
+    x = torch.randn(sum(sizes), 3, generator=g, dtype=dtype)
+    x[900:1201] = torch.randn(301, 3, generator=g, dtype=dtype)  # keep every segment >= k + 1 except the single row
+    batch = torch.arange(len(sizes)).repeat_interleave(torch.tensor(sizes))
+    k = 12
+    want = knn_graph(x.to(DEV), k, batch.to(DEV), flow=flow).cpu()
+    got = knn_graph_host(x.pin_memory(), k, batch.pin_memory(), flow=flow)  # one-row segment: the general route
+    assert torch.equal(got, want)
+    keep = batch != 2
+    xr, br = x[keep].contiguous(), batch[keep].contiguous()
+    want = knn_graph(xr.to(DEV), k, br.to(DEV), flow=flow).cpu()
+    out = torch.empty(2, xr.shape[0] * k, dtype=torch.long).pin_memory()
+    for groups in (1, 2, 4, 16):
+        out.fill_(-7)
+        got = knn_graph_host(xr.pin_memory(), k, br.pin_memory(), flow=flow, out=out, num_groups=groups)
+        assert got.data_ptr() == out.data_ptr() and torch.equal(got, want)
+    # no batch vector, unpinned input, other routes
+    assert torch.equal(knn_graph_host(xr, k), knn_graph(xr.to(DEV), k).cpu())
+    assert torch.equal(knn_graph_host(xr, k, br, loop=True), knn_graph(xr.to(DEV), k, br.to(DEV), loop=True).cpu())
