@@ -9,7 +9,7 @@ the whole batch.  Printed: ONE JSON line with
   value       queries/s with inputs resident in HBM (CUDA events, L2 flushed between steps)
   e2e         the same result from pinned host buffers to a pinned host buffer
               (``knn_graph_host``): upload of x, search and download of edge_index inside the
-              timed region, overlapped across groups of clouds on two streams
+              timed region, overlapped across 8 groups of clouds, one stream each
   roofline    of the dominant kernel (knn_lowd_kernel, FP32-pipe bound): 8 flop per
               (query, point) pair / its CUDA-event time when launched alone through the C ABI
   cpu_baseline  the reference's own CPU path (oracle/_ref: kd-tree search, single thread)
@@ -404,8 +404,8 @@ def run_ours(args, rank, world, local_rank):
         "e2e": {"value": total_queries * args.steps / (ms_e2e * 1e-3), "unit": "queries/s",
                 # the points and the per-group segment pointers go up (the batch vector is only read on the
                 # host), the edge rows and one flag per group come down
-                "h2d_bytes_per_step": hx.numel() * 4 + (w["clouds"] + 4) * 8,
-                "d2h_bytes_per_step": 2 * edges * 8 + 4 * 4},
+                "h2d_bytes_per_step": hx.numel() * 4 + (w["clouds"] + 8) * 8,
+                "d2h_bytes_per_step": 2 * edges * 8 + 8 * 4},
         # per knn_graph call: segment_ptr and the kNN kernel, which writes the final edge rows itself
         "gpu_launches": 2 * args.steps,
         "clocks": clocks.summary(),

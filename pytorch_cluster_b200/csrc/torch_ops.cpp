@@ -7,6 +7,7 @@
 // error here, not a fallback.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <ATen/cuda/CUDAEvent.h>
 #include <torch/script.h>
 
 #include "b200_cluster.h"
@@ -289,6 +290,86 @@ torch::Tensor fps(torch::Tensor src, torch::Tensor ptr, torch::Tensor ratio, boo
   return out;
 }
 
+// knn_graph from host memory to host memory for low-dimensional points (loop = False): the call is cut
+// into groups of whole segments, one stream each, so that uploads and downloads of the other groups
+// overlap the search of a group and the block scheduler keeps the SMs filled across the groups'
+// kernels.  x: CPU [n, dim] (pinned for overlap); ptr: CPU int64 [B + 1]; out: CPU int64 [2, n * k]
+// (pinned).  Returns the number of irregular queries (see b200c_knn_graph): 0 means `out` is final.
+int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool source_to_target, torch::Tensor out,
+                       int64_t num_groups, int64_t device_index) {
+  TORCH_CHECK(!x.is_cuda() && !ptr.is_cuda() && !out.is_cuda(), "knn_graph_host expects host tensors");
+  CHECK_CONTIGUOUS(x);
+  CHECK_INPUT(x.dim() == 2 && ptr.dim() == 1 && ptr.numel() >= 2);
+  TORCH_CHECK(ptr.scalar_type() == at::kLong && out.scalar_type() == at::kLong, "ptr and out must be int64 tensors");
+  const int64_t n = x.size(0), dim = x.size(1), segs = ptr.numel() - 1, total = n * k;
+  TORCH_CHECK(out.is_contiguous() && out.dim() == 2 && out.size(0) == 2 && out.size(1) == total,
+              "out must be a contiguous [2, n * k] tensor");
+  const int dtype = dtype_code(x);
+  TORCH_CHECK(dtype == B200C_F32 || dtype == B200C_F64, "knn_graph_host covers float and double points");
+  if (n == 0) return 0;
+  const int64_t *p = ptr.data_ptr<int64_t>();
+  TORCH_CHECK(p[0] == 0 && p[segs] == n, "Input mismatch");
+
+  // groups of consecutive segments with about equal numbers of (query, point) pairs
+  num_groups = std::max<int64_t>(1, std::min<int64_t>(num_groups, segs));
+  double all = 0;
+  for (int64_t b = 0; b < segs; ++b) all += (double)(p[b + 1] - p[b]) * (double)(p[b + 1] - p[b]);
+  std::vector<int64_t> cut{0};
+  double acc = 0;
+  for (int64_t b = 0; b < segs; ++b) {
+    acc += (double)(p[b + 1] - p[b]) * (double)(p[b + 1] - p[b]);
+    if ((int64_t)cut.size() < num_groups && acc >= all * (double)cut.size() / (double)num_groups && b + 1 < segs)
+      cut.push_back(b + 1);
+  }
+  cut.push_back(segs);
+  const int64_t groups = (int64_t)cut.size() - 1;
+
+  c10::cuda::CUDAGuard guard((c10::DeviceIndex)device_index);
+  const auto dopts = torch::TensorOptions().device(torch::kCUDA, (c10::DeviceIndex)device_index);
+  const size_t elem = dtype == B200C_F64 ? 8 : 4;
+  auto x_dev = torch::empty({n, dim}, dopts.dtype(x.scalar_type()));
+  auto edges_dev = torch::empty({2, total}, dopts.dtype(torch::kLong));
+  auto flags_dev = torch::empty({groups}, dopts.dtype(torch::kInt));
+  auto ptr_dev = torch::empty({segs + groups}, dopts.dtype(torch::kLong));
+  // every group's own pointers (starting at 0), back to back, and the flags coming back: pinned
+  auto small = torch::empty({segs + groups + groups}, torch::TensorOptions().dtype(torch::kLong).pinned_memory(true));
+  int64_t *local = small.data_ptr<int64_t>();
+  int32_t *flags_host = reinterpret_cast<int32_t *>(local + segs + groups);
+  int64_t off = 0;
+  for (int64_t g = 0; g < groups; ++g)
+    for (int64_t b = cut[g]; b <= cut[g + 1]; ++b) local[off++] = p[b] - p[cut[g]];
+
+  auto current = at::cuda::getCurrentCUDAStream();
+  C10_CUDA_CHECK(cudaMemcpyAsync(ptr_dev.data_ptr(), local, (size_t)off * 8, cudaMemcpyHostToDevice, current.stream()));
+  at::cuda::CUDAEvent ready;
+  ready.record(current);  // the buffers above, and the pointers, belong to the current stream
+  std::vector<at::cuda::CUDAStream> streams;
+  const char *xh = (const char *)x.data_ptr();
+  char *xd = (char *)x_dev.data_ptr();
+  int64_t *ed = edges_dev.data_ptr<int64_t>(), *oh = out.data_ptr<int64_t>();
+  off = 0;
+  for (int64_t g = 0; g < groups; ++g) {
+    streams.push_back(at::cuda::getStreamFromPool(false, (c10::DeviceIndex)device_index));
+    cudaStream_t st = streams.back().stream();
+    ready.block(streams.back());
+    const int64_t r0 = p[cut[g]], r1 = p[cut[g + 1]], nseg = cut[g + 1] - cut[g];
+    C10_CUDA_CHECK(cudaMemcpyAsync(xd + r0 * dim * elem, xh + r0 * dim * elem, (size_t)(r1 - r0) * dim * elem,
+                                   cudaMemcpyHostToDevice, st));
+    check_status(b200c_knn_graph_part(xd + r0 * dim * elem, ptr_dev.data_ptr<int64_t>() + off, nseg, r1 - r0, dim, k,
+                                      dtype, source_to_target ? 1 : 0, r0, ed + r0 * k, total,
+                                      flags_dev.data_ptr<int32_t>() + g, st));
+    C10_CUDA_CHECK(cudaMemcpyAsync(oh + r0 * k, ed + r0 * k, (size_t)(r1 - r0) * k * 8, cudaMemcpyDeviceToHost, st));
+    C10_CUDA_CHECK(cudaMemcpyAsync(oh + total + r0 * k, ed + total + r0 * k, (size_t)(r1 - r0) * k * 8,
+                                   cudaMemcpyDeviceToHost, st));
+    C10_CUDA_CHECK(cudaMemcpyAsync(flags_host + g, flags_dev.data_ptr<int32_t>() + g, 4, cudaMemcpyDeviceToHost, st));
+    off += nseg + 1;
+  }
+  for (auto &s : streams) s.synchronize();
+  int64_t irregular = 0;
+  for (int64_t g = 0; g < groups; ++g) irregular += flags_host[g];
+  return irregular;
+}
+
 }  // namespace
 
 static auto registry = torch::RegisterOperators()
@@ -297,4 +378,5 @@ static auto registry = torch::RegisterOperators()
                            .op("torch_cluster::segment_ptr", &segment_ptr)
                            .op("torch_cluster::knn_graph_edges", &knn_graph_edges)
                            .op("torch_cluster::nearest", &nearest)
-                           .op("torch_cluster::fps", &fps);
+                           .op("torch_cluster::fps", &fps)
+                           .op("torch_cluster::knn_graph_host", &knn_graph_host);

@@ -2,8 +2,9 @@
 
 The reference's functions take device tensors; a caller whose points and result live on the host
 pays the copies around them one after the other.  ``knn_graph_host`` cuts the call into groups of
-whole batch segments and runs them on two CUDA streams, so that the upload of group i + 1 and the
-download of group i - 1 overlap the search of group i (``b200c_knn_graph_part`` writes each group's
+whole batch segments, one CUDA stream each, so that the uploads and downloads of the other groups
+overlap the search of a group, while the block scheduler keeps the SMs filled across the groups'
+kernels (``b200c_knn_graph_part`` writes each group's
 edges, with global row numbers, straight into its slice of the device-side result).  The result
 equals ``knn_graph(x.cuda(), k, batch.cuda(), loop=False, flow=flow).cpu()`` exactly.
 
@@ -13,27 +14,13 @@ pushed out of their own list by duplicates), takes the ordinary route through ``
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Optional
 
 import torch
 
-from . import _native
 from .knn import knn_graph
-from .sharded import balanced_ranges
 
-_DTYPES = {torch.float32: _native.B200C_F32, torch.float64: _native.B200C_F64}
-
-
-class _Pipeline:
-    """Streams and small pinned buffers reused between calls on a device."""
-
-    def __init__(self, device: torch.device):
-        self.streams = [torch.cuda.Stream(device), torch.cuda.Stream(device)]
-        self.flags_host: Optional[torch.Tensor] = None
-        self.ptrs_host: Optional[torch.Tensor] = None
-
-
-_pipelines: dict = {}
+_DTYPES = (torch.float32, torch.float64)
 
 
 def _segment_ptr_host(batch: Optional[torch.Tensor], rows: int, batch_size: Optional[int]) -> torch.Tensor:
@@ -47,7 +34,7 @@ def _segment_ptr_host(batch: Optional[torch.Tensor], rows: int, batch_size: Opti
 def knn_graph_host(x: torch.Tensor, k: int, batch: Optional[torch.Tensor] = None, loop: bool = False,
                    flow: str = 'source_to_target', cosine: bool = False, batch_size: Optional[int] = None,
                    device: Optional[torch.device] = None, out: Optional[torch.Tensor] = None,
-                   num_groups: int = 4) -> torch.Tensor:
+                   num_groups: int = 8) -> torch.Tensor:
     """``knn_graph`` for host tensors.  x: [N, D] CPU tensor (pinned for overlap), batch: sorted CPU
     int64 [N] or None.  Returns a pinned CPU int64 [2, E] tensor (``out`` is used when it has the
     right shape)."""
@@ -70,51 +57,11 @@ def knn_graph_host(x: torch.Tensor, k: int, batch: Optional[torch.Tensor] = None
         return ordinary()
 
     ptr = _segment_ptr_host(batch, n, batch_size)
-    sizes = (ptr[1:] - ptr[:-1]).tolist()
-    groups: List = [g for g in balanced_ranges([s * s for s in sizes], max(1, min(num_groups, len(sizes)))) if g[1] > g[0]]
-    pipe = _pipelines.setdefault(device, _Pipeline(device))
-    lib = _native.cabi()
-    s2t = int(flow == 'source_to_target')
-    total = n * k
-
-    res = out if out is not None and tuple(out.shape) == (2, total) and out.is_pinned() else \
-        torch.empty(2, total, dtype=torch.long).pin_memory()
-    if pipe.flags_host is None or pipe.flags_host.numel() < len(groups):
-        pipe.flags_host = torch.empty(max(8, len(groups)), dtype=torch.int32).pin_memory()
-    # every group's own pointers (starting at 0), back to back in one pinned buffer
-    count = sum(s1 - s0 + 1 for s0, s1 in groups)
-    if pipe.ptrs_host is None or pipe.ptrs_host.numel() < count:
-        pipe.ptrs_host = torch.empty(max(1024, count), dtype=torch.long).pin_memory()
-    off = 0
-    for s0, s1 in groups:
-        torch.sub(ptr[s0:s1 + 1], ptr[s0], out=pipe.ptrs_host[off:off + s1 - s0 + 1])
-        off += s1 - s0 + 1
-    with torch.cuda.device(device):
-        x_dev = torch.empty(n, dim, dtype=x.dtype, device=device)
-        ptr_dev = torch.empty(count, dtype=torch.long, device=device)
-        ptr_dev.copy_(pipe.ptrs_host[:count], non_blocking=True)
-        edges_dev = torch.empty(2, total, dtype=torch.long, device=device)
-        flags_dev = torch.empty(len(groups), dtype=torch.int32, device=device)
-        start = torch.cuda.Event()
-        start.record()  # the buffers above, and the copy of the pointers, belong to the current stream
-        ptr_off = 0
-        for gi, (s0, s1) in enumerate(groups):
-            stream = pipe.streams[gi & 1]
-            r0, r1 = int(ptr[s0]), int(ptr[s1])
-            nseg = s1 - s0
-            with torch.cuda.stream(stream):
-                stream.wait_event(start)
-                x_dev[r0:r1].copy_(x[r0:r1], non_blocking=True)
-                local = ptr_dev[ptr_off:ptr_off + nseg + 1]
-                _native.check(lib.b200c_knn_graph_part(
-                    x_dev[r0:].data_ptr(), local.data_ptr(), nseg, r1 - r0, dim, k, _DTYPES[x.dtype], s2t, r0,
-                    edges_dev[0, r0 * k:].data_ptr(), total, flags_dev[gi:].data_ptr(), stream.cuda_stream))
-                res[0, r0 * k:r1 * k].copy_(edges_dev[0, r0 * k:r1 * k], non_blocking=True)
-                res[1, r0 * k:r1 * k].copy_(edges_dev[1, r0 * k:r1 * k], non_blocking=True)
-                pipe.flags_host[gi:gi + 1].copy_(flags_dev[gi:gi + 1], non_blocking=True)
-            ptr_off += nseg + 1
-        for stream in pipe.streams:
-            stream.synchronize()
-    if int(pipe.flags_host[:len(groups)].sum()) != 0:
+    res = out if out is not None and tuple(out.shape) == (2, n * k) and out.is_contiguous() else \
+        torch.empty(2, n * k, dtype=torch.long).pin_memory()
+    irregular = torch.ops.torch_cluster.knn_graph_host(x, ptr, k, flow == 'source_to_target', res, num_groups,
+                                                       device.index if device.index is not None else
+                                                       torch.cuda.current_device())
+    if irregular != 0:
         return ordinary()  # some query does not have the regular shape: the general route handles it
     return res
