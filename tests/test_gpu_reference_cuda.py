@@ -161,44 +161,49 @@ def _ms(fn, reps=3):
 
 def test_time_beside_reference_kernels():
     """Operator-level time (CUDA events, whole op call incl. its compaction) of the reference's CUDA
-    path and of this library on the same tensors.  A report, not a threshold — except that the
-    product must not be slower."""
+    path and of this library on the same tensors, at the full sizes of the benchmark's workloads;
+    the two results are also compared (identical tensors).  The timing is a report, not a
+    threshold — except that the product must not be slower."""
     rep = {}
+
+    def both(name, ref_fn, our_fn, ref_reps=3):
+        _same(our_fn(), ref_fn())
+        rep[name] = (_ms(ref_fn, ref_reps), _ms(our_fn))
+
     g = torch.Generator().manual_seed(2)
     x = torch.randn(32 * 4096, 3, generator=g).to(DEV)
     p = _ptr(32, 4096)
-    rep["knn_32x4096x3_k21"] = (_ms(lambda: refc.knn(x, x, p, p, 21)), _ms(lambda: _ours_knn(x, x, p, p, 21)))
+    both("knn_32x4096x3_k21", lambda: refc.knn(x, x, p, p, 21), lambda: _ours_knn(x, x, p, p, 21))
     g = torch.Generator().manual_seed(3)
     xb = (100 * torch.rand(8 * 131072, 3, generator=g)).to(DEV)
     yb = (100 * torch.rand(8 * 8192, 3, generator=g)).to(DEV)
     pxb, pyb = _ptr(8, 131072), _ptr(8, 8192)
-    rep["knn_8x131072x8192x3_k32"] = (_ms(lambda: refc.knn(xb, yb, pxb, pyb, 32), 1),
-                                      _ms(lambda: _ours_knn(xb, yb, pxb, pyb, 32)))
+    both("knn_8x131072x8192x3_k32", lambda: refc.knn(xb, yb, pxb, pyb, 32), lambda: _ours_knn(xb, yb, pxb, pyb, 32), 1)
     g = torch.Generator().manual_seed(4)
     xf = torch.randn(16 * 2048, 64, generator=g).to(DEV)
     pf = _ptr(16, 2048)
     for cosine in (False, True):
-        rep[f"knn_16x2048x64_k21_cosine{int(cosine)}"] = (_ms(lambda: refc.knn(xf, xf, pf, pf, 21, cosine)),
-                                                         _ms(lambda: _ours_knn(xf, xf, pf, pf, 21, cosine)))
+        both(f"knn_16x2048x64_k21_cosine{int(cosine)}", lambda: refc.knn(xf, xf, pf, pf, 21, cosine),
+             lambda: _ours_knn(xf, xf, pf, pf, 21, cosine))
     xr = _mixture(64, 8192)
     pr = _ptr(64, 8192)
-    rep["radius_64x8192x3_r0.05_max64"] = (_ms(lambda: refc.radius(xr, xr, pr, pr, 0.05, 64, True)),
-                                           _ms(lambda: _ours_radius(xr, xr, pr, pr, 0.05, 64, True)))
+    both("radius_64x8192x3_r0.05_max64", lambda: refc.radius(xr, xr, pr, pr, 0.05, 64, True),
+         lambda: _ours_radius(xr, xr, pr, pr, 0.05, 64, True))
     # max_num_neighbors = 8192 on all 64 clouds would make the reference allocate 2 x 34 GB of padded
     # output plus masks; it is timed on 8 clouds instead
     xs, ps = xr[: 8 * 8192].contiguous(), _ptr(8, 8192)
-    rep["radius_8x8192x3_r0.05_max8192"] = (_ms(lambda: refc.radius(xs, xs, ps, ps, 0.05, 8192, True)),
-                                            _ms(lambda: _ours_radius(xs, xs, ps, ps, 0.05, 8192, True)))
+    both("radius_8x8192x3_r0.05_max8192", lambda: refc.radius(xs, xs, ps, ps, 0.05, 8192, True),
+         lambda: _ours_radius(xs, xs, ps, ps, 0.05, 8192, True))
     # nearest: every point of the 64 clouds to the closest of 2048 samples of its cloud; fps: 25 % of
     # every cloud, first point first
     from pytorch_cluster_b200 import cabi  # noqa: F401  (loads the operators)
     ys = torch.cat([xr[c * 8192: c * 8192 + 2048] for c in range(64)]).contiguous()
     pys = _ptr(64, 2048)
-    rep["nearest_64x8192_to_2048x3"] = (_ms(lambda: refc.nearest(xr, ys, pr, pys)),
-                                        _ms(lambda: torch.ops.torch_cluster.nearest(xr, ys, pr, pys)))
+    both("nearest_64x8192_to_2048x3", lambda: refc.nearest(xr, ys, pr, pys),
+         lambda: torch.ops.torch_cluster.nearest(xr, ys, pr, pys))
     ratio = torch.tensor(0.25, device=DEV)
-    rep["fps_64x8192x3_ratio0.25"] = (_ms(lambda: refc.fps(xr, pr, ratio, False), 1),
-                                      _ms(lambda: torch.ops.torch_cluster.fps(xr, pr, ratio, False)))
+    both("fps_64x8192x3_ratio0.25", lambda: refc.fps(xr, pr, ratio, False),
+         lambda: torch.ops.torch_cluster.fps(xr, pr, ratio, False), 1)
     out = {k: {"reference_cuda_ms": round(a, 4), "this_library_ms": round(b, 4), "ratio": round(a / b, 2)}
            for k, (a, b) in rep.items()}
     print(json.dumps(out, indent=1))
