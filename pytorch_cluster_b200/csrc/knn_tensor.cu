@@ -42,7 +42,6 @@ constexpr int TC_COLS = TC_N / TC_PARTS;
 constexpr int TC_GH = 16;        // group minima kept per thread: 64 per query
 constexpr int TC_CAP = 128;      // candidates kept per query: two lists of 64, each filled from both ends
 constexpr int TC_THREADS = TC_M * TC_PARTS;
-constexpr int TC_SQX_SLOTS = 3;
 constexpr int TC_SPIN_LIMIT = 1 << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -174,6 +173,7 @@ struct TensorArgs {
   int32_t *cand;               // [m, TC_CAP]
   int32_t *cand_count;         // [m]; four 8-bit counts: list A front, A back, list B front, B back
   int *error_flag;
+  int ring;                    // point tiles held in shared memory: 2 or 4
 };
 
 template <bool COSINE>
@@ -187,9 +187,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
   const int dim = a.dim;
   const uint32_t tile_bytes = (uint32_t)((dim + 31) >> 5) * 16384u;  // whole atoms of 32 features
   unsigned char *sQ = smem;
-  unsigned char *sX = smem + tile_bytes;                             // ring of two point tiles
-  float *s_sqx = reinterpret_cast<float *>(smem + 3 * tile_bytes);   // |x|^2 per column, ring of three tiles
-  float *gmin = s_sqx + TC_SQX_SLOTS * TC_N;                         // [TC_M][64] group minima, see gmin_slot
+  const int ring = a.ring, ahead = ring - 1, sqx_slots = ring + 1;
+  unsigned char *sX = smem + tile_bytes;                                      // ring of point tiles
+  float *s_sqx = reinterpret_cast<float *>(smem + (1 + ring) * tile_bytes);   // |x|^2 per column, ring + 1 tiles
+  float *gmin = s_sqx + sqx_slots * TC_N;                                     // [TC_M][64] group minima, see gmin_slot
   __shared__ __align__(8) uint64_t mbar[2];
   __shared__ uint32_t tmem_base_s;
 
@@ -253,19 +254,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
 
     // Software pipeline over the 2 * ntiles steps (pass A then pass B over the same tiles): in
     // iteration s the tensor core works on step s while the threads read back step s - 1 and the
-    // copies of step s + 1 are in flight.  Point tile of step s: ring slot s & 1; accumulator:
-    // TMEM columns (s & 1) * 128 ..; |x|^2 of its columns: slot s % 3.
+    // copies of steps s + 1 .. s + ring - 1 are in flight.  Point tile of step s: ring slot
+    // s % ring; accumulator: TMEM columns (s & 1) * 128 ..; |x|^2 of its columns: slot
+    // s % (ring + 1).  Every iteration commits exactly one copy group (possibly empty), so that
+    // "all but the newest ring - 2 groups" always means "step s has landed".
     const int nsteps = 2 * ntiles;
+    auto stage_step = [&](int step) {
+      if (step < nsteps) {
+        const int t1 = step < ntiles ? step : step - ntiles;
+        const int64_t p1 = x_lo + (int64_t)t1 * TC_N;
+        stage_operand(sX + (uint32_t)(step % ring) * tile_bytes, a.xa, p1, x_hi, dim, tid);
+        if (tid < TC_N)
+          s_sqx[(step % sqx_slots) * TC_N + tid] =
+              p1 + tid < x_hi ? (COSINE ? 0.f : a.sq_x[p1 + tid]) : pos_inf<float>();
+      }
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
     stage_operand(sQ, a.ya, q_lo, q_hi, dim, tid);  // joins the first point tile's copy group
-    stage_operand(sX, a.xa, x_lo, x_hi, dim, tid);
-    if (tid < TC_N) s_sqx[tid] = x_lo + tid < x_hi ? (COSINE ? 0.f : a.sq_x[x_lo + tid]) : pos_inf<float>();
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    for (int step = 0; step < ahead; ++step) stage_step(step);
 
     float thr = 0.f, run_min = pos_inf<float>();
     int group = 0, in_group = 0, ncand = 0;
     for (int s = 0; s <= nsteps; ++s) {
       if (s < nsteps) {
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        if (ahead == 1)
+          asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        else
+          asm volatile("cp.async.wait_group 2;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -277,7 +292,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (s < nsteps && tid == 0) {
-        const uint32_t sx = smem_u32(sX) + (uint32_t)(s & 1) * tile_bytes;
+        const uint32_t sx = smem_u32(sX) + (uint32_t)(s % ring) * tile_bytes;
         const uint32_t acc = tmem + (uint32_t)(s & 1) * TC_N;
         for (int ks = 0; ks < (dim >> 3); ++ks) {
           const uint32_t off = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
@@ -305,22 +320,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
           phase0 ^= 1u;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       }
-      if (s + 1 < nsteps && ok) {
-        const int t1 = s + 1 < ntiles ? s + 1 : s + 1 - ntiles;
-        const int64_t p1 = x_lo + (int64_t)t1 * TC_N;
-        stage_operand(sX + (uint32_t)((s + 1) & 1) * tile_bytes, a.xa, p1, x_hi, dim, tid);
-        if (tid < TC_N)
-          s_sqx[((s + 1) % TC_SQX_SLOTS) * TC_N + tid] =
-              p1 + tid < x_hi ? (COSINE ? 0.f : a.sq_x[p1 + tid]) : pos_inf<float>();
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-      }
+      // the slot of step s - 1 is free again: it takes step s + ring - 1
+      if (ok) stage_step(s + ahead);
       if (s >= 1 && ok) {
         // read back step s - 1: this thread's 32 columns of its query's row
         const int e = s - 1;
         const int pass = e >= ntiles ? 1 : 0;
         const int t = e - pass * ntiles;
         const int64_t p0 = x_lo + (int64_t)t * TC_N + part * TC_COLS;
-        const float *sqx = s_sqx + (e % TC_SQX_SLOTS) * TC_N + part * TC_COLS;
+        const float *sqx = s_sqx + (e % sqx_slots) * TC_N + part * TC_COLS;
         uint32_t v[32];
         tmem_load32(my_taddr + (uint32_t)(e & 1) * TC_N, v);
         constexpr int c0 = 0;
@@ -586,9 +594,18 @@ __global__ void tensor_prep_kernel(const float *__restrict__ a, int64_t rows, in
     for (int d = 0; d < dim; ++d) normalised[i * dim + d] = a[i * dim + d] / nrm;
 }
 
-// query tile + ring of two point tiles + |x|^2 ring + group minima + alignment slack
-size_t knn_tensor_smem_bytes(int dim) {
-  return 3 * (size_t)((dim + 31) / 32) * 16384 + (size_t)TC_SQX_SLOTS * TC_N * 4 + (size_t)TC_GH * TC_THREADS * 4 + 1024;
+// query tile + ring of point tiles + |x|^2 ring + group minima + alignment slack
+size_t knn_tensor_smem_bytes(int dim, int ring) {
+  return (size_t)(1 + ring) * ((dim + 31) / 32) * 16384 + (size_t)(ring + 1) * TC_N * 4 + (size_t)TC_GH * TC_THREADS * 4 +
+         1024;
+}
+
+// Point tiles held in shared memory.  The kernel also runs with four (they fit up to 64 features), but
+// three tiles of look-ahead measured slower than one on 16 x 2048 x 64 (148 us against 129 us): the
+// step is not waiting for its copies.
+int knn_tensor_ring(int dim) {
+  (void)dim;
+  return 2;
 }
 
 static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
@@ -667,8 +684,8 @@ int launch_knn_tensor_f32(const KnnArgs &a, void *workspace) {
   }
 
   TensorArgs t{a.cosine ? xhat : (const float *)a.x, a.cosine ? yhat : (const float *)a.y, sq_x, sq_y, xmax,
-               a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, cand, cand_count, error_flag};
-  const size_t smem = knn_tensor_smem_bytes(a.dim);
+               a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, cand, cand_count, error_flag, knn_tensor_ring(a.dim)};
+  const size_t smem = knn_tensor_smem_bytes(a.dim, t.ring);
   const unsigned ctas = (unsigned)((a.m + TC_M - 1) / TC_M);
   if (a.cosine) {
     B200C_CUDA(cudaFuncSetAttribute(knn_tensor_candidates_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
