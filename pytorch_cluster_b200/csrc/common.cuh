@@ -36,6 +36,21 @@ void set_error(const char *fmt, ...);
     }                                                                           \
   } while (0)
 
+// Opt a kernel in to `bytes` of dynamic shared memory on the current device.  The attribute belongs
+// to the (function, device) pair, so it is set once per device: `done` is the caller's bit mask of
+// devices already configured (one static per kernel instantiation; a lost update only repeats an
+// idempotent call).
+template <typename Kern>
+static inline cudaError_t opt_in_shared_memory(Kern kern, size_t bytes, unsigned long long &done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && ((done >> dev) & 1ull)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && dev < 64) done |= 1ull << dev;
+  return e;
+}
+
 #define B200C_LAUNCH_CHECK(name)                                                \
   do {                                                                          \
     cudaError_t e__ = cudaGetLastError();                                       \

@@ -218,11 +218,8 @@ template <typename T, int RND, int DIM = 0, int PT = 1>
 static int launch_fps_t(const void *src, const int64_t *ptr, const int64_t *out_ptr, const int64_t *start,
                         int64_t num_segments, int dim, void *dist, int64_t *out, cudaStream_t stream) {
   auto kern = fps_kernel<T, RND, DIM, PT>;
-  static bool configured = false;
-  if (!configured) {
-    B200C_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FPS_SMEM_BUDGET));
-    configured = true;
-  }
+  static unsigned long long configured = 0ull;  // devices on which the shared-memory opt-in is done
+  B200C_CUDA(opt_in_shared_memory(kern, FPS_SMEM_BUDGET, configured));
   // points of (dim + 1) values each, planes padded to 4 elements
   const int64_t capacity = (int64_t)(FPS_SMEM_BUDGET / sizeof(T) - 4 * (size_t)dim) / (dim + 1);
   kern<<<(unsigned)num_segments, FPS_THREADS, FPS_SMEM_BUDGET, stream>>>(

@@ -11,11 +11,8 @@ static int launch_generic_one(const KnnArgs *ka, const RadiusArgs *ra) {
   using S = GenSmem<T, KP>;
   using G = GenD<T>;
   auto kern = generic_kernel<T, MODE, KP, COSINE, RND>;
-  static bool configured = false;
-  if (!configured) {
-    B200C_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES));
-    configured = true;
-  }
+  static unsigned long long configured = 0ull;  // devices on which the shared-memory opt-in is done
+  B200C_CUDA(opt_in_shared_memory(kern, S::SMEM_BYTES, configured));
   const int64_t m = ka ? ka->m : ra->m;
   const int64_t tiles = (m + G::TQ - 1) / G::TQ;
   if (tiles > 0x7fffffffLL) {

@@ -10,12 +10,8 @@ template <typename T, int DIM, int KP>
 static int launch_knn_lowd_one(const KnnArgs &a) {
   using Cfg = KnnLowD<T, DIM, KP>;
   auto kern = knn_lowd_kernel<T, DIM, KP>;
-  static bool configured = false;  // per instantiation; benign race (idempotent call)
-  if (!configured) {
-    B200C_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)Cfg::SMEM_BYTES));
-    configured = true;
-  }
+  static unsigned long long configured = 0ull;  // devices on which the shared-memory opt-in is done
+  B200C_CUDA(opt_in_shared_memory(kern, Cfg::SMEM_BYTES, configured));
   const int64_t tiles = (a.m + Cfg::TQ - 1) / Cfg::TQ;
   if (tiles > 0x7fffffffLL) {
     set_error("too many query tiles");

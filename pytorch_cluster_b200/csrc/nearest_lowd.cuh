@@ -152,11 +152,8 @@ template <typename T, int DIM>
 static int launch_nearest_lowd_one(const KnnArgs &a) {
   using Cfg = NearestLowD<T, DIM>;
   auto kern = nearest_lowd_kernel<T, DIM>;
-  static bool configured = false;
-  if (!configured) {
-    B200C_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM_BYTES));
-    configured = true;
-  }
+  static unsigned long long configured = 0ull;  // devices on which the shared-memory opt-in is done
+  B200C_CUDA(opt_in_shared_memory(kern, Cfg::SMEM_BYTES, configured));
   const int64_t tiles = (a.m + Cfg::TQ - 1) / Cfg::TQ;
   if (tiles > 0x7fffffffLL) {
     set_error("too many row tiles");

@@ -48,3 +48,26 @@ def test_sharded_equals_single_gpu(tmp_path):
     for rank in range(world):
         res = torch.load(os.path.join(tmp_path, f"rank{rank}.pt"))
         assert res["ok"] and res["edges"] > 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_two_devices():
+    """One process using both GPUs in turn: launch configuration (the shared-memory opt-in of every
+    kernel) is per device, and results do not depend on the device."""
+    import pytorch_cluster_b200 as pc
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(6000, 3, generator=g)
+    f = torch.randn(4096, 64, generator=g)
+    batch = torch.arange(3).repeat_interleave(2000)
+    res = []
+    for d in ("cuda:0", "cuda:1", "cuda:0"):
+        xd, bd, fd = x.to(d), batch.to(d), f.to(d)
+        samples = pc.fps(xd, bd, ratio=0.1, random_start=False)
+        res.append([t.cpu() for t in (
+            pc.knn_graph(xd, 12, bd), pc.radius_graph(xd, 0.2, bd, max_num_neighbors=40),
+            pc.knn(fd, fd, 9), pc.knn(fd, fd, 9, cosine=True), samples, pc.nearest(xd, xd[samples], bd, bd[samples]),
+            pc.knn_graph_host(x, 12, batch, device=torch.device(d)))])
+    for other in res[1:]:
+        for a, b in zip(res[0], other):
+            assert torch.equal(a, b)
