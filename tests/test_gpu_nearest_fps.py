@@ -143,6 +143,20 @@ def test_fps_cabi(dim, dt):
     assert np.array_equal(got, orc.fps(_np(x), ptr.numpy(), out_ptr.numpy(), start.numpy(), round16=_kind(dt)))
 
 
+def test_fps_segment_in_shared_memory():
+    """10000 three-dimensional fp32 points: too many for the register-resident path (8192), few
+    enough for the shared-memory one; beside it segments of 1, 2 and 8192 points, ratio 1."""
+    from pytorch_cluster_b200 import cabi
+
+    g = torch.Generator().manual_seed(14)
+    sizes = [10000, 1, 2, 8192]
+    x = torch.randn(sum(sizes), 3, generator=g)
+    ptr = _ptr(sizes)
+    for out_ptr in (torch.tensor([0, 500, 501, 503, 903]), torch.tensor([0, 1, 2, 3, 4])):
+        got = cabi.fps(x.to(DEV), ptr.to(DEV), out_ptr.to(DEV)).cpu().numpy()
+        assert np.array_equal(got, orc.fps(x.numpy(), ptr.numpy(), out_ptr.numpy()))
+
+
 @pytest.mark.parametrize("dt", ["f32", "f64"])
 def test_fps_segment_larger_than_shared_memory(dt):
     """30000 three-dimensional points do not fit on chip: the kernel runs that segment from
