@@ -202,6 +202,31 @@ int b200c_radius_fill(const void *x, const void *y, const int64_t *ptr_x,
                       int64_t num_edges, int64_t *edge_index, void *workspace,
                       size_t workspace_bytes, b200c_stream_t stream);
 
+/* Fixed-radius search that evaluates every pair once, for neighbour caps too large for the one-pass
+ * mode above (fp32 / fp64, up to 8 features): pass 1 counts like b200c_radius_count and also stores one
+ * hit bit per (query, point) in a bit matrix in the workspace; pass 2 writes the edges from those bits
+ * (an HBM-bound kernel) instead of scanning the points again.  Same results as count + fill.
+ *
+ * The matrix's size depends on the segment sizes, so the caller hands over host copies of the segment
+ * pointers (ptr_x_host, ptr_y_host: int64 [num_segments + 1] in host memory; NULL with ptr_x == NULL
+ * for one segment): b200c_radius_mask_workspace_bytes gives the size (0 = not applicable), pass 1
+ * checks it.  Rows: a query of a segment with n_b points owns ceil(n_b / c) * c / 32 words, c being the
+ * scan's chunk (1024 points for 3-D fp32).  No counterpart in the reference, which evaluates once but
+ * pads its output to max_num_neighbors slots per query. */
+size_t b200c_radius_mask_workspace_bytes(const int64_t *ptr_x_host, const int64_t *ptr_y_host,
+                                         int64_t num_segments, int64_t n, int64_t m, int64_t dim,
+                                         int dtype);
+int b200c_radius_count_masks(const void *x, const void *y, const int64_t *ptr_x,
+                             const int64_t *ptr_y, const int64_t *ptr_x_host,
+                             const int64_t *ptr_y_host, int64_t num_segments, int64_t n,
+                             int64_t m, int64_t dim, double r, int64_t max_num_neighbors,
+                             int ignore_same_index, int dtype, int32_t *counts,
+                             void *workspace, size_t workspace_bytes, b200c_stream_t stream);
+int b200c_radius_fill_masks(const int64_t *ptr_x, const int64_t *ptr_y, int64_t num_segments,
+                            int64_t n, int64_t m, int64_t dim, int dtype,
+                            const int32_t *counts, const int64_t *offsets, int64_t num_edges,
+                            int64_t *edge_index, const void *workspace, b200c_stream_t stream);
+
 /* Nearest point assignment — replaces nearest_kernel + nearest_cuda
  * (csrc/cuda/nearest_cuda.cu:9-61, 63-88).
  *

@@ -146,3 +146,26 @@ def knn_graph(x, k, ptr=None, source_to_target=True):
     _native.check(lib.b200c_knn_graph(_p(x), _p(ptr), nseg, n, dim, k, _dtype(x), int(source_to_target), _p(out),
                                       _p(irregular), _stream()))
     return out, int(irregular.item())
+
+
+def radius_masks(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_index=False):
+    """Radius search through the bit-matrix entry points (b200c_radius_count_masks / _fill_masks)."""
+    lib = _native.cabi()
+    n, m, dim = x.shape[0], y.shape[0], x.shape[1]
+    nseg = 1 if ptr_x is None else ptr_x.numel() - 1
+    hx = None if ptr_x is None else ptr_x.cpu()
+    hy = None if ptr_y is None else ptr_y.cpu()
+    nbytes = lib.b200c_radius_mask_workspace_bytes(_p(hx), _p(hy), nseg, n, m, dim, _dtype(x))
+    if nbytes == 0:
+        raise RuntimeError("bit-matrix radius search not applicable")
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    counts = torch.empty(m, dtype=torch.int32, device=x.device)
+    _native.check(lib.b200c_radius_count_masks(_p(x), _p(y), _p(ptr_x), _p(ptr_y), _p(hx), _p(hy), nseg, n, m, dim,
+                                               float(r), max_num_neighbors, int(ignore_same_index), _dtype(x),
+                                               _p(counts), _p(ws), nbytes, _stream()))
+    offsets = exclusive_scan(counts)
+    total = int(offsets[-1].item())
+    out = torch.empty(2, total, dtype=torch.long, device=x.device)
+    _native.check(lib.b200c_radius_fill_masks(_p(ptr_x), _p(ptr_y), nseg, n, m, dim, _dtype(x), _p(counts), _p(offsets),
+                                              total, _p(out), _p(ws), _stream()))
+    return out

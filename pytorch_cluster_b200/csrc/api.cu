@@ -3,6 +3,7 @@
 // checked on raw pointers) and kernel selection.
 #include <cstdarg>
 #include <cstdio>
+#include <vector>
 
 #include "common.cuh"
 #include "launchers.h"
@@ -266,6 +267,80 @@ extern "C" int b200c_radius_fill(const void *x, const void *y, const int64_t *pt
   return radius_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
                        ignore_same_index, dtype, (int32_t *)counts, offsets, edge_index,
                        edge_index + num_edges, true, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+// ---- radius with a bit matrix of hits (every pair evaluated once, for large neighbour caps) ----------
+
+// First word of every segment's rows, from host copies of the segment pointers; returns the total number
+// of words.  A query of segment b owns ceil(n_b / chunk) * (chunk / 32) words.
+static int64_t radius_mask_layout(const int64_t *px, const int64_t *py, int64_t segs, int64_t n, int64_t m, int chunk,
+                                  std::vector<int64_t> *base) {
+  int64_t total = 0;
+  for (int64_t b = 0; b < segs; ++b) {
+    const int64_t nb = px ? px[b + 1] - px[b] : n, mb = py ? py[b + 1] - py[b] : m;
+    if (base) base->push_back(total);
+    if (nb > 0 && mb > 0) total += mb * ((nb + chunk - 1) / chunk) * (chunk / 32);
+  }
+  return total;
+}
+
+extern "C" size_t b200c_radius_mask_workspace_bytes(const int64_t *ptr_x_host, const int64_t *ptr_y_host,
+                                                    int64_t num_segments, int64_t n, int64_t m, int64_t dim,
+                                                    int dtype) {
+  if (dim < 1 || dim > 8 || (dtype != B200C_F32 && dtype != B200C_F64) || num_segments < 1 || n <= 0 || m <= 0) return 0;
+  if ((ptr_x_host == nullptr) != (ptr_y_host == nullptr) || (ptr_x_host == nullptr && num_segments != 1)) return 0;
+  const int chunk = radius_lowd_chunk_points((int)dim, dtype);
+  const int64_t words = radius_mask_layout(ptr_x_host, ptr_y_host, num_segments, n, m, chunk, nullptr);
+  return words > 0 ? align256((size_t)num_segments * 8) + (size_t)words * 4 : 0;
+}
+
+extern "C" int b200c_radius_count_masks(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                                        const int64_t *ptr_x_host, const int64_t *ptr_y_host, int64_t num_segments,
+                                        int64_t n, int64_t m, int64_t dim, double r, int64_t max_num_neighbors,
+                                        int ignore_same_index, int dtype, int32_t *counts, void *workspace,
+                                        size_t workspace_bytes, b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int st = check_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, dtype);
+  if (st != B200C_OK) return st;
+  B200C_CHECK_ARG(max_num_neighbors >= 1, "max_num_neighbors must be positive");
+  B200C_CHECK_ARG(counts != nullptr || m == 0, "null output pointer");
+  B200C_CHECK_ARG((ptr_x == nullptr) == (ptr_x_host == nullptr), "device and host segment pointers must come together");
+  const size_t need = b200c_radius_mask_workspace_bytes(ptr_x_host, ptr_y_host, num_segments, n, m, dim, dtype);
+  if (need == 0) {
+    set_error("the bit-matrix radius search covers fp32 / fp64 points of up to 8 features");
+    return B200C_ERR_UNSUPPORTED;
+  }
+  if (workspace == nullptr || workspace_bytes < need) {
+    set_error("radius mask workspace too small: %zu < %zu", workspace_bytes, need);
+    return B200C_ERR_WORKSPACE;
+  }
+  if ((st = check_device()) != B200C_OK) return st;
+  std::vector<int64_t> base;
+  radius_mask_layout(ptr_x_host, ptr_y_host, num_segments, n, m, radius_lowd_chunk_points((int)dim, dtype), &base);
+  B200C_CUDA(cudaMemcpyAsync(workspace, base.data(), base.size() * 8, cudaMemcpyHostToDevice, stream));
+  RadiusArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, r, max_num_neighbors,
+               ignore_same_index, counts, nullptr, nullptr, nullptr, nullptr, stream};
+  a.mask_base = (const int64_t *)workspace;
+  a.mask_words = (uint32_t *)((char *)workspace + align256((size_t)num_segments * 8));
+  return dtype == B200C_F32 ? launch_radius_lowd_f32(a, false) : launch_radius_lowd_f64(a, false);
+}
+
+extern "C" int b200c_radius_fill_masks(const int64_t *ptr_x, const int64_t *ptr_y, int64_t num_segments, int64_t n,
+                                       int64_t m, int64_t dim, int dtype, const int32_t *counts,
+                                       const int64_t *offsets, int64_t num_edges, int64_t *edge_index,
+                                       const void *workspace, b200c_stream_t stream_) {
+  B200C_CHECK_ARG(num_edges >= 0 && n >= 0 && m >= 0 && dim >= 1 && dim <= 8, "Input mismatch");
+  B200C_CHECK_ARG(dtype == B200C_F32 || dtype == B200C_F64, "unsupported dtype");
+  B200C_CHECK_ARG((ptr_x == nullptr) == (ptr_y == nullptr), "Input mismatch");
+  if (num_edges == 0 || m == 0) return B200C_OK;
+  B200C_CHECK_ARG(counts != nullptr && offsets != nullptr && edge_index != nullptr && workspace != nullptr, "null pointer");
+  int st = check_device();
+  if (st != B200C_OK) return st;
+  RadiusArgs a{nullptr, nullptr, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, 0.0, 0, 0, (int32_t *)counts, offsets,
+               edge_index, edge_index + num_edges, nullptr, (cudaStream_t)stream_};
+  a.mask_base = (const int64_t *)workspace;
+  a.mask_words = (uint32_t *)((char *)workspace + align256((size_t)num_segments * 8));
+  return dtype == B200C_F32 ? launch_radius_lowd_f32(a, true) : launch_radius_lowd_f64(a, true);
 }
 
 // ---- nearest ------------------------------------------------------------------------------------------

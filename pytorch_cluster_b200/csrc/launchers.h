@@ -43,12 +43,16 @@ struct RadiusArgs {
   int64_t *out_row, *out_col;
   int32_t *direct_rows;     // one-pass mode: [m, max_nn] int32 scratch, else nullptr
   cudaStream_t stream;
+  // bit-matrix mode: per-segment first word of the segment's rows, and the words
+  const int64_t *mask_base = nullptr;
+  uint32_t *mask_words = nullptr;
 };
 
 int launch_knn_lowd_f32(const KnnArgs &a);
 int launch_knn_lowd_f64(const KnnArgs &a);
 int launch_radius_lowd_f32(const RadiusArgs &a, bool fill);
 int launch_radius_lowd_f64(const RadiusArgs &a, bool fill);
+int radius_lowd_chunk_points(int dim, int dtype);  // points per chunk of the low-dimensional scan: 32 x (mask words per chunk)
 int launch_knn_generic_f32(const KnnArgs &a);
 int launch_knn_generic_f64(const KnnArgs &a);
 int launch_radius_generic_f32(const RadiusArgs &a, bool fill);

@@ -8,6 +8,9 @@
 //   FILL    hits are written at offsets[q] + running total + (hits of lower lanes) + (lower bits)
 //   DIRECT  as FILL, but into a row of `max_nn` int32 slots per query (one pass; a compaction
 //           copy follows the scan) — used when that scratch is small enough
+//   COUNT_MASK  as COUNT, and the words themselves go to a bit matrix in global memory (one row of
+//           chunks x WORDS words per query), from which radius_mask_fill_kernel writes the edges
+//           without evaluating a single distance again — for large neighbour caps
 // Ballot words cover points in ascending index order and one warp owns a query for the whole
 // scan, so "append in ascending x order, stop at max_num_neighbors"
 // (csrc/cuda/radius_cuda.cu:33-40) needs no atomics.  A warp stops scanning once all its queries
@@ -19,7 +22,7 @@
 
 namespace b200c {
 
-enum RadiusMode { RADIUS_COUNT = 0, RADIUS_FILL = 1, RADIUS_DIRECT = 2 };
+enum RadiusMode { RADIUS_COUNT = 0, RADIUS_FILL = 1, RADIUS_DIRECT = 2, RADIUS_COUNT_MASK = 3 };
 
 template <typename T, int DIM>
 struct RadiusLowD {
@@ -41,7 +44,8 @@ radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
                    int num_segments, int64_t n, int64_t m, T r2, int64_t max_nn, int ignore_same,
                    int32_t *__restrict__ counts, const int64_t *__restrict__ offsets,
                    int64_t *__restrict__ out_row, int64_t *__restrict__ out_col,
-                   int32_t *__restrict__ direct_rows) {
+                   int32_t *__restrict__ direct_rows, const int64_t *__restrict__ mask_base,
+                   uint32_t *__restrict__ mask_words) {
   using Cfg = RadiusLowD<T, DIM>;
   using C = LowD<T, DIM>;
   constexpr int QW = Cfg::QW, TQ = Cfg::TQ, R = C::R;
@@ -106,6 +110,9 @@ radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
 
     const int64_t nx = x_hi > x_lo ? x_hi - x_lo : 0;
     const int nchunks = (int)((nx + C::XC - 1) / C::XC);
+    // COUNT_MASK: the bit rows of this segment's queries start at mask_base[b]; a row has
+    // nchunks * WORDS words
+    const int64_t row_words = (int64_t)nchunks * Cfg::WORDS;
     if (nchunks > 0) {
       const int npts0 = nx < C::XC ? (int)nx : C::XC;
       stage_chunk<T, DIM>(planes, x, x_lo, npts0, tid);
@@ -158,7 +165,11 @@ radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
             }
             const int mine = __popc(word);
             const int total = __reduce_add_sync(FULL_MASK, mine);
-            if constexpr (MODE != RADIUS_COUNT) {
+            if constexpr (MODE == RADIUS_COUNT_MASK) {
+              if (lane < Cfg::WORDS)
+                mask_words[mask_base[b] + (q - y_lo) * row_words + (int64_t)c * Cfg::WORDS + lane] = word;
+            }
+            if constexpr (MODE == RADIUS_FILL || MODE == RADIUS_DIRECT) {
               if (total > 0) {
                 // hits of lower lanes: inclusive scan over the lanes, minus own
                 int incl = mine;
@@ -202,6 +213,55 @@ radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
       }
     }
     __syncthreads();
+  }
+}
+
+// Edges from the bit matrix a COUNT_MASK pass left: one warp per query walks the query's row in
+// blocks of 32 words (one coalesced load), places every set bit at offsets[q] + (bits before it)
+// and stops after counts[q] of them (the truncation rule of csrc/cuda/radius_cuda.cu:33-40; words
+// of chunks the scan skipped after the query reached its quota are never needed).
+static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask_words,
+                                               const int64_t *__restrict__ mask_base,
+                                               const int64_t *__restrict__ ptr_x, const int64_t *__restrict__ ptr_y,
+                                               int num_segments, int64_t n, int64_t m, int chunk_points,
+                                               const int32_t *__restrict__ counts,
+                                               const int64_t *__restrict__ offsets, int64_t *__restrict__ out_row,
+                                               int64_t *__restrict__ out_col) {
+  const int lane = threadIdx.x & 31;
+  const int64_t q = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (q >= m) return;
+  const int count = counts[q];
+  if (count <= 0) return;
+  const int b = segment_of(ptr_y, num_segments, q);
+  int64_t y_lo, y_hi, x_lo, x_hi;
+  segment_rows(ptr_y, num_segments, m, b, y_lo, y_hi);
+  segment_points(ptr_x, n, b, x_lo, x_hi);
+  const int64_t nx = x_hi > x_lo ? x_hi - x_lo : 0;
+  const int chunk_words = chunk_points / 32;
+  const int64_t row_words = (nx + chunk_points - 1) / chunk_points * chunk_words;
+  const uint32_t *row = mask_words + mask_base[b] + (q - y_lo) * row_words;
+  const int64_t o = offsets[q];
+  int run = 0;
+  for (int64_t w0 = 0; w0 < row_words && run < count; w0 += 32) {
+    uint32_t word = w0 + lane < row_words ? row[w0 + lane] : 0u;
+    const int mine = __popc(word);
+    // hits of lower lanes
+    int incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(FULL_MASK, incl, d);
+      if (lane >= d) incl += t;
+    }
+    int pos = run + incl - mine;
+    const int64_t idx0 = x_lo + (w0 + lane) * 32;
+    while (word != 0u && pos < count) {
+      const int bit = __ffs(word) - 1;
+      word &= word - 1u;
+      out_row[o + pos] = q;
+      out_col[o + pos] = idx0 + bit;
+      ++pos;
+    }
+    run += __shfl_sync(FULL_MASK, incl, 31);
   }
 }
 

@@ -18,6 +18,11 @@ namespace {
 #define CHECK_INPUT(x) TORCH_CHECK(x, "Input mismatch")
 #define CHECK_CONTIGUOUS(x) TORCH_CHECK(x.is_contiguous(), #x " must be contiguous")
 
+// neighbour caps up to this use the one-pass mode of b200c_radius_count (when its scratch fits); above it,
+// the bit-matrix mode when the matrix stays below the byte limit
+constexpr int64_t kRadiusDirectCap = 256;
+constexpr size_t kRadiusMaskMaxBytes = (size_t)8 << 30;
+
 void check_status(int status) {
   TORCH_CHECK(status == B200C_OK, "b200_cluster: ", b200c_last_error());
 }
@@ -186,6 +191,40 @@ torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tens
   if (m == 0 || max_num_neighbors <= 0) return torch::empty({2, 0}, lopts);
 
   auto counts = torch::empty({m}, x.options().dtype(torch::kInt));
+  auto offsets = torch::empty({m + 1}, lopts);
+  const size_t scan_bytes = b200c_scan_workspace_bytes(m);
+  auto scan_ws = torch::empty({(int64_t)scan_bytes}, x.options().dtype(torch::kByte));
+
+  // Large neighbour caps on low-dimensional points: every pair is evaluated once, its hit bit kept in
+  // a bit matrix from which the edges are written afterwards.  The matrix's size depends on the segment
+  // sizes, so the segment pointers are read to the host (a second small sync of this call).
+  if (max_num_neighbors > kRadiusDirectCap && dim <= 8 && (p.dtype == B200C_F32 || p.dtype == B200C_F64)) {
+    torch::Tensor hx, hy;
+    const int64_t *hpx = nullptr, *hpy = nullptr;
+    if (p.px != nullptr) {
+      hx = p.ptr_x.cpu();
+      hy = p.ptr_y.cpu();
+      hpx = hx.data_ptr<int64_t>();
+      hpy = hy.data_ptr<int64_t>();
+    }
+    const size_t mask_bytes = b200c_radius_mask_workspace_bytes(hpx, hpy, p.num_segments, n, m, dim, p.dtype);
+    if (mask_bytes > 0 && mask_bytes <= kRadiusMaskMaxBytes) {
+      auto mask_ws = torch::empty({(int64_t)mask_bytes}, x.options().dtype(torch::kByte));
+      check_status(b200c_radius_count_masks(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, hpx, hpy, p.num_segments, n, m,
+                                            dim, r, max_num_neighbors, ignore_same_index ? 1 : 0, p.dtype,
+                                            counts.data_ptr<int32_t>(), mask_ws.data_ptr(), mask_bytes,
+                                            stream.stream()));
+      check_status(b200c_exclusive_scan(counts.data_ptr<int32_t>(), m, offsets.data_ptr<int64_t>(), scan_ws.data_ptr(),
+                                        scan_bytes, stream.stream()));
+      const int64_t total = offsets[m].item<int64_t>();  // the output size
+      auto out = torch::empty({2, total}, lopts);
+      check_status(b200c_radius_fill_masks(p.px, p.py, p.num_segments, n, m, dim, p.dtype, counts.data_ptr<int32_t>(),
+                                           offsets.data_ptr<int64_t>(), total, out.data_ptr<int64_t>(),
+                                           mask_ws.data_ptr(), stream.stream()));
+      return out;
+    }
+  }
+
   // small neighbour caps: one scan that also parks the hits, then a copy (see b200_cluster.h)
   const size_t ws_bytes = b200c_radius_workspace_bytes(n, m, dim, max_num_neighbors, p.dtype);
   auto ws = torch::empty({(int64_t)ws_bytes}, x.options().dtype(torch::kByte));
@@ -193,9 +232,6 @@ torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tens
   check_status(b200c_radius_count(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
                                   max_num_neighbors, ignore_same_index ? 1 : 0, p.dtype,
                                   counts.data_ptr<int32_t>(), ws_ptr, ws_bytes, stream.stream()));
-  auto offsets = torch::empty({m + 1}, lopts);
-  const size_t scan_bytes = b200c_scan_workspace_bytes(m);
-  auto scan_ws = torch::empty({(int64_t)scan_bytes}, x.options().dtype(torch::kByte));
   check_status(b200c_exclusive_scan(counts.data_ptr<int32_t>(), m, offsets.data_ptr<int64_t>(),
                                     scan_ws.data_ptr(), scan_bytes, stream.stream()));
   const int64_t total = offsets[m].item<int64_t>();  // the one host sync: the output size

@@ -420,3 +420,36 @@ def test_knn_graph_one_kernel_unsupported_shapes():
     with pytest.raises(RuntimeError):
         _cabi.knn_graph(x, 4)
     assert "8 features" in _native.cabi().b200c_last_error().decode()
+
+
+# ---- radius through the bit matrix of hits (b200c_radius_count_masks / _fill_masks) --------------------
+
+@pytest.mark.parametrize("dt", ["f32", "f64"])
+@pytest.mark.parametrize("dim", [1, 2, 3, 4, 7, 8])
+def test_radius_masks_equal_count_and_fill(dim, dt):
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    g = torch.Generator().manual_seed(500 + dim)
+    sx, sy = [3000, 0, 1, 2500, 900], [700, 5, 0, 1100, 64]
+    x = torch.rand(sum(sx), dim, generator=g, dtype=DT[dt])
+    y = torch.rand(sum(sy), dim, generator=g, dtype=DT[dt])
+    px, py = _segments(sx), _segments(sy)
+    r = 0.01 if dim == 1 else (0.1 if dim <= 3 else 0.45)
+    for max_nn, ignore in ((100000, False), (300, False), (5, True)):
+        got = _cabi.radius_masks(x.to(DEV), y.to(DEV), r, px.to(DEV), py.to(DEV), max_nn, ignore).cpu().numpy()
+        want = orc.radius(x.numpy(), y.numpy(), r, px.numpy(), py.numpy(), max_nn, ignore)
+        assert got.shape == want.shape and np.array_equal(got, want)
+    got = _cabi.radius_masks(x.to(DEV), x.to(DEV), r, None, None, 4000, True).cpu().numpy()
+    assert np.array_equal(got, orc.radius(x.numpy(), x.numpy(), r, None, None, 4000, True))
+
+
+def test_radius_masks_workspace_rules():
+    from pytorch_cluster_b200 import _native
+
+    lib = _native.cabi()
+    hp = torch.tensor([0, 2000, 5000])
+    # 3-D fp32: chunks of 1024 points = 32 words; 2000 points -> 2 chunks, 3000 -> 3
+    words = 2000 * 2 * 32 + 3000 * 3 * 32
+    assert lib.b200c_radius_mask_workspace_bytes(hp.data_ptr(), hp.data_ptr(), 2, 5000, 5000, 3, 0) == 256 + words * 4
+    assert lib.b200c_radius_mask_workspace_bytes(hp.data_ptr(), hp.data_ptr(), 2, 5000, 5000, 9, 0) == 0
+    assert lib.b200c_radius_mask_workspace_bytes(None, None, 1, 100, 50, 3, 0) == 256 + 50 * 32 * 4
