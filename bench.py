@@ -311,11 +311,14 @@ def run_only(args):
         x = torch.randn(32768, 64, generator=g).to(dev)
         ptr = torch.arange(0, 32768 + 1, 2048, device=dev)
         fn = lambda: cabi.knn_padded_nosync(x, x, 21, ptr, ptr, args.cosine)
-    elif name in ("radius_mixture_small", "radius_mixture_small_two_scans"):  # 16 of the 64 clouds
-        w = make_radius_mixture(clouds=16)
+    elif name in ("radius_mixture_small", "radius_mixture_small_two_scans", "radius_mixture_small_masks"):
+        w = make_radius_mixture(clouds=16)     # 16 of the 64 clouds
         x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 16)
-        max_nn = 8192 if name.endswith("two_scans") else 64
-        fn = lambda: cabi.radius(x, x, w["r"], ptr, ptr, max_nn, True)
+        if name.endswith("masks"):             # large cap: count scan + bit matrix, edges from the bits
+            fn = lambda: cabi.radius_masks(x, x, w["r"], ptr, ptr, 8192, True)
+        else:
+            max_nn = 8192 if name.endswith("two_scans") else 64
+            fn = lambda: cabi.radius(x, x, w["r"], ptr, ptr, max_nn, True)
     elif name == "knn_graph_one_kernel":       # the headline call's kernel in its graph-output mode
         w = make_knn_graph_batched()
         x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 32)
