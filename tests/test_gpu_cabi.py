@@ -453,3 +453,38 @@ def test_radius_masks_workspace_rules():
     assert lib.b200c_radius_mask_workspace_bytes(hp.data_ptr(), hp.data_ptr(), 2, 5000, 5000, 3, 0) == 256 + words * 4
     assert lib.b200c_radius_mask_workspace_bytes(hp.data_ptr(), hp.data_ptr(), 2, 5000, 5000, 9, 0) == 0
     assert lib.b200c_radius_mask_workspace_bytes(None, None, 1, 100, 50, 3, 0) == 256 + 50 * 32 * 4
+
+
+# ---- large row counts ---------------------------------------------------------------------------------------
+
+def test_knn_and_radius_on_16m_points():
+    """16.7 M points in two segments (row numbers beyond 2^24, byte offsets beyond 2^27), k = 100:
+    a sample of the queries against the oracle, and size-independent properties for all of them."""
+    from pytorch_cluster_b200 import cabi as _cabi
+
+    g = torch.Generator().manual_seed(99)
+    n, m = 1 << 24, 2048
+    x = torch.rand(n, 3, generator=g)
+    y = torch.rand(m, 3, generator=g)
+    px = torch.tensor([0, 5_000_000, n])
+    py = torch.tensor([0, 1000, m])
+    dx, dy, dpx, dpy = x.to(DEV), y.to(DEV), px.to(DEV), py.to(DEV)
+    padded, counts, nvalid = _cabi.knn_padded(dx, dy, 100, dpx, dpy)
+    assert nvalid == m * 100 and int(counts.min()) == 100
+    col = padded[1].view(m, 100)
+    lo = torch.where(torch.arange(m, device=DEV) < 1000, 0, 5_000_000)
+    hi = torch.where(torch.arange(m, device=DEV) < 1000, 5_000_000, n)
+    assert bool(((col >= lo[:, None]) & (col < hi[:, None])).all())          # neighbours stay in the segment
+    d = ((dx[col.reshape(-1)] - dy.repeat_interleave(100, 0)) ** 2).sum(1).view(m, 100)
+    assert bool((d[:, 1:] >= d[:, :-1] - 1e-9).all())                        # ascending distances
+    sample = torch.cat([torch.arange(0, 16), torch.arange(1000, 1016)])
+    ys = y[sample].contiguous()
+    pys = torch.tensor([0, 16, 32])
+    want, _ = orc.knn_padded(x.numpy(), ys.numpy(), 100, px.numpy(), pys.numpy())
+    assert np.array_equal(col[sample.to(DEV)].cpu().numpy(), want)
+    e = _cabi.radius(dx, dy, 0.004, dpx, dpy, 64, False).cpu().numpy()
+    rows = np.isin(e[0], sample.numpy())
+    want = orc.radius(x.numpy(), ys.numpy(), 0.004, px.numpy(), pys.numpy(), 64, False)
+    remap = {int(s): i for i, s in enumerate(sample.tolist())}
+    got = np.stack([np.array([remap[int(r)] for r in e[0][rows]], dtype=np.int64), e[1][rows]])
+    assert np.array_equal(got, want)
