@@ -43,6 +43,10 @@ constexpr int TC_GH = 16;        // group minima kept per thread: 64 per query
 constexpr int TC_CAP = 128;      // candidates kept per query: two lists of 64, each filled from both ends
 constexpr int TC_THREADS = TC_M * TC_PARTS;
 constexpr int TC_SPIN_LIMIT = 1 << 22;
+// Point tiles held in shared memory.  The kernel also runs with 4 (they fit up to 64 features), but three
+// tiles of look-ahead measured slower than one on 16 x 2048 x 64 (148 us against 129 us): the step is
+// not waiting for its copies.
+constexpr int TC_RING = 2;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -173,7 +177,6 @@ struct TensorArgs {
   int32_t *cand;               // [m, TC_CAP]
   int32_t *cand_count;         // [m]; four 8-bit counts: list A front, A back, list B front, B back
   int *error_flag;
-  int ring;                    // point tiles held in shared memory: 2 or 4
 };
 
 template <bool COSINE>
@@ -187,7 +190,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
   const int dim = a.dim;
   const uint32_t tile_bytes = (uint32_t)((dim + 31) >> 5) * 16384u;  // whole atoms of 32 features
   unsigned char *sQ = smem;
-  const int ring = a.ring, ahead = ring - 1, sqx_slots = ring + 1;
+  constexpr int ring = TC_RING, ahead = ring - 1, sqx_slots = ring + 1;
   unsigned char *sX = smem + tile_bytes;                                      // ring of point tiles
   float *s_sqx = reinterpret_cast<float *>(smem + (1 + ring) * tile_bytes);   // |x|^2 per column, ring + 1 tiles
   float *gmin = s_sqx + sqx_slots * TC_N;                                     // [TC_M][64] group minima, see gmin_slot
@@ -277,10 +280,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) knn_tensor_candidates_kernel(Te
     int group = 0, in_group = 0, ncand = 0;
     for (int s = 0; s <= nsteps; ++s) {
       if (s < nsteps) {
-        if (ahead == 1)
+        if constexpr (ahead == 1)
           asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         else
           asm volatile("cp.async.wait_group 2;\n" ::: "memory");
+        static_assert(ahead == 1 || ahead == 3, "the wait above names the number of groups that may stay in flight");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> tensor-core reads
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -600,14 +604,6 @@ size_t knn_tensor_smem_bytes(int dim, int ring) {
          1024;
 }
 
-// Point tiles held in shared memory.  The kernel also runs with four (they fit up to 64 features), but
-// three tiles of look-ahead measured slower than one on 16 x 2048 x 64 (148 us against 129 us): the
-// step is not waiting for its copies.
-int knn_tensor_ring(int dim) {
-  (void)dim;
-  return 2;
-}
-
 static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
 
 // workspace: [sq_x n][sq_y m][xmax + error flag 256][cand m*CAP][cand_count m]
@@ -684,8 +680,8 @@ int launch_knn_tensor_f32(const KnnArgs &a, void *workspace) {
   }
 
   TensorArgs t{a.cosine ? xhat : (const float *)a.x, a.cosine ? yhat : (const float *)a.y, sq_x, sq_y, xmax,
-               a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, cand, cand_count, error_flag, knn_tensor_ring(a.dim)};
-  const size_t smem = knn_tensor_smem_bytes(a.dim, t.ring);
+               a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, cand, cand_count, error_flag};
+  const size_t smem = knn_tensor_smem_bytes(a.dim, TC_RING);
   const unsigned ctas = (unsigned)((a.m + TC_M - 1) / TC_M);
   if (a.cosine) {
     B200C_CUDA(cudaFuncSetAttribute(knn_tensor_candidates_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
