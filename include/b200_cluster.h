@@ -260,6 +260,32 @@ int b200c_fps(const void *src, const int64_t *ptr, const int64_t *out_ptr,
               int dtype, int64_t *out, void *workspace, size_t workspace_bytes,
               b200c_stream_t stream);
 
+/* b200c_fps, leaving out the segments of more than max_segment_points points (their slots of
+ * `out` stay unwritten): for callers that hand those to b200c_fps_large_segment. */
+int b200c_fps_up_to(const void *src, const int64_t *ptr, const int64_t *out_ptr,
+                    const int64_t *start, int64_t num_segments, int64_t n, int64_t dim,
+                    int dtype, int64_t max_segment_points, int64_t *out, void *workspace,
+                    size_t workspace_bytes, b200c_stream_t stream);
+
+/* Farthest point sampling of ONE large segment spread over many SMs (fp32, up to 8 features, up to
+ * b200c_fps_large_segment_max_points points: 8192 — or 4096 above 3 features — per SM): a
+ * cooperative launch of one CTA per 8192 points, each holding its points in registers; per step
+ * the CTAs publish their best candidate in global memory, meet at a counter (bounded polling) and
+ * all continue with the overall winner.  The reference runs any segment on one thread block; this
+ * entry point has no counterpart there.  Same results as b200c_fps.
+ *
+ * src: the whole point array; seg_lo / seg_points: the segment's rows; start_offset: first sample
+ * relative to seg_lo; count >= 1 samples are written to out[0..count) (global row numbers).
+ * *status (int32, device; zero it before) becomes 1 if a wait ran out — the samples are then not
+ * valid.  workspace: b200c_fps_large_segment_workspace_bytes() bytes.  Calls on one device must
+ * not overlap (every launch wants all its CTAs resident). */
+int64_t b200c_fps_large_segment_max_points(int64_t dim, int dtype);
+size_t b200c_fps_large_segment_workspace_bytes(void);
+int b200c_fps_large_segment(const void *src, int64_t seg_lo, int64_t seg_points,
+                            int64_t start_offset, int64_t count, int64_t dim, int dtype,
+                            int64_t *out, void *workspace, size_t workspace_bytes,
+                            int32_t *status, b200c_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -80,6 +80,14 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_fps_workspace_bytes.restype = sz
     lib.b200c_fps.argtypes = [p, p, p, p, i64, i64, i64, i32, p, p, sz, p]
     lib.b200c_fps.restype = i32
+    lib.b200c_fps_up_to.argtypes = [p, p, p, p, i64, i64, i64, i32, i64, p, p, sz, p]
+    lib.b200c_fps_up_to.restype = i32
+    lib.b200c_fps_large_segment_max_points.argtypes = [i64, i32]
+    lib.b200c_fps_large_segment_max_points.restype = i64
+    lib.b200c_fps_large_segment_workspace_bytes.argtypes = []
+    lib.b200c_fps_large_segment_workspace_bytes.restype = sz
+    lib.b200c_fps_large_segment.argtypes = [p, i64, i64, i64, i64, i64, i32, p, p, sz, p, p]
+    lib.b200c_fps_large_segment.restype = i32
     for name in ("b200c_segment_ptr", "b200c_exclusive_scan", "b200c_exclusive_scan_static", "b200c_knn", "b200c_knn_compact", "b200c_knn_graph_tail_count", "b200c_knn_graph_tail_write",
                  "b200c_radius_count", "b200c_radius_fill"):
         getattr(lib, name).restype = i32

@@ -169,3 +169,15 @@ def radius_masks(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_s
     _native.check(lib.b200c_radius_fill_masks(_p(ptr_x), _p(ptr_y), nseg, n, m, dim, _dtype(x), _p(counts), _p(offsets),
                                               total, _p(out), _p(ws), _stream()))
     return out
+
+
+def fps_large_segment(src, seg_lo, seg_points, count, start_offset=0):
+    """-> (int64 [count] samples of one segment, status int): b200c_fps_large_segment."""
+    lib = _native.cabi()
+    out = torch.empty(count, dtype=torch.long, device=src.device)
+    nbytes = lib.b200c_fps_large_segment_workspace_bytes()
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=src.device)
+    status = torch.zeros(1, dtype=torch.int32, device=src.device)
+    _native.check(lib.b200c_fps_large_segment(_p(src), seg_lo, seg_points, start_offset, count, src.shape[1],
+                                              _dtype(src), _p(out), _p(ws), nbytes, _p(status), _stream()))
+    return out, int(status.item())

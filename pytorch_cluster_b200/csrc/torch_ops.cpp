@@ -10,6 +10,8 @@
 #include <ATen/cuda/CUDAEvent.h>
 #include <torch/script.h>
 
+#include <vector>
+
 #include "b200_cluster.h"
 
 namespace {
@@ -320,9 +322,43 @@ torch::Tensor fps(torch::Tensor src, torch::Tensor ptr, torch::Tensor ratio, boo
   const int64_t n = src.size(0), dim = src.size(1);
   const size_t ws_bytes = b200c_fps_workspace_bytes(n, dim, dtype);
   auto ws = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kByte));
+  auto stream = at::cuda::getCurrentCUDAStream();
+
+  // Segments too large for one SM's registers are sampled by many SMs together, one launch each; whether
+  // there are any is only known from the segment sizes, which are read to the host when the input is large
+  // enough to hold one.
+  const int64_t per_cta = dim <= 3 ? 8192 : 4096;
+  const int64_t multi_cap = b200c_fps_large_segment_max_points(dim, dtype);
+  if (multi_cap > 0 && n > per_cta) {
+    auto hptr = ptr.cpu();
+    auto hout = out_ptr.cpu();
+    torch::Tensor hstart;
+    if (random_start) hstart = start.cpu();
+    const int64_t *hp = hptr.data_ptr<int64_t>(), *ho = hout.data_ptr<int64_t>();
+    std::vector<int64_t> large;
+    for (int64_t b = 0; b < batch_size; ++b) {
+      const int64_t pts = hp[b + 1] - hp[b];
+      if (pts > per_cta && pts <= multi_cap && ho[b + 1] > ho[b]) large.push_back(b);
+    }
+    if (!large.empty()) {
+      check_status(b200c_fps_up_to(src.data_ptr(), ptr.data_ptr<int64_t>(), out_ptr.data_ptr<int64_t>(), start_ptr,
+                                   batch_size, n, dim, dtype, per_cta, out.data_ptr<int64_t>(), ws.data_ptr(), ws_bytes,
+                                   stream.stream()));
+      const size_t big_bytes = b200c_fps_large_segment_workspace_bytes();
+      auto big_ws = torch::empty({(int64_t)big_bytes}, src.options().dtype(torch::kByte));
+      auto status = torch::zeros({1}, src.options().dtype(torch::kInt));
+      for (int64_t b : large)
+        check_status(b200c_fps_large_segment(src.data_ptr(), hp[b], hp[b + 1] - hp[b],
+                                             random_start ? hstart.data_ptr<int64_t>()[b] : 0, ho[b + 1] - ho[b], dim,
+                                             dtype, out.data_ptr<int64_t>() + ho[b], big_ws.data_ptr(), big_bytes,
+                                             status.data_ptr<int32_t>(), stream.stream()));
+      TORCH_CHECK(status.item<int32_t>() == 0, "b200_cluster: a wait between the thread blocks of fps ran out");
+      return out;
+    }
+  }
   check_status(b200c_fps(src.data_ptr(), ptr.data_ptr<int64_t>(), out_ptr.data_ptr<int64_t>(), start_ptr,
                          batch_size, n, dim, dtype, out.data_ptr<int64_t>(), ws.data_ptr(), ws_bytes,
-                         at::cuda::getCurrentCUDAStream().stream()));
+                         stream.stream()));
   return out;
 }
 

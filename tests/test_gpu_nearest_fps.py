@@ -239,3 +239,51 @@ def test_fps_equals_reference_cuda(dtype):
     pl = torch.tensor([0, 40000], device=DEV)
     r = torch.tensor(0.005, dtype=dtype, device=DEV)
     assert torch.equal(fps(xl, ptr=pl, ratio=r, random_start=False), refc.fps(xl, pl, r, False))
+
+
+# ---- one large segment on many SMs (b200c_fps_large_segment) ------------------------------------------
+
+@pytest.mark.parametrize("n,dim", [(8193, 3), (20000, 3), (131072, 3), (300000, 2), (9000, 7)])
+def test_fps_large_segment_cabi(n, dim):
+    from pytorch_cluster_b200 import cabi
+
+    g = torch.Generator().manual_seed(1000 + dim)
+    pad = 37  # the segment does not start at row 0
+    x = torch.rand(pad + n, dim, generator=g)
+    count = 200
+    got, status = cabi.fps_large_segment(x.to(DEV), pad, n, count, start_offset=5)
+    assert status == 0
+    want = orc.fps(x.numpy(), [0, pad, pad + n], [0, 0, count], np.array([0, 5]))
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_fps_large_segment_ties():
+    """Lattice points: many equal maxima across the thread blocks."""
+    from pytorch_cluster_b200 import cabi
+
+    g = torch.Generator().manual_seed(17)
+    x = torch.randint(0, 6, (40000, 3), generator=g).float()
+    got, status = cabi.fps_large_segment(x.to(DEV), 0, 40000, 150)
+    assert status == 0
+    assert np.array_equal(got.cpu().numpy(), orc.fps(x.numpy(), [0, 40000], [0, 150]))
+
+
+def test_fps_api_mixes_small_and_large_segments():
+    from pytorch_cluster_b200 import fps
+
+    g = torch.Generator().manual_seed(18)
+    sizes = [3000, 50000, 8192, 1, 9000]
+    x = torch.rand(sum(sizes), 3, generator=g)
+    ptr = _ptr(sizes)
+    ratio = torch.tensor([0.05, 0.004, 0.01, 1.0, 0.02])
+    got = fps(x.to(DEV), ptr=ptr.to(DEV), ratio=ratio.to(DEV), random_start=False).cpu().numpy()
+    out_ptr = torch.cat([torch.zeros(1, dtype=torch.long),
+                         ((ptr[1:] - ptr[:-1]).float() * ratio).ceil().long().cumsum(0)])
+    assert np.array_equal(got, orc.fps(x.numpy(), ptr.numpy(), out_ptr.numpy()))
+    idx = fps(x.to(DEV), ptr=ptr.to(DEV), ratio=0.01)  # random start: valid, distinct, per segment
+    assert idx.unique().numel() == idx.numel()
+    if refc.available():
+        r = torch.tensor(0.003, device=DEV)
+        big = torch.rand(100000, 3, generator=g).to(DEV)
+        bp = torch.tensor([0, 100000], device=DEV)
+        assert torch.equal(fps(big, ptr=bp, ratio=r, random_start=False), refc.fps(big, bp, r, False))

@@ -204,6 +204,12 @@ def test_time_beside_reference_kernels():
     ratio = torch.tensor(0.25, device=DEV)
     both("fps_64x8192x3_ratio0.25", lambda: refc.fps(xr, pr, ratio, False),
          lambda: torch.ops.torch_cluster.fps(xr, pr, ratio, False), 1)
+    # one large cloud: 1024 samples of 1 M points (the reference runs a segment on one thread block)
+    xl = torch.rand(1 << 20, 3, generator=torch.Generator().manual_seed(6)).to(DEV)
+    pl = torch.tensor([0, 1 << 20], device=DEV)
+    rl = torch.tensor(1024 / (1 << 20) - 1e-9, device=DEV)
+    both("fps_1x1048576x3_1024_samples", lambda: refc.fps(xl, pl, rl, False),
+         lambda: torch.ops.torch_cluster.fps(xl, pl, rl, False), 1)
     out = {k: {"reference_cuda_ms": round(a, 4), "this_library_ms": round(b, 4), "ratio": round(a / b, 2)}
            for k, (a, b) in rep.items()}
     print(json.dumps(out, indent=1))
