@@ -236,6 +236,13 @@ def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank):
     samples = pc.fps(xr, br, ratio=0.25, random_start=False, batch_size=64)
     out["fps_64x8192x3_ratio0.25"] = {"api_ms": t, "samples": int(samples.numel()),
                                       "samples_per_s": samples.numel() / (t * 1e-3)}
+    # one large cloud: 1024 samples of 1 M points, spread over the SMs of the device
+    g = torch.Generator().manual_seed(6)
+    xl = torch.rand(1 << 20, 3, generator=g).to(dev)
+    pl = torch.tensor([0, 1 << 20], device=dev)
+    t = ms_of(lambda: pc.fps(xl, ptr=pl, ratio=1024 / (1 << 20) - 1e-9, random_start=False))
+    out["fps_1x1048576x3_1024_samples"] = {"api_ms": t, "us_per_step": t * 1e3 / 1024}
+    del xl
     ys, bs = xr[samples].contiguous(), br[samples].contiguous()
     t = ms_of(lambda: pc.nearest(xr, ys, br, bs))
     out["nearest_64x8192_to_2048x3"] = {"api_ms": t, "rows_per_s": xr.shape[0] / (t * 1e-3),
