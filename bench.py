@@ -194,13 +194,6 @@ def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank):
     out["knn_bipartite_8x131072x8192_k32"] = {
         "kernel_ms": tk, "api_ms": ta, "queries_per_s": w["queries"] / (ta * 1e-3),
         "fp32_frac": 8.0 * w["pairs"] / (tk * 1e-3) / 1e12 / peak_tf}
-    if world > 1:
-        from pytorch_cluster_b200 import knn_sharded
-
-        ts = max_over_ranks(ms_of(lambda: knn_sharded(x, y, 32, bx, by, batch_size=8)), world)
-        tl = max_over_ranks(ms_of(lambda: knn_sharded(x, y, 32, bx, by, batch_size=8, assemble=False)), world)
-        out["knn_bipartite_8x131072x8192_k32"].update(
-            {"sharded_ms": ts, "sharded_no_assembly_ms": tl, "sharded_queries_per_s": w["queries"] / (ts * 1e-3)})
     del x, y
 
     # feature-space kNN: 16 clouds x 2048 points x 64 features, k = 20
@@ -222,12 +215,6 @@ def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank):
         ta = ms_of(lambda: pc.radius_graph(xr, w["r"], br, max_num_neighbors=max_nn))
         rec = {"api_ms": ta, "edges": int(e.shape[1]), "edges_per_s": e.shape[1] / (ta * 1e-3),
                "fp32_frac": 8.0 * w["pairs"] / (ta * 1e-3) / 1e12 / peak_tf}
-        if world > 1:
-            from pytorch_cluster_b200 import radius_sharded
-
-            ts = max_over_ranks(ms_of(lambda: radius_sharded(xr, xr, w["r"], br, br, max_num_neighbors=max_nn,
-                                                             batch_size=64, assemble=False)), world)
-            rec["sharded_no_assembly_ms"] = ts
         out[f"radius_graph_64x8192x3_r0.05_max{max_nn}"] = rec
 
     # the operators either side of the path: farthest point sampling (25 % of every cloud, first
@@ -247,6 +234,69 @@ def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank):
     t = ms_of(lambda: pc.nearest(xr, ys, br, bs))
     out["nearest_64x8192_to_2048x3"] = {"api_ms": t, "rows_per_s": xr.shape[0] / (t * 1e-3),
                                         "fp32_frac": 8.0 * 64 * 8192 * 2048 / (t * 1e-3) / 1e12 / peak_tf}
+    return out
+
+
+def strong_scaling(pc, dev, flush, world, rank):
+    """Fixed total work split over the ranks (replicated inputs, segments sharded): the large bipartite
+    kNN, radius_graph with both neighbour caps and the bipartite radius search.  Per workload: the
+    single-GPU call on this rank (`ms_1gpu`), the sharded call with every rank keeping its own slice
+    (`ms_sharded`) and with the global edge_index assembled on every rank (`ms_assembled`); times are
+    the max over ranks.  Before timing, the assembled result is checked to equal the single-GPU
+    result on every rank."""
+    import torch.distributed as dist
+
+    reps, warm = 5, 2
+    out = {}
+
+    def ms_of(fn):
+        return max_over_ranks(timed_steps(fn, reps, warm, flush) / reps, world)
+
+    def record(name, single, sharded, units, unit_name, gather_bytes):
+        want = single()
+        got = sharded(True)
+        same = torch.tensor([int(torch.equal(want, got))], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        assert int(same.item()) == 1, f"{name}: the assembled sharded result differs from the single-GPU result"
+        units_n = units(want)
+        del got
+        t1 = ms_of(single)
+        ts = ms_of(lambda: sharded(False))
+        ta = ms_of(lambda: sharded(True))
+        out[name] = {"ms_1gpu": t1, "ms_sharded": ts, "ms_assembled": ta, "speedup_sharded": t1 / ts,
+                     "speedup_assembled": t1 / ta, unit_name + "_per_s_sharded": units_n / (ts * 1e-3),
+                     unit_name + "_per_s_assembled": units_n / (ta * 1e-3),
+                     "assembly": {"collective": "all-gather of the edge rows (NCCL), one per row",
+                                  "bytes_received_per_rank": gather_bytes(want) * (world - 1) // world,
+                                  "ms": ta - ts}}
+
+    w = make_knn_bipartite()
+    x, y = w["x"].to(dev), w["y"].to(dev)
+    bx, by = w["batch_x"].to(dev), w["batch_y"].to(dev)
+    plan = pc.make_plan(x.size(0), y.size(0), bx, by, 8, world)
+    record("knn_bipartite_8x131072x8192_k32", lambda: pc.knn(x, y, 32, bx, by, batch_size=8),
+           lambda asm: pc.knn_sharded(x, y, 32, bx, by, batch_size=8, plan=plan, assemble=asm),
+           lambda e: w["queries"], "queries", lambda e: e.numel() * 8)
+    del x, y
+
+    w = make_radius_mixture()
+    xr, br = w["x"].to(dev), w["batch"].to(dev)
+    plan = pc.make_plan(xr.size(0), xr.size(0), br, br, 64, world)
+    for max_nn in (64, 8192):
+        record(f"radius_graph_64x8192x3_r0.05_max{max_nn}",
+               lambda: pc.radius_graph(xr, w["r"], br, max_num_neighbors=max_nn, batch_size=64),
+               lambda asm: pc.radius_graph_sharded(xr, w["r"], br, max_num_neighbors=max_nn, batch_size=64, plan=plan,
+                                                   assemble=asm),
+               lambda e: e.shape[1], "edges", lambda e: e.numel() * 8)
+    g = torch.Generator().manual_seed(9)
+    keep = torch.cat([torch.randperm(8192, generator=g)[:2048].sort().values + 8192 * c for c in range(64)]).to(dev)
+    ys, bs = xr[keep].contiguous(), br[keep].contiguous()
+    plan = pc.make_plan(xr.size(0), ys.size(0), br, bs, 64, world)
+    record("radius_bipartite_64x8192_to_2048_r0.05_max64",
+           lambda: pc.radius(xr, ys, w["r"], br, bs, max_num_neighbors=64, batch_size=64),
+           lambda asm: pc.radius_sharded(xr, ys, w["r"], br, bs, max_num_neighbors=64, batch_size=64, plan=plan,
+                                         assemble=asm),
+           lambda e: e.shape[1], "edges", lambda e: e.numel() * 8)
     return out
 
 
@@ -397,6 +447,7 @@ def run_ours(args, rank, world, local_rank):
         ms_kernel = max_over_ranks(ms_kernel, world)
         extra = {} if args.no_extra else extra_workloads(pc, _cabi, dev, flush, fp32_peak_tf(props, load_peaks()),
                                                          world, rank)
+        strong = strong_scaling(pc, dev, flush, world, rank) if (world > 1 and not args.no_extra) else None
 
     if rank != 0:
         return
@@ -429,6 +480,8 @@ def run_ours(args, rank, world, local_rank):
                      "traffic": KNN_LOWD_CFG2_DRAM_BYTES},
         "extra": extra,
     }
+    if strong is not None:
+        line["strong"] = strong
     if not args.no_cpu_baseline:
         from oracle import reference_cpu as rc
 

@@ -202,15 +202,39 @@ int b200c_radius_fill(const void *x, const void *y, const int64_t *ptr_x,
                       int64_t num_edges, int64_t *edge_index, void *workspace,
                       size_t workspace_bytes, b200c_stream_t stream);
 
+/* The same two passes for a y that is a slice of a larger query set whose row numbers x shares
+ * (one point cloud searched in itself, its queries split over several GPUs): the pair skipped by
+ * ignore_same_index is x row (q + query_index_base), q being the row of the slice — the global
+ * row comparison of csrc/cuda/radius_cuda.cu:33 carried over to a slice.  The edge rows still
+ * hold q, the row of the slice; the caller adds the base.  With swap_rows the fill pass writes
+ * row 0 = x index, row 1 = q: the `source_to_target` orientation of radius_graph
+ * (torch_cluster/radius.py:143-148) without a second pass over the result.  query_index_base = 0
+ * and swap_rows = 0 give b200c_radius_count / b200c_radius_fill.  The slice form has no
+ * counterpart in the reference, which has no multi-GPU path. */
+int b200c_radius_count_part(const void *x, const void *y, const int64_t *ptr_x,
+                            const int64_t *ptr_y, int64_t num_segments, int64_t n,
+                            int64_t m, int64_t dim, double r, int64_t max_num_neighbors,
+                            int ignore_same_index, int64_t query_index_base, int dtype,
+                            int32_t *counts, void *workspace, size_t workspace_bytes,
+                            b200c_stream_t stream);
+int b200c_radius_fill_part(const void *x, const void *y, const int64_t *ptr_x,
+                           const int64_t *ptr_y, int64_t num_segments, int64_t n,
+                           int64_t m, int64_t dim, double r, int64_t max_num_neighbors,
+                           int ignore_same_index, int64_t query_index_base, int swap_rows,
+                           int dtype, const int32_t *counts, const int64_t *offsets,
+                           int64_t num_edges, int64_t *edge_index, void *workspace,
+                           size_t workspace_bytes, b200c_stream_t stream);
+
 /* Fixed-radius search that evaluates every pair once, for neighbour caps too large for the one-pass
  * mode above (fp32 / fp64, up to 8 features): pass 1 counts like b200c_radius_count and also stores one
  * hit bit per (query, point) in a bit matrix in the workspace; pass 2 writes the edges from those bits
  * (an HBM-bound kernel) instead of scanning the points again.  Same results as count + fill.
  *
  * The matrix's size depends on the segment sizes, so the caller hands over host copies of the segment
- * pointers (ptr_x_host, ptr_y_host: int64 [num_segments + 1] in host memory; NULL with ptr_x == NULL
- * for one segment): b200c_radius_mask_workspace_bytes gives the size (0 = not applicable), pass 1
- * checks it.  Rows: a query of a segment with n_b points owns ceil(n_b / c) * c / 32 words, c being the
+ * pointers (ptr_x_host, ptr_y_host: int64 [num_segments + 1] in host memory, equal to the device
+ * copies; NULL with ptr_x == NULL for one segment): b200c_radius_mask_workspace_bytes gives the size
+ * (0 = not applicable, also for pointers that do not start at 0, decrease, or do not end at n / m),
+ * pass 1 checks it.  Rows: a query of a segment with n_b points owns ceil(n_b / c) * c / 32 words, c being the
  * scan's chunk (1024 points for 3-D fp32).  No counterpart in the reference, which evaluates once but
  * pads its output to max_num_neighbors slots per query. */
 size_t b200c_radius_mask_workspace_bytes(const int64_t *ptr_x_host, const int64_t *ptr_y_host,
@@ -222,6 +246,19 @@ int b200c_radius_count_masks(const void *x, const void *y, const int64_t *ptr_x,
                              int64_t m, int64_t dim, double r, int64_t max_num_neighbors,
                              int ignore_same_index, int dtype, int32_t *counts,
                              void *workspace, size_t workspace_bytes, b200c_stream_t stream);
+/* b200c_radius_count_masks for a slice of a larger query set: see b200c_radius_count_part. */
+int b200c_radius_count_masks_part(const void *x, const void *y, const int64_t *ptr_x,
+                                  const int64_t *ptr_y, const int64_t *ptr_x_host,
+                                  const int64_t *ptr_y_host, int64_t num_segments, int64_t n,
+                                  int64_t m, int64_t dim, double r, int64_t max_num_neighbors,
+                                  int ignore_same_index, int64_t query_index_base, int dtype,
+                                  int32_t *counts, void *workspace, size_t workspace_bytes,
+                                  b200c_stream_t stream);
+int b200c_radius_fill_masks_part(const int64_t *ptr_x, const int64_t *ptr_y,
+                                 int64_t num_segments, int64_t n, int64_t m, int64_t dim,
+                                 int swap_rows, int dtype, const int32_t *counts,
+                                 const int64_t *offsets, int64_t num_edges, int64_t *edge_index,
+                                 const void *workspace, b200c_stream_t stream);
 int b200c_radius_fill_masks(const int64_t *ptr_x, const int64_t *ptr_y, int64_t num_segments,
                             int64_t n, int64_t m, int64_t dim, int dtype,
                             const int32_t *counts, const int64_t *offsets, int64_t num_edges,

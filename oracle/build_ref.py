@@ -25,6 +25,12 @@ OUT = os.path.join(OUT_DIR, "ref_cluster_cpu.so")
 OUT_CUDA = os.path.join(OUT_DIR, "ref_cluster_cuda.so")
 
 
+def default_reference_dir() -> str:
+    """Where the reference checkout is looked for: ``$REFERENCE_DIR``, else a directory named
+    ``reference`` beside this repository."""
+    return os.environ.get("REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def torch_flags():
     import torch
     from torch.utils import cpp_extension as ce
@@ -128,7 +134,7 @@ def build_cuda(reference: str, force: bool = False, verbose: bool = True) -> str
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--reference", default=default_reference_dir())
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     out = build(a.reference, a.force)

@@ -62,6 +62,16 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_radius_workspace_bytes.restype = sz
     lib.b200c_radius_count.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, sz, p]
     lib.b200c_radius_fill.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, i64, p, p, sz, p]
+    lib.b200c_radius_count_part.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i64, i32, p, p, sz, p]
+    lib.b200c_radius_count_part.restype = i32
+    lib.b200c_radius_fill_part.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i64, i32, i32, p, p, i64, p, p,
+                                           sz, p]
+    lib.b200c_radius_fill_part.restype = i32
+    lib.b200c_radius_count_masks_part.argtypes = [p, p, p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i64, i32, p, p,
+                                                  sz, p]
+    lib.b200c_radius_count_masks_part.restype = i32
+    lib.b200c_radius_fill_masks_part.argtypes = [p, p, i64, i64, i64, i64, i32, i32, p, p, i64, p, p, p]
+    lib.b200c_radius_fill_masks_part.restype = i32
     lib.b200c_knn_graph.argtypes = [p, p, i64, i64, i64, i64, i32, i32, p, p, p]
     lib.b200c_knn_graph.restype = i32
     lib.b200c_knn_graph_part.argtypes = [p, p, i64, i64, i64, i64, i32, i32, i64, p, i64, p, p]

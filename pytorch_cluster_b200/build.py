@@ -75,7 +75,7 @@ def build_ops(force: bool = False, verbose: bool = False) -> str:
     from torch.utils import cpp_extension as ce
 
     src = os.path.join(CSRC, "torch_ops.cpp")
-    deps = [src, os.path.join(INCLUDE, "b200_cluster.h"), LIB_CABI]
+    deps = [src, os.path.join(INCLUDE, "b200_cluster.h"), os.path.join(INCLUDE, "b200_cluster_torch.h"), LIB_CABI]
     if not force and _newer(LIB_OPS, deps):
         return LIB_OPS
     lib_dir = ce.library_paths()[0]

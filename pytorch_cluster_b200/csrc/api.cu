@@ -3,7 +3,6 @@
 // checked on raw pointers) and kernel selection.
 #include <cstdarg>
 #include <cstdio>
-#include <vector>
 
 #include "common.cuh"
 #include "launchers.h"
@@ -215,10 +214,11 @@ static int radius_common(const void *x, const void *y, const int64_t *ptr_x, con
                          int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
                          int64_t max_num_neighbors, int ignore_same_index, int dtype, int32_t *counts,
                          const int64_t *offsets, int64_t *out_row, int64_t *out_col, bool fill,
-                         void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+                         void *workspace, size_t workspace_bytes, int64_t query_base, cudaStream_t stream) {
   int st = check_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, dtype);
   if (st != B200C_OK) return st;
   B200C_CHECK_ARG(max_num_neighbors >= 1, "max_num_neighbors must be positive");
+  B200C_CHECK_ARG(query_base >= 0, "Input mismatch");
   if ((st = check_device()) != B200C_OK) return st;
   if (m == 0) return B200C_OK;
   if (is16(dtype)) {
@@ -231,6 +231,7 @@ static int radius_common(const void *x, const void *y, const int64_t *ptr_x, con
     if ((st = widen_inputs(x, y, n, m, dim, dtype, workspace, !fill, stream)) != B200C_OK) return st;
     RadiusArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, r, max_num_neighbors,
                  ignore_same_index, counts, offsets, out_row, out_col, nullptr, stream};
+    a.query_base = query_base;
     return dtype == B200C_F16 ? launch_radius_generic_f16(a, fill) : launch_radius_generic_bf16(a, fill);
   }
   const size_t direct_bytes = radius_direct_bytes(m, dim, max_num_neighbors);
@@ -239,9 +240,21 @@ static int radius_common(const void *x, const void *y, const int64_t *ptr_x, con
                         : nullptr;
   RadiusArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, r, max_num_neighbors,
                ignore_same_index, counts, offsets, out_row, out_col, direct, stream};
+  a.query_base = query_base;
   B200C_CHECK_ARG(dim <= 0x7fffffffLL / 4, "Input mismatch");
   if (dim <= 8) return dtype == B200C_F32 ? launch_radius_lowd_f32(a, fill) : launch_radius_lowd_f64(a, fill);
   return dtype == B200C_F32 ? launch_radius_generic_f32(a, fill) : launch_radius_generic_f64(a, fill);
+}
+
+extern "C" int b200c_radius_count_part(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                                       int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
+                                       int64_t max_num_neighbors, int ignore_same_index, int64_t query_index_base,
+                                       int dtype, int32_t *counts, void *workspace, size_t workspace_bytes,
+                                       b200c_stream_t stream) {
+  B200C_CHECK_ARG(counts != nullptr || m == 0, "null output pointer");
+  return radius_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
+                       ignore_same_index, dtype, counts, nullptr, nullptr, nullptr, false, workspace,
+                       workspace_bytes, query_index_base, (cudaStream_t)stream);
 }
 
 extern "C" int b200c_radius_count(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
@@ -249,10 +262,24 @@ extern "C" int b200c_radius_count(const void *x, const void *y, const int64_t *p
                                   int64_t max_num_neighbors, int ignore_same_index, int dtype,
                                   int32_t *counts, void *workspace, size_t workspace_bytes,
                                   b200c_stream_t stream) {
-  B200C_CHECK_ARG(counts != nullptr || m == 0, "null output pointer");
+  return b200c_radius_count_part(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
+                                 ignore_same_index, 0, dtype, counts, workspace, workspace_bytes, stream);
+}
+
+extern "C" int b200c_radius_fill_part(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                                      int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
+                                      int64_t max_num_neighbors, int ignore_same_index, int64_t query_index_base,
+                                      int swap_rows, int dtype, const int32_t *counts, const int64_t *offsets,
+                                      int64_t num_edges, int64_t *edge_index, void *workspace,
+                                      size_t workspace_bytes, b200c_stream_t stream) {
+  B200C_CHECK_ARG(num_edges >= 0, "Input mismatch");
+  if (num_edges == 0) return B200C_OK;
+  B200C_CHECK_ARG(counts != nullptr && offsets != nullptr && edge_index != nullptr, "null pointer");
+  int64_t *row_q = swap_rows ? edge_index + num_edges : edge_index;
+  int64_t *row_x = swap_rows ? edge_index : edge_index + num_edges;
   return radius_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
-                       ignore_same_index, dtype, counts, nullptr, nullptr, nullptr, false, workspace,
-                       workspace_bytes, (cudaStream_t)stream);
+                       ignore_same_index, dtype, (int32_t *)counts, offsets, row_q, row_x, true, workspace,
+                       workspace_bytes, query_index_base, (cudaStream_t)stream);
 }
 
 extern "C" int b200c_radius_fill(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
@@ -261,24 +288,24 @@ extern "C" int b200c_radius_fill(const void *x, const void *y, const int64_t *pt
                                  const int32_t *counts, const int64_t *offsets, int64_t num_edges,
                                  int64_t *edge_index, void *workspace, size_t workspace_bytes,
                                  b200c_stream_t stream) {
-  B200C_CHECK_ARG(num_edges >= 0, "Input mismatch");
-  if (num_edges == 0) return B200C_OK;
-  B200C_CHECK_ARG(counts != nullptr && offsets != nullptr && edge_index != nullptr, "null pointer");
-  return radius_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
-                       ignore_same_index, dtype, (int32_t *)counts, offsets, edge_index,
-                       edge_index + num_edges, true, workspace, workspace_bytes, (cudaStream_t)stream);
+  return b200c_radius_fill_part(x, y, ptr_x, ptr_y, num_segments, n, m, dim, r, max_num_neighbors,
+                                ignore_same_index, 0, 0, dtype, counts, offsets, num_edges, edge_index, workspace,
+                                workspace_bytes, stream);
 }
 
 // ---- radius with a bit matrix of hits (every pair evaluated once, for large neighbour caps) ----------
 
 // First word of every segment's rows, from host copies of the segment pointers; returns the total number
 // of words.  A query of segment b owns ceil(n_b / chunk) * (chunk / 32) words.
-static int64_t radius_mask_layout(const int64_t *px, const int64_t *py, int64_t segs, int64_t n, int64_t m, int chunk,
-                                  std::vector<int64_t> *base) {
+// The host copies must describe x and y exactly (start at 0, never decrease, end at n / m): the
+// kernels derive the rows of a segment from the device copies with the reference's tolerant rule,
+// and a layout sized from anything else would be overrun.  Returns -1 for pointers that do not.
+static int64_t radius_mask_layout(const int64_t *px, const int64_t *py, int64_t segs, int64_t n, int64_t m, int chunk) {
+  if (px != nullptr && (px[0] != 0 || py[0] != 0 || px[segs] != n || py[segs] != m)) return -1;
   int64_t total = 0;
   for (int64_t b = 0; b < segs; ++b) {
     const int64_t nb = px ? px[b + 1] - px[b] : n, mb = py ? py[b + 1] - py[b] : m;
-    if (base) base->push_back(total);
+    if (nb < 0 || mb < 0) return -1;
     if (nb > 0 && mb > 0) total += mb * ((nb + chunk - 1) / chunk) * (chunk / 32);
   }
   return total;
@@ -290,24 +317,27 @@ extern "C" size_t b200c_radius_mask_workspace_bytes(const int64_t *ptr_x_host, c
   if (dim < 1 || dim > 8 || (dtype != B200C_F32 && dtype != B200C_F64) || num_segments < 1 || n <= 0 || m <= 0) return 0;
   if ((ptr_x_host == nullptr) != (ptr_y_host == nullptr) || (ptr_x_host == nullptr && num_segments != 1)) return 0;
   const int chunk = radius_lowd_chunk_points((int)dim, dtype);
-  const int64_t words = radius_mask_layout(ptr_x_host, ptr_y_host, num_segments, n, m, chunk, nullptr);
+  const int64_t words = radius_mask_layout(ptr_x_host, ptr_y_host, num_segments, n, m, chunk);
   return words > 0 ? align256((size_t)num_segments * 8) + (size_t)words * 4 : 0;
 }
 
-extern "C" int b200c_radius_count_masks(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
-                                        const int64_t *ptr_x_host, const int64_t *ptr_y_host, int64_t num_segments,
-                                        int64_t n, int64_t m, int64_t dim, double r, int64_t max_num_neighbors,
-                                        int ignore_same_index, int dtype, int32_t *counts, void *workspace,
-                                        size_t workspace_bytes, b200c_stream_t stream_) {
+extern "C" int b200c_radius_count_masks_part(const void *x, const void *y, const int64_t *ptr_x,
+                                             const int64_t *ptr_y, const int64_t *ptr_x_host,
+                                             const int64_t *ptr_y_host, int64_t num_segments, int64_t n, int64_t m,
+                                             int64_t dim, double r, int64_t max_num_neighbors, int ignore_same_index,
+                                             int64_t query_index_base, int dtype, int32_t *counts, void *workspace,
+                                             size_t workspace_bytes, b200c_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   int st = check_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, dtype);
   if (st != B200C_OK) return st;
   B200C_CHECK_ARG(max_num_neighbors >= 1, "max_num_neighbors must be positive");
   B200C_CHECK_ARG(counts != nullptr || m == 0, "null output pointer");
   B200C_CHECK_ARG((ptr_x == nullptr) == (ptr_x_host == nullptr), "device and host segment pointers must come together");
+  B200C_CHECK_ARG(query_index_base >= 0, "Input mismatch");
   const size_t need = b200c_radius_mask_workspace_bytes(ptr_x_host, ptr_y_host, num_segments, n, m, dim, dtype);
   if (need == 0) {
-    set_error("the bit-matrix radius search covers fp32 / fp64 points of up to 8 features");
+    set_error("the bit-matrix radius search covers fp32 / fp64 points of up to 8 features and needs host segment "
+              "pointers that start at 0, never decrease and end at the row counts");
     return B200C_ERR_UNSUPPORTED;
   }
   if (workspace == nullptr || workspace_bytes < need) {
@@ -315,20 +345,33 @@ extern "C" int b200c_radius_count_masks(const void *x, const void *y, const int6
     return B200C_ERR_WORKSPACE;
   }
   if ((st = check_device()) != B200C_OK) return st;
-  std::vector<int64_t> base;
-  radius_mask_layout(ptr_x_host, ptr_y_host, num_segments, n, m, radius_lowd_chunk_points((int)dim, dtype), &base);
-  B200C_CUDA(cudaMemcpyAsync(workspace, base.data(), base.size() * 8, cudaMemcpyHostToDevice, stream));
+  // the per-segment bases are formed on the device (no copy from pageable host memory, hence no
+  // hidden synchronisation of the stream); the host copies above only sized the workspace
+  if ((st = launch_radius_mask_base(ptr_x, ptr_y, (int)num_segments, n, m, radius_lowd_chunk_points((int)dim, dtype),
+                                    (int64_t *)workspace, stream)) != B200C_OK)
+    return st;
   RadiusArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, r, max_num_neighbors,
                ignore_same_index, counts, nullptr, nullptr, nullptr, nullptr, stream};
   a.mask_base = (const int64_t *)workspace;
   a.mask_words = (uint32_t *)((char *)workspace + align256((size_t)num_segments * 8));
+  a.query_base = query_index_base;
   return dtype == B200C_F32 ? launch_radius_lowd_f32(a, false) : launch_radius_lowd_f64(a, false);
 }
 
-extern "C" int b200c_radius_fill_masks(const int64_t *ptr_x, const int64_t *ptr_y, int64_t num_segments, int64_t n,
-                                       int64_t m, int64_t dim, int dtype, const int32_t *counts,
-                                       const int64_t *offsets, int64_t num_edges, int64_t *edge_index,
-                                       const void *workspace, b200c_stream_t stream_) {
+extern "C" int b200c_radius_count_masks(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
+                                        const int64_t *ptr_x_host, const int64_t *ptr_y_host, int64_t num_segments,
+                                        int64_t n, int64_t m, int64_t dim, double r, int64_t max_num_neighbors,
+                                        int ignore_same_index, int dtype, int32_t *counts, void *workspace,
+                                        size_t workspace_bytes, b200c_stream_t stream) {
+  return b200c_radius_count_masks_part(x, y, ptr_x, ptr_y, ptr_x_host, ptr_y_host, num_segments, n, m, dim, r,
+                                       max_num_neighbors, ignore_same_index, 0, dtype, counts, workspace,
+                                       workspace_bytes, stream);
+}
+
+extern "C" int b200c_radius_fill_masks_part(const int64_t *ptr_x, const int64_t *ptr_y, int64_t num_segments,
+                                            int64_t n, int64_t m, int64_t dim, int swap_rows, int dtype,
+                                            const int32_t *counts, const int64_t *offsets, int64_t num_edges,
+                                            int64_t *edge_index, const void *workspace, b200c_stream_t stream_) {
   B200C_CHECK_ARG(num_edges >= 0 && n >= 0 && m >= 0 && dim >= 1 && dim <= 8, "Input mismatch");
   B200C_CHECK_ARG(dtype == B200C_F32 || dtype == B200C_F64, "unsupported dtype");
   B200C_CHECK_ARG((ptr_x == nullptr) == (ptr_y == nullptr), "Input mismatch");
@@ -337,10 +380,19 @@ extern "C" int b200c_radius_fill_masks(const int64_t *ptr_x, const int64_t *ptr_
   int st = check_device();
   if (st != B200C_OK) return st;
   RadiusArgs a{nullptr, nullptr, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, 0.0, 0, 0, (int32_t *)counts, offsets,
-               edge_index, edge_index + num_edges, nullptr, (cudaStream_t)stream_};
+               swap_rows ? edge_index + num_edges : edge_index, swap_rows ? edge_index : edge_index + num_edges,
+               nullptr, (cudaStream_t)stream_};
   a.mask_base = (const int64_t *)workspace;
   a.mask_words = (uint32_t *)((char *)workspace + align256((size_t)num_segments * 8));
   return dtype == B200C_F32 ? launch_radius_lowd_f32(a, true) : launch_radius_lowd_f64(a, true);
+}
+
+extern "C" int b200c_radius_fill_masks(const int64_t *ptr_x, const int64_t *ptr_y, int64_t num_segments, int64_t n,
+                                       int64_t m, int64_t dim, int dtype, const int32_t *counts,
+                                       const int64_t *offsets, int64_t num_edges, int64_t *edge_index,
+                                       const void *workspace, b200c_stream_t stream) {
+  return b200c_radius_fill_masks_part(ptr_x, ptr_y, num_segments, n, m, dim, 0, dtype, counts, offsets, num_edges,
+                                      edge_index, workspace, stream);
 }
 
 // ---- nearest ------------------------------------------------------------------------------------------

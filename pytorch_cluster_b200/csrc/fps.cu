@@ -231,7 +231,7 @@ struct FpsSlot {
   unsigned long long pad;
 };
 
-constexpr int FPS_MULTI_SPIN_LIMIT = 1 << 24;
+constexpr int FPS_MULTI_SPIN_LIMIT = 1 << 20;  // polls of an L2 word: well under a second; co-residency is guaranteed by the cooperative launch, this is a safety net
 
 template <int DIM, int PT>
 __global__ void __launch_bounds__(FPS_THREADS, 1)
@@ -455,7 +455,10 @@ extern "C" int64_t b200c_fps_large_segment_max_points(int64_t dim, int dtype) {
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
   if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess || !coop) return 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-  const int64_t cap = (int64_t)sms * fps_multi_points_per_cta(dim);
+  // one CTA per SM (1024 threads holding their points in registers), at most the 256 CTAs the
+  // exchange slots in the workspace are laid out for
+  const int64_t ctas = sms < 256 ? sms : 256;
+  const int64_t cap = ctas * fps_multi_points_per_cta(dim);
   return cap < (1 << 24) ? cap : (1 << 24);  // offsets travel in 24 bits of the key
 }
 
@@ -465,6 +468,16 @@ template <int DIM, int PT>
 static int launch_fps_multi(const float *src, int64_t seg_lo, int64_t npts, int64_t start_offset, int64_t count,
                             int64_t *out, void *workspace, int32_t *status, cudaStream_t stream) {
   const int G = (int)((npts + (int64_t)FPS_THREADS * PT - 1) / ((int64_t)FPS_THREADS * PT));
+  // all G CTAs must be resident together: what this context can hold (fewer SMs than the device
+  // has under MPS or a green context) decides, not the device's SM count alone
+  int dev = 0, sms = 0, per_sm = 0;
+  B200C_CUDA(cudaGetDevice(&dev));
+  B200C_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  B200C_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_multi_kernel<DIM, PT>, FPS_THREADS, 0));
+  if (G > 256 || G > FPS_THREADS || (int64_t)G > (int64_t)per_sm * sms) {
+    set_error("fps: %d thread blocks cannot be resident together on this device (%d x %d)", G, per_sm, sms);
+    return B200C_ERR_UNSUPPORTED;
+  }
   FpsSlot *slots = (FpsSlot *)workspace;
   unsigned *counter = (unsigned *)((char *)workspace + 2 * 256 * sizeof(FpsSlot));
   B200C_CUDA(cudaMemsetAsync(counter, 0, 256, stream));
@@ -472,8 +485,13 @@ static int launch_fps_multi(const float *src, int64_t seg_lo, int64_t npts, int6
   void *args[] = {(void *)&src, (void *)&seg_lo, (void *)&npts, (void *)&start_offset, (void *)&count,
                   (void *)&out, (void *)&slots, (void *)&counter, (void *)&error_flag};
   // cooperative: all G CTAs are resident at once or the launch is refused
-  B200C_CUDA(cudaLaunchCooperativeKernel((const void *)fps_multi_kernel<DIM, PT>, dim3(G), dim3(FPS_THREADS), args, 0,
-                                         stream));
+  const cudaError_t le = cudaLaunchCooperativeKernel((const void *)fps_multi_kernel<DIM, PT>, dim3(G),
+                                                     dim3(FPS_THREADS), args, 0, stream);
+  if (le != cudaSuccess) {
+    (void)cudaGetLastError();  // a refused launch leaves nothing enqueued; the caller may use b200c_fps
+    set_error("cooperative launch of fps_multi_kernel refused: %s", cudaGetErrorString(le));
+    return B200C_ERR_UNSUPPORTED;
+  }
   return B200C_OK;
 }
 

@@ -108,7 +108,7 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
                T r2, int64_t max_nn, int ignore_same, const T *__restrict__ norms_x,
                const T *__restrict__ norms_y, const int64_t *__restrict__ offsets,
                int64_t *__restrict__ out_row, int64_t *__restrict__ out_col, int32_t *__restrict__ counts,
-               unsigned long long *__restrict__ num_valid) {
+               unsigned long long *__restrict__ num_valid, int64_t query_base) {
   using G = GenD<T>;
   using S = GenSmem<T, KP>;
   using K = Key<T>;
@@ -299,7 +299,7 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
                     knn_offer<T, KP, NR, !COSINE>(my_keys + qi * 2 * KP, my_cnt + qi, bound[qi], dist,
                                                   (uint32_t)idx0, k, lane);
                   else
-                    radius_fill_offer<T, NR>(dist, bound[qi], idx0, q, ignore_same != 0, cnt[qi], limit[qi],
+                    radius_fill_offer<T, NR>(dist, bound[qi], idx0, q, q + query_base, ignore_same != 0, cnt[qi], limit[qi],
                                              base[qi], out_row, out_col, lane);
                 }
               }
@@ -360,9 +360,10 @@ generic_kernel(const T *__restrict__ x, const T *__restrict__ y, const int64_t *
           for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(FULL_MASK, tot, o);
           if (lane == 0) {
             int64_t c = tot;
-            if (ignore_same && q >= x_lo && q < x_hi) {
+            const int64_t same = q + query_base;  // the x row with the query's own row number
+            if (ignore_same && same >= x_lo && same < x_hi) {
               T a = 0;
-              for (int d = 0; d < dim; ++d) a = sq_accumulate<RND>(x[q * dim + d], y[q * dim + d], a);
+              for (int d = 0; d < dim; ++d) a = sq_accumulate<RND>(x[same * dim + d], y[q * dim + d], a);
               if (a < r2) c -= 1;
             }
             counts[q] = (int32_t)(c < max_nn ? c : max_nn);

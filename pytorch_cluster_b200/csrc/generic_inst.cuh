@@ -23,7 +23,7 @@ static int launch_generic_one(const KnnArgs *ka, const RadiusArgs *ra) {
     kern<<<(unsigned)tiles, CTA_THREADS, S::SMEM_BYTES, ka->stream>>>(
         (const T *)ka->x, (const T *)ka->y, ka->ptr_x, ka->ptr_y, ka->num_segments, ka->n, ka->m, ka->dim,
         ka->k, (T)0, (int64_t)0, 0, (const T *)ka->norms_x, (const T *)ka->norms_y, nullptr, ka->out_row,
-        ka->out_col, ka->counts, ka->num_valid);
+        ka->out_col, ka->counts, ka->num_valid, (int64_t)0);
   } else {
     // formed in double, narrowed once (csrc/cuda/radius_cuda.cu:90); the 16-bit types narrow through
     // float, as the conversion constructors of c10::Half / c10::BFloat16 do
@@ -33,7 +33,7 @@ static int launch_generic_one(const KnnArgs *ka, const RadiusArgs *ra) {
     kern<<<(unsigned)tiles, CTA_THREADS, S::SMEM_BYTES, ra->stream>>>(
         (const T *)ra->x, (const T *)ra->y, ra->ptr_x, ra->ptr_y, ra->num_segments, ra->n, ra->m, ra->dim, 0,
         r2, ra->max_nn, ra->ignore_same, nullptr, nullptr, ra->offsets, ra->out_row, ra->out_col, ra->counts,
-        nullptr);
+        nullptr, ra->query_base);
   }
   B200C_LAUNCH_CHECK("generic_kernel");
   return B200C_OK;

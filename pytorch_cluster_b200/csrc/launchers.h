@@ -46,6 +46,8 @@ struct RadiusArgs {
   // bit-matrix mode: per-segment first word of the segment's rows, and the words
   const int64_t *mask_base = nullptr;
   uint32_t *mask_words = nullptr;
+  // row number of y's first row in the numbering of x: `ignore_same` skips x row q + query_base
+  int64_t query_base = 0;
 };
 
 int launch_knn_lowd_f32(const KnnArgs &a);
@@ -70,6 +72,8 @@ int launch_nearest_generic_f32(const KnnArgs &a);
 int launch_nearest_generic_f64(const KnnArgs &a);
 int launch_nearest_generic_f16(const KnnArgs &a);
 int launch_nearest_generic_bf16(const KnnArgs &a);
+int launch_radius_mask_base(const int64_t *ptr_x, const int64_t *ptr_y, int num_segments, int64_t n, int64_t m,
+                            int chunk, int64_t *base, cudaStream_t stream);
 int launch_widen16(const void *src, int64_t elems, int dtype, float *dst, cudaStream_t s);
 int launch_row_norms_f32(const void *a, int64_t rows, int dim, void *out, cudaStream_t s);
 int launch_row_norms_f64(const void *a, int64_t rows, int dim, void *out, cudaStream_t s);

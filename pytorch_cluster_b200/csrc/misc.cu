@@ -213,6 +213,47 @@ __global__ void widen16_kernel(const H *__restrict__ src, int64_t elems, float *
   }
 }
 
+// First bit-matrix word of every segment's rows for the bit-matrix radius search: the exclusive
+// sum over segments of m_b * ceil(n_b / chunk) * (chunk / 32), formed from the device copies of the
+// segment pointers.  One CTA: thread t sums a contiguous run of segments, the run totals are
+// scanned in shared memory, then every thread writes its segments' bases.
+constexpr int MASK_BASE_THREADS = 1024;
+__global__ void __launch_bounds__(MASK_BASE_THREADS)
+radius_mask_base_kernel(const int64_t *__restrict__ ptr_x, const int64_t *__restrict__ ptr_y, int num_segments,
+                        int64_t n, int64_t m, int chunk, int64_t *__restrict__ base) {
+  __shared__ int64_t run_total[MASK_BASE_THREADS];
+  const int t = threadIdx.x;
+  const int per = (num_segments + MASK_BASE_THREADS - 1) / MASK_BASE_THREADS;
+  const int lo = t * per < num_segments ? t * per : num_segments;
+  const int hi = lo + per < num_segments ? lo + per : num_segments;
+  auto words_of = [&](int b) -> int64_t {
+    const int64_t nb = ptr_x ? ptr_x[b + 1] - ptr_x[b] : n, mb = ptr_y ? ptr_y[b + 1] - ptr_y[b] : m;
+    return (nb > 0 && mb > 0) ? mb * ((nb + chunk - 1) / chunk) * (chunk / 32) : 0;
+  };
+  int64_t sum = 0;
+  for (int b = lo; b < hi; ++b) sum += words_of(b);
+  run_total[t] = sum;
+  __syncthreads();
+  for (int o = 1; o < MASK_BASE_THREADS; o <<= 1) {
+    const int64_t add = t >= o ? run_total[t - o] : 0;
+    __syncthreads();
+    run_total[t] += add;
+    __syncthreads();
+  }
+  int64_t run = run_total[t] - sum;  // exclusive
+  for (int b = lo; b < hi; ++b) {
+    base[b] = run;
+    run += words_of(b);
+  }
+}
+
+int launch_radius_mask_base(const int64_t *ptr_x, const int64_t *ptr_y, int num_segments, int64_t n, int64_t m,
+                            int chunk, int64_t *base, cudaStream_t stream) {
+  radius_mask_base_kernel<<<1, MASK_BASE_THREADS, 0, stream>>>(ptr_x, ptr_y, num_segments, n, m, chunk, base);
+  B200C_LAUNCH_CHECK("radius_mask_base_kernel");
+  return B200C_OK;
+}
+
 int launch_widen16(const void *src, int64_t elems, int dtype, float *dst, cudaStream_t stream) {
   if (elems == 0) return B200C_OK;
   const int64_t want = (elems + 255) / 256;

@@ -45,7 +45,7 @@ radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
                    int32_t *__restrict__ counts, const int64_t *__restrict__ offsets,
                    int64_t *__restrict__ out_row, int64_t *__restrict__ out_col,
                    int32_t *__restrict__ direct_rows, const int64_t *__restrict__ mask_base,
-                   uint32_t *__restrict__ mask_words) {
+                   uint32_t *__restrict__ mask_words, int64_t query_base) {
   using Cfg = RadiusLowD<T, DIM>;
   using C = LowD<T, DIM>;
   constexpr int QW = Cfg::QW, TQ = Cfg::TQ, R = C::R;
@@ -160,7 +160,9 @@ radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
             const int64_t q = q_lo + warp + (int64_t)qi * WARPS_PER_CTA;
             uint32_t word = lane < nwords ? my_masks[qi * 32 + lane] : 0u;
             if (ignore_same) {
-              const int64_t rel = q - first;  // the pair with equal row numbers is skipped
+              // the pair with equal row numbers is skipped; query_base is the row number of y's first
+              // row in the set x indexes (non-zero when y is a slice of a larger query set)
+              const int64_t rel = q + query_base - first;
               if (rel >= 0 && (rel >> 5) == lane) word &= ~(1u << (rel & 31));
             }
             const int mine = __popc(word);

@@ -20,7 +20,8 @@ static int launch_radius_lowd_one(const RadiusArgs &a) {
   const T r2 = (T)(a.r * a.r);  // formed in double, narrowed once (csrc/cuda/radius_cuda.cu:90)
   kern<<<(unsigned)tiles, CTA_THREADS, Cfg::SMEM_BYTES, a.stream>>>(
       (const T *)a.x, (const T *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, r2, a.max_nn,
-      a.ignore_same, a.counts, a.offsets, a.out_row, a.out_col, a.direct_rows, a.mask_base, a.mask_words);
+      a.ignore_same, a.counts, a.offsets, a.out_row, a.out_col, a.direct_rows, a.mask_base, a.mask_words,
+      a.query_base);
   B200C_LAUNCH_CHECK("radius_lowd_kernel");
   return B200C_OK;
 }

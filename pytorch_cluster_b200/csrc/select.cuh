@@ -201,17 +201,18 @@ __device__ __forceinline__ bool knn_finish_graph(Key<T> *keys, int cnt, int k1, 
   return true;
 }
 
-// Ordered append of radius hits.  `run` = hits of the query so far (warp-uniform).
+// Ordered append of radius hits.  `run` = hits of the query so far (warp-uniform); `same` = the x
+// row skipped when ignore_same (the query's own row number in x's numbering).
 template <typename T, int NR>
 __device__ __forceinline__ void radius_fill_offer(const T (&dist)[NR], T r2, int64_t idx0, int64_t q,
-                                                  bool ignore_same, int &run, int limit, int64_t base,
+                                                  int64_t same, bool ignore_same, int &run, int limit, int64_t base,
                                                   int64_t *__restrict__ out_row,
                                                   int64_t *__restrict__ out_col, int lane) {
   const unsigned lt_mask = (1u << lane) - 1u;
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
     const int64_t idx = idx0 + 32 * r;
-    const bool hit = dist[r] < r2 && !(ignore_same && idx == q);
+    const bool hit = dist[r] < r2 && !(ignore_same && idx == same);
     const unsigned mask = __ballot_sync(FULL_MASK, hit);
     if (mask) {
       const int pos = run + __popc(mask & lt_mask);

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "b200_cluster.h"
+#include "b200_cluster_torch.h"
 
 namespace {
 
@@ -89,6 +90,8 @@ Prepared prepare(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> 
   return p;
 }
 
+}  // namespace
+
 torch::Tensor knn(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
                   std::optional<torch::Tensor> ptr_y, int64_t k, bool cosine, int64_t num_workers) {
   (void)num_workers;  // no effect on the GPU, as in the reference
@@ -127,6 +130,8 @@ torch::Tensor knn(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor>
                                  stream.stream()));
   return out;
 }
+
+namespace {
 
 // knn_graph in one operator: kNN of x in x, then self-match removal, padding removal and flow
 // orientation on the device (torch_cluster/knn.py:131-144), with a single host sync for the size.
@@ -180,11 +185,15 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
   return out;
 }
 
-torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
-                     std::optional<torch::Tensor> ptr_y, double r, int64_t max_num_neighbors,
-                     int64_t num_workers, bool ignore_same_index) {
-  (void)num_workers;
+// The radius search behind `radius` and `radius_graph`.  query_index_base: row number of y's first row
+// in x's numbering, for `ignore_same_index` on a slice of the queries (multi-GPU); swap_rows: write
+// row 0 = x index, row 1 = query, the `source_to_target` orientation of radius_graph
+// (torch_cluster/radius.py:143-148), instead of stacking the rows again afterwards.
+torch::Tensor radius_part(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
+                          std::optional<torch::Tensor> ptr_y, double r, int64_t max_num_neighbors,
+                          bool ignore_same_index, int64_t query_index_base, bool swap_rows) {
   Prepared p = prepare(x, y, ptr_x, ptr_y);
+  TORCH_CHECK(query_index_base >= 0, "Input mismatch");
 
   c10::cuda::CUDAGuard guard(x.device());
   auto stream = at::cuda::getCurrentCUDAStream();
@@ -196,10 +205,12 @@ torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tens
   auto offsets = torch::empty({m + 1}, lopts);
   const size_t scan_bytes = b200c_scan_workspace_bytes(m);
   auto scan_ws = torch::empty({(int64_t)scan_bytes}, x.options().dtype(torch::kByte));
+  const int same = ignore_same_index ? 1 : 0, swap = swap_rows ? 1 : 0;
 
   // Large neighbour caps on low-dimensional points: every pair is evaluated once, its hit bit kept in
   // a bit matrix from which the edges are written afterwards.  The matrix's size depends on the segment
-  // sizes, so the segment pointers are read to the host (a second small sync of this call).
+  // sizes, so the segment pointers are read to the host (a second small sync of this call).  Pointers
+  // that do not describe x and y exactly make the size query answer 0 and take the route below.
   if (max_num_neighbors > kRadiusDirectCap && dim <= 8 && (p.dtype == B200C_F32 || p.dtype == B200C_F64)) {
     torch::Tensor hx, hy;
     const int64_t *hpx = nullptr, *hpy = nullptr;
@@ -212,17 +223,17 @@ torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tens
     const size_t mask_bytes = b200c_radius_mask_workspace_bytes(hpx, hpy, p.num_segments, n, m, dim, p.dtype);
     if (mask_bytes > 0 && mask_bytes <= kRadiusMaskMaxBytes) {
       auto mask_ws = torch::empty({(int64_t)mask_bytes}, x.options().dtype(torch::kByte));
-      check_status(b200c_radius_count_masks(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, hpx, hpy, p.num_segments, n, m,
-                                            dim, r, max_num_neighbors, ignore_same_index ? 1 : 0, p.dtype,
-                                            counts.data_ptr<int32_t>(), mask_ws.data_ptr(), mask_bytes,
-                                            stream.stream()));
+      check_status(b200c_radius_count_masks_part(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, hpx, hpy, p.num_segments,
+                                                 n, m, dim, r, max_num_neighbors, same, query_index_base, p.dtype,
+                                                 counts.data_ptr<int32_t>(), mask_ws.data_ptr(), mask_bytes,
+                                                 stream.stream()));
       check_status(b200c_exclusive_scan(counts.data_ptr<int32_t>(), m, offsets.data_ptr<int64_t>(), scan_ws.data_ptr(),
                                         scan_bytes, stream.stream()));
       const int64_t total = offsets[m].item<int64_t>();  // the output size
       auto out = torch::empty({2, total}, lopts);
-      check_status(b200c_radius_fill_masks(p.px, p.py, p.num_segments, n, m, dim, p.dtype, counts.data_ptr<int32_t>(),
-                                           offsets.data_ptr<int64_t>(), total, out.data_ptr<int64_t>(),
-                                           mask_ws.data_ptr(), stream.stream()));
+      check_status(b200c_radius_fill_masks_part(p.px, p.py, p.num_segments, n, m, dim, swap, p.dtype,
+                                                counts.data_ptr<int32_t>(), offsets.data_ptr<int64_t>(), total,
+                                                out.data_ptr<int64_t>(), mask_ws.data_ptr(), stream.stream()));
       return out;
     }
   }
@@ -231,19 +242,30 @@ torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tens
   const size_t ws_bytes = b200c_radius_workspace_bytes(n, m, dim, max_num_neighbors, p.dtype);
   auto ws = torch::empty({(int64_t)ws_bytes}, x.options().dtype(torch::kByte));
   void *ws_ptr = ws_bytes ? ws.data_ptr() : nullptr;
-  check_status(b200c_radius_count(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
-                                  max_num_neighbors, ignore_same_index ? 1 : 0, p.dtype,
-                                  counts.data_ptr<int32_t>(), ws_ptr, ws_bytes, stream.stream()));
+  check_status(b200c_radius_count_part(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
+                                       max_num_neighbors, same, query_index_base, p.dtype,
+                                       counts.data_ptr<int32_t>(), ws_ptr, ws_bytes, stream.stream()));
   check_status(b200c_exclusive_scan(counts.data_ptr<int32_t>(), m, offsets.data_ptr<int64_t>(),
                                     scan_ws.data_ptr(), scan_bytes, stream.stream()));
   const int64_t total = offsets[m].item<int64_t>();  // the one host sync: the output size
   auto out = torch::empty({2, total}, lopts);
-  check_status(b200c_radius_fill(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
-                                 max_num_neighbors, ignore_same_index ? 1 : 0, p.dtype,
-                                 counts.data_ptr<int32_t>(), offsets.data_ptr<int64_t>(), total,
-                                 out.data_ptr<int64_t>(), ws_ptr, ws_bytes, stream.stream()));
+  check_status(b200c_radius_fill_part(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
+                                      max_num_neighbors, same, query_index_base, swap, p.dtype,
+                                      counts.data_ptr<int32_t>(), offsets.data_ptr<int64_t>(), total,
+                                      out.data_ptr<int64_t>(), ws_ptr, ws_bytes, stream.stream()));
   return out;
 }
+
+}  // namespace
+
+torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
+                     std::optional<torch::Tensor> ptr_y, double r, int64_t max_num_neighbors,
+                     int64_t num_workers, bool ignore_same_index) {
+  (void)num_workers;  // no effect on the GPU, as in the reference
+  return radius_part(x, y, ptr_x, ptr_y, r, max_num_neighbors, ignore_same_index, 0, false);
+}
+
+namespace {
 
 // Device-side construction of the segment pointers from a sorted batch vector
 // (what torch_cluster/knn.py:77-79 does with torch.bucketize).
@@ -259,6 +281,8 @@ torch::Tensor segment_ptr(torch::Tensor batch, int64_t num_segments) {
                                  ptr.data_ptr<int64_t>(), at::cuda::getCurrentCUDAStream().stream()));
   return ptr;
 }
+
+}  // namespace
 
 // nearest: torch_cluster::nearest of csrc/nearest.cpp:22-36; host side of csrc/cuda/nearest_cuda.cu:63-88.
 torch::Tensor nearest(torch::Tensor x, torch::Tensor y, torch::Tensor ptr_x, torch::Tensor ptr_y) {
@@ -287,6 +311,36 @@ torch::Tensor nearest(torch::Tensor x, torch::Tensor y, torch::Tensor ptr_x, tor
                              ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
                              at::cuda::getCurrentCUDAStream().stream()));
   return out;
+}
+
+// Which segments of an fps call go where: `large` (more than per_cta points, at most multi_cap, at least
+// one sample) are sampled by many SMs together, `oversize` (more than multi_cap) by one thread block from
+// global memory in a call of their own; every other segment runs in the common call.
+static void fps_classify_segments(const int64_t *ptr, const int64_t *out_ptr, int64_t segments, int64_t per_cta,
+                                  int64_t multi_cap, std::vector<int64_t> *large, std::vector<int64_t> *oversize) {
+  for (int64_t b = 0; b < segments; ++b) {
+    const int64_t pts = ptr[b + 1] - ptr[b];
+    if (out_ptr[b + 1] <= out_ptr[b]) continue;
+    if (pts > per_cta && pts <= multi_cap) large->push_back(b);
+    else if (pts > multi_cap) oversize->push_back(b);
+  }
+}
+
+// The classification above on host tensors: -> int64 [segments], 0 = common call, 1 = large, 2 = oversize.
+torch::Tensor fps_segment_classes(torch::Tensor ptr, torch::Tensor out_ptr, int64_t per_cta, int64_t multi_cap) {
+  TORCH_CHECK(!ptr.is_cuda() && !out_ptr.is_cuda() && ptr.scalar_type() == at::kLong &&
+                  out_ptr.scalar_type() == at::kLong && ptr.numel() == out_ptr.numel() && ptr.numel() >= 1,
+              "fps_segment_classes expects two host int64 vectors of equal length");
+  ptr = ptr.contiguous();
+  out_ptr = out_ptr.contiguous();
+  const int64_t segments = ptr.numel() - 1;
+  std::vector<int64_t> large, oversize;
+  fps_classify_segments(ptr.data_ptr<int64_t>(), out_ptr.data_ptr<int64_t>(), segments, per_cta, multi_cap, &large,
+                        &oversize);
+  auto cls = torch::zeros({segments}, torch::kLong);
+  for (int64_t b : large) cls[b] = 1;
+  for (int64_t b : oversize) cls[b] = 2;
+  return cls;
 }
 
 // fps: torch_cluster::fps of csrc/fps.cpp:22-36; host side of csrc/cuda/fps_cuda.cu:70-112.  The
@@ -335,11 +389,10 @@ torch::Tensor fps(torch::Tensor src, torch::Tensor ptr, torch::Tensor ratio, boo
     torch::Tensor hstart;
     if (random_start) hstart = start.cpu();
     const int64_t *hp = hptr.data_ptr<int64_t>(), *ho = hout.data_ptr<int64_t>();
-    std::vector<int64_t> large;
-    for (int64_t b = 0; b < batch_size; ++b) {
-      const int64_t pts = hp[b + 1] - hp[b];
-      if (pts > per_cta && pts <= multi_cap && ho[b + 1] > ho[b]) large.push_back(b);
-    }
+    // large: sampled by many SMs together; oversize: beyond what those hold, one thread block each from
+    // global memory like every small segment, but in a call of their own (b200c_fps_up_to skips them)
+    std::vector<int64_t> large, oversize;
+    fps_classify_segments(hp, ho, batch_size, per_cta, multi_cap, &large, &oversize);
     if (!large.empty()) {
       check_status(b200c_fps_up_to(src.data_ptr(), ptr.data_ptr<int64_t>(), out_ptr.data_ptr<int64_t>(), start_ptr,
                                    batch_size, n, dim, dtype, per_cta, out.data_ptr<int64_t>(), ws.data_ptr(), ws_bytes,
@@ -347,11 +400,21 @@ torch::Tensor fps(torch::Tensor src, torch::Tensor ptr, torch::Tensor ratio, boo
       const size_t big_bytes = b200c_fps_large_segment_workspace_bytes();
       auto big_ws = torch::empty({(int64_t)big_bytes}, src.options().dtype(torch::kByte));
       auto status = torch::zeros({1}, src.options().dtype(torch::kInt));
-      for (int64_t b : large)
-        check_status(b200c_fps_large_segment(src.data_ptr(), hp[b], hp[b + 1] - hp[b],
-                                             random_start ? hstart.data_ptr<int64_t>()[b] : 0, ho[b + 1] - ho[b], dim,
-                                             dtype, out.data_ptr<int64_t>() + ho[b], big_ws.data_ptr(), big_bytes,
-                                             status.data_ptr<int32_t>(), stream.stream()));
+      for (int64_t b : large) {
+        const int st = b200c_fps_large_segment(src.data_ptr(), hp[b], hp[b + 1] - hp[b],
+                                               random_start ? hstart.data_ptr<int64_t>()[b] : 0, ho[b + 1] - ho[b], dim,
+                                               dtype, out.data_ptr<int64_t>() + ho[b], big_ws.data_ptr(), big_bytes,
+                                               status.data_ptr<int32_t>(), stream.stream());
+        if (st == B200C_ERR_UNSUPPORTED)
+          oversize.push_back(b);  // e.g. a context with too few SMs for a cooperative launch: one block does it
+        else
+          check_status(st);
+      }
+      // a one-segment call per remaining segment: the pointer arrays are entered at b
+      for (int64_t b : oversize)
+        check_status(b200c_fps(src.data_ptr(), ptr.data_ptr<int64_t>() + b, out_ptr.data_ptr<int64_t>() + b,
+                               start_ptr ? start_ptr + b : nullptr, 1, n, dim, dtype, out.data_ptr<int64_t>(),
+                               ws.data_ptr(), ws_bytes, stream.stream()));
       TORCH_CHECK(status.item<int32_t>() == 0, "b200_cluster: a wait between the thread blocks of fps ran out");
       return out;
     }
@@ -361,6 +424,16 @@ torch::Tensor fps(torch::Tensor src, torch::Tensor ptr, torch::Tensor ratio, boo
                          stream.stream()));
   return out;
 }
+
+// fps with the segment boundaries as a host list: no device-to-host read of the boundaries is
+// needed to find the segments that want the many-SM kernel.
+torch::Tensor fps_ptr_list(torch::Tensor src, std::vector<int64_t> ptr, torch::Tensor ratio, bool random_start) {
+  CHECK_CUDA(src);
+  auto ptr_dev = torch::tensor(ptr, torch::TensorOptions().dtype(torch::kLong)).to(src.device());
+  return fps(src, ptr_dev, ratio, random_start);
+}
+
+namespace {
 
 // knn_graph from host memory to host memory for low-dimensional points (loop = False): the call is cut
 // into groups of whole segments, one stream each, so that uploads and downloads of the other groups
@@ -420,6 +493,7 @@ int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool sourc
   char *xd = (char *)x_dev.data_ptr();
   int64_t *ed = edges_dev.data_ptr<int64_t>(), *oh = out.data_ptr<int64_t>();
   off = 0;
+  try {
   for (int64_t g = 0; g < groups; ++g) {
     streams.push_back(at::cuda::getStreamFromPool(false, (c10::DeviceIndex)device_index));
     cudaStream_t st = streams.back().stream();
@@ -436,6 +510,12 @@ int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool sourc
     C10_CUDA_CHECK(cudaMemcpyAsync(flags_host + g, flags_dev.data_ptr<int32_t>() + g, 4, cudaMemcpyDeviceToHost, st));
     off += nseg + 1;
   }
+  } catch (...) {
+    // copies and kernels already enqueued still use x_dev, edges_dev, the pinned buffer and `out`:
+    // let them finish before the buffers go back to their allocators
+    for (auto &s : streams) (void)cudaStreamSynchronize(s.stream());
+    throw;
+  }
   for (auto &s : streams) s.synchronize();
   int64_t irregular = 0;
   for (int64_t g = 0; g < groups; ++g) irregular += flags_host[g];
@@ -447,6 +527,9 @@ int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool sourc
 static auto registry = torch::RegisterOperators()
                            .op("torch_cluster::knn", &knn)
                            .op("torch_cluster::radius", &radius)
+                           .op("torch_cluster::radius_part", &radius_part)
+                           .op("torch_cluster::fps_ptr_list", &fps_ptr_list)
+                           .op("torch_cluster::fps_segment_classes", &fps_segment_classes)
                            .op("torch_cluster::segment_ptr", &segment_ptr)
                            .op("torch_cluster::knn_graph_edges", &knn_graph_edges)
                            .op("torch_cluster::nearest", &nearest)

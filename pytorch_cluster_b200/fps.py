@@ -54,21 +54,17 @@ def fps(  # noqa
 
     if ptr is not None:
         if isinstance(ptr, list):
-            return torch.ops.torch_cluster.fps(src, torch.tensor(ptr, device=src.device), r, random_start)
-        else:
-            return torch.ops.torch_cluster.fps(src, ptr, r, random_start)
+            # boundaries known on the host (torch_cluster/fps.py:84-86)
+            return torch.ops.torch_cluster.fps_ptr_list(src, ptr, r, random_start)
+        return torch.ops.torch_cluster.fps(src, ptr, r, random_start)
 
-    if batch is not None:
-        assert src.size(0) == batch.numel()
-        if batch_size is None:
-            batch_size = int(batch.max()) + 1
-        # batch need not be sorted here (torch_cluster/fps.py:98-103 counts members), so the
-        # boundaries come from a count, not from a bisection
-        deg = src.new_zeros(batch_size, dtype=torch.long)
-        deg.scatter_add_(0, batch, torch.ones_like(batch))
-        ptr_vec = deg.new_zeros(batch_size + 1)
-        torch.cumsum(deg, 0, out=ptr_vec[1:])
-    else:
-        ptr_vec = torch.tensor([0, src.size(0)], device=src.device)
+    if batch is None:
+        return torch.ops.torch_cluster.fps_ptr_list(src, [0, src.size(0)], r, random_start)
 
-    return torch.ops.torch_cluster.fps(src, ptr_vec, r, random_start)
+    assert src.size(0) == batch.numel()
+    num_examples = batch_size if batch_size is not None else int(batch.max()) + 1
+    # The example ids need not be sorted for this operator (torch_cluster/fps.py:98-103 counts
+    # members instead of bisecting), so the boundaries are the running sum of a histogram.
+    members = torch.bincount(batch, minlength=num_examples)
+    boundaries = torch.nn.functional.pad(members.cumsum(0), [1, 0])
+    return torch.ops.torch_cluster.fps(src, boundaries, r, random_start)

@@ -67,8 +67,10 @@ def uneven_batch(g, sizes):
 
 
 def main():
+    from oracle import build_ref
+
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--reference", default=build_ref.default_reference_dir())
     a = ap.parse_args()
     keep = bind_reference_ops()  # noqa: F841  (keeps the registration alive)
     ref_knn = load_by_path("ref_knn_py", os.path.join(a.reference, "torch_cluster", "knn.py"))

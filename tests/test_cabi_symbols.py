@@ -88,3 +88,62 @@ def test_cpu_tensors_are_refused_not_served():
         pc.radius_graph(torch.rand(8, 3), 0.5)
     # empty inputs never reach the operator (torch_cluster/knn.py:55-56)
     assert pc.knn(torch.empty(0, 3), torch.rand(2, 3), 2).shape == (2, 0)
+
+
+def test_fps_segment_classification():
+    """Which fps kernel a segment goes to: the common call (0), the many-SM kernel (1: more points than
+    one thread block keeps in registers, at most what all SMs hold) or a call of its own from global
+    memory (2: more than that).  Segments without samples stay in the common call."""
+    import pytorch_cluster_b200  # noqa: F401
+
+    ptr = torch.tensor([0, 10, 8202, 8202, 30000, 30010, 1300000, 1300005])
+    out = torch.tensor([0, 1, 3, 3, 4, 5, 6, 6])
+    cls = torch.ops.torch_cluster.fps_segment_classes(ptr, out, 8192, 1212416)
+    #            10 pts  8192   0 pts  21798  10   1269990  5 pts / no sample
+    assert cls.tolist() == [0, 0, 0, 1, 0, 2, 0]
+    cls = torch.ops.torch_cluster.fps_segment_classes(ptr, out, 8192, 20000)
+    assert cls.tolist() == [0, 0, 0, 2, 0, 2, 0]
+    big = torch.tensor([0, 8193]), torch.tensor([0, 0])
+    assert torch.ops.torch_cluster.fps_segment_classes(big[0], big[1], 8192, 100000).tolist() == [0]
+
+
+def test_cpp_api_header_links_against_the_operator_library(tmp_path):
+    """A libtorch program includes include/b200_cluster_torch.h, links _torch_ops.so and calls the free
+    functions `knn` and `radius` (the reference's C++ API, csrc/cluster.h:23-32).  Without a GPU the
+    calls must end in c10::Error "x must be CUDA tensor": there is no CPU branch."""
+    import subprocess
+
+    from torch.utils import cpp_extension as ce
+
+    from pytorch_cluster_b200 import _native
+
+    src = tmp_path / "use_api.cpp"
+    src.write_text('''
+#include "b200_cluster_torch.h"
+#include <iostream>
+int main() {
+  auto x = torch::rand({16, 3});
+  int caught = 0;
+  try { knn(x, x, std::nullopt, std::nullopt, 4, false, 1); } catch (const c10::Error &e) {
+    caught += std::string(e.what()).find("x must be CUDA tensor") != std::string::npos;
+  }
+  try { radius(x, x, std::nullopt, std::nullopt, 0.5, 8, 1, false); } catch (const c10::Error &e) {
+    caught += std::string(e.what()).find("x must be CUDA tensor") != std::string::npos;
+  }
+  try { nearest(x, x, torch::tensor({0, 16}), torch::tensor({0, 16})); } catch (const c10::Error &e) { caught += 1; }
+  try { fps(x, torch::tensor({0, 16}), torch::tensor(0.5), false); } catch (const c10::Error &e) { caught += 1; }
+  std::cout << "caught " << caught << std::endl;
+  return caught == 4 ? 0 : 1;
+}
+''')
+    exe = tmp_path / "use_api"
+    pkg = os.path.dirname(_native.LIB_OPS)
+    lib_dir = ce.library_paths()[0]
+    cmd = ["g++", "-std=c++17", "-O0", str(src), "-o", str(exe), f"-I{os.path.join(ROOT, 'include')}"]
+    cmd += [f"-I{p}" for p in ce.include_paths()]
+    cmd += [f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", f"-L{pkg}", "-l:_torch_ops.so",
+            "-lb200cluster", f"-Wl,-rpath,{pkg}", f"-L{lib_dir}", f"-Wl,-rpath,{lib_dir}", "-ltorch", "-ltorch_cpu",
+            "-lc10"]
+    subprocess.run(cmd, check=True, capture_output=True, text=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr

@@ -287,3 +287,24 @@ def test_fps_api_mixes_small_and_large_segments():
         big = torch.rand(100000, 3, generator=g).to(DEV)
         bp = torch.tensor([0, 100000], device=DEV)
         assert torch.equal(fps(big, ptr=bp, ratio=r, random_start=False), refc.fps(big, bp, r, False))
+
+
+def test_fps_api_segment_beyond_the_many_sm_kernel_next_to_a_mid_size_one():
+    """One call holding a segment the many-SM kernel takes (more than 8192 points) and one larger than
+    all SMs together hold: the second runs from global memory in a call of its own, and a list of
+    boundaries gives the same samples as a tensor."""
+    from pytorch_cluster_b200 import _native, fps
+
+    cap = _native.cabi().b200c_fps_large_segment_max_points(3, 0)
+    assert cap >= 8192
+    sizes = [10000, cap + 1, 300]
+    g = torch.Generator().manual_seed(19)
+    x = torch.rand(sum(sizes), 3, generator=g)
+    ptr = _ptr(sizes)
+    ratio = torch.tensor([0.001, 4.0 / (cap + 1) - 1e-9, 0.01])
+    got = fps(x.to(DEV), ptr=ptr.to(DEV), ratio=ratio.to(DEV), random_start=False).cpu().numpy()
+    out_ptr = torch.cat([torch.zeros(1, dtype=torch.long),
+                         ((ptr[1:] - ptr[:-1]).float() * ratio).ceil().long().cumsum(0)])
+    assert np.array_equal(got, orc.fps(x.numpy(), ptr.numpy(), out_ptr.numpy()))
+    same = fps(x.to(DEV), ptr=ptr.tolist(), ratio=ratio.to(DEV), random_start=False).cpu().numpy()
+    assert np.array_equal(same, got)

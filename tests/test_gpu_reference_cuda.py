@@ -1,12 +1,7 @@
 """GPU parity against the reference's own CUDA kernels, compiled unmodified for sm_100a
 (``oracle/_ref/ref_cluster_cuda.so``): the product's operators must return the very same
 ``edge_index`` tensors — values and order — as ``knn_cuda`` (csrc/cuda/knn_cuda.cu:86-135) and
-``radius_cuda`` (csrc/cuda/radius_cuda.cu:44-96) on the same device tensors.  Also records how long
-the reference's kernels take on this GPU beside the product's (printed, and written as JSON when
-``B200C_REPORT_DIR`` names a directory)."""
-import json
-import os
-
+``radius_cuda`` (csrc/cuda/radius_cuda.cu:44-96) on the same device tensors.  (``bench.py --impl reference-cuda`` times the two side by side.)"""
 import pytest
 import torch
 
@@ -82,6 +77,15 @@ def test_knn_bipartite_two_clouds():
     _same(_ours_knn(x, y, px, py, 32), refc.knn(x, y, px, py, 32))
 
 
+def test_knn_bipartite_full_size():
+    """8 clouds x (131072 points, 8192 queries), 3-D in [0, 100)^3, k = 32."""
+    g = torch.Generator().manual_seed(3)
+    x = (100 * torch.rand(8 * 131072, 3, generator=g)).to(DEV)
+    y = (100 * torch.rand(8 * 8192, 3, generator=g)).to(DEV)
+    px, py = _ptr(8, 131072), _ptr(8, 8192)
+    _same(_ours_knn(x, y, px, py, 32), refc.knn(x, y, px, py, 32))
+
+
 @pytest.mark.parametrize("cosine", [False, True])
 @pytest.mark.parametrize("dim", [32, 64, 128])
 def test_knn_feature_space_tensor_path(cosine, dim):
@@ -147,78 +151,47 @@ def test_radius_dims(dim):
         _same(_ours_radius(x, y, px, py, r, max_nn, False), refc.radius(x, y, px, py, r, max_nn, False))
 
 
-def _ms(fn, reps=3):
-    fn()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(reps):
-        fn()
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) / reps
+def _reference_radius_per_cloud(x, y, clouds, nx, ny, r, max_nn, ignore_same):
+    """The reference's CUDA operator run cloud by cloud (ptr = None) with the indices shifted
+    afterwards: clouds are independent, so this is its result on the whole batch, without its
+    2 * M * max_num_neighbors int64 of padded output for the whole batch at once
+    (csrc/cuda/radius_cuda.cu:75-78: 69 GB for 64 clouds x 8192 points with a cap of 8192)."""
+    parts = []
+    for c in range(clouds):
+        e = refc.radius(x[c * nx:(c + 1) * nx], y[c * ny:(c + 1) * ny], None, None, r, max_nn, ignore_same)
+        e[0] += c * ny
+        e[1] += c * nx
+        parts.append(e)
+    return torch.cat(parts, dim=1)
 
 
-def test_time_beside_reference_kernels():
-    """Operator-level time (CUDA events, whole op call incl. its compaction) of the reference's CUDA
-    path and of this library on the same tensors, at the full sizes of the benchmark's workloads;
-    the two results are also compared (identical tensors).  The timing is a report, not a
-    threshold — except that the product must not be slower."""
-    rep = {}
+def test_radius_graph_full_size_untruncated():
+    """64 clouds x 8192 points, r = 0.05, neighbour cap 8192 (nothing is cut), self pairs skipped:
+    the edge set of the whole batch, bit for bit."""
+    x = _mixture(64, 8192)
+    p = _ptr(64, 8192)
+    ours = _ours_radius(x, x, p, p, 0.05, 8192, True)
+    _same(ours, _reference_radius_per_cloud(x, x, 64, 8192, 8192, 0.05, 8192, True))
+    assert ours.shape[1] > 40_000_000
 
-    def both(name, ref_fn, our_fn, ref_reps=3):
-        _same(our_fn(), ref_fn())
-        rep[name] = (_ms(ref_fn, ref_reps), _ms(our_fn))
 
-    g = torch.Generator().manual_seed(2)
-    x = torch.randn(32 * 4096, 3, generator=g).to(DEV)
-    p = _ptr(32, 4096)
-    both("knn_32x4096x3_k21", lambda: refc.knn(x, x, p, p, 21), lambda: _ours_knn(x, x, p, p, 21))
-    g = torch.Generator().manual_seed(3)
-    xb = (100 * torch.rand(8 * 131072, 3, generator=g)).to(DEV)
-    yb = (100 * torch.rand(8 * 8192, 3, generator=g)).to(DEV)
-    pxb, pyb = _ptr(8, 131072), _ptr(8, 8192)
-    both("knn_8x131072x8192x3_k32", lambda: refc.knn(xb, yb, pxb, pyb, 32), lambda: _ours_knn(xb, yb, pxb, pyb, 32), 1)
-    g = torch.Generator().manual_seed(4)
-    xf = torch.randn(16 * 2048, 64, generator=g).to(DEV)
-    pf = _ptr(16, 2048)
-    for cosine in (False, True):
-        both(f"knn_16x2048x64_k21_cosine{int(cosine)}", lambda: refc.knn(xf, xf, pf, pf, 21, cosine),
-             lambda: _ours_knn(xf, xf, pf, pf, 21, cosine))
-    xr = _mixture(64, 8192)
-    pr = _ptr(64, 8192)
-    both("radius_64x8192x3_r0.05_max64", lambda: refc.radius(xr, xr, pr, pr, 0.05, 64, True),
-         lambda: _ours_radius(xr, xr, pr, pr, 0.05, 64, True))
-    # max_num_neighbors = 8192 on all 64 clouds would make the reference allocate 2 x 34 GB of padded
-    # output plus masks; it is timed on 8 clouds instead
-    xs, ps = xr[: 8 * 8192].contiguous(), _ptr(8, 8192)
-    both("radius_8x8192x3_r0.05_max8192", lambda: refc.radius(xs, xs, ps, ps, 0.05, 8192, True),
-         lambda: _ours_radius(xs, xs, ps, ps, 0.05, 8192, True))
-    # nearest: every point of the 64 clouds to the closest of 2048 samples of its cloud; fps: 25 % of
-    # every cloud, first point first
-    from pytorch_cluster_b200 import cabi  # noqa: F401  (loads the operators)
-    ys = torch.cat([xr[c * 8192: c * 8192 + 2048] for c in range(64)]).contiguous()
-    pys = _ptr(64, 2048)
-    both("nearest_64x8192_to_2048x3", lambda: refc.nearest(xr, ys, pr, pys),
-         lambda: torch.ops.torch_cluster.nearest(xr, ys, pr, pys))
-    ratio = torch.tensor(0.25, device=DEV)
-    both("fps_64x8192x3_ratio0.25", lambda: refc.fps(xr, pr, ratio, False),
-         lambda: torch.ops.torch_cluster.fps(xr, pr, ratio, False), 1)
-    # one large cloud: 1024 samples of 1 M points (the reference runs a segment on one thread block)
-    xl = torch.rand(1 << 20, 3, generator=torch.Generator().manual_seed(6)).to(DEV)
-    pl = torch.tensor([0, 1 << 20], device=DEV)
-    rl = torch.tensor(1024 / (1 << 20) - 1e-9, device=DEV)
-    both("fps_1x1048576x3_1024_samples", lambda: refc.fps(xl, pl, rl, False),
-         lambda: torch.ops.torch_cluster.fps(xl, pl, rl, False), 1)
-    out = {k: {"reference_cuda_ms": round(a, 4), "this_library_ms": round(b, 4), "ratio": round(a / b, 2)}
-           for k, (a, b) in rep.items()}
-    print(json.dumps(out, indent=1))
-    d = os.environ.get("B200C_REPORT_DIR")
-    if d and os.path.isdir(d):
-        with open(os.path.join(d, "reference_cuda_timings.json"), "w") as f:
-            json.dump(out, f, indent=1)
-    for k, v in out.items():
-        assert v["ratio"] >= 1.0, (k, v)
+@pytest.mark.parametrize("max_nn", [64, 8192])
+def test_radius_bipartite_full_size(max_nn):
+    """The queries are a sorted 25 % subset of every cloud (2048 of 8192 rows), all 64 clouds."""
+    x = _mixture(64, 8192)
+    keep = torch.cat([torch.randperm(8192, generator=torch.Generator().manual_seed(9 + c))[:2048].sort().values + 8192 * c
+                      for c in range(64)]).to(DEV)
+    y = x[keep].contiguous()
+    p, py = _ptr(64, 8192), _ptr(64, 2048)
+    _same(_ours_radius(x, y, p, py, 0.05, max_nn, False),
+          _reference_radius_per_cloud(x, y, 64, 8192, 2048, 0.05, max_nn, False))
+
+
+def test_radius_graph_full_size_truncated():
+    """The same 64 clouds with a cap of 64: the surviving hits are the reference's (lowest x rows)."""
+    x = _mixture(64, 8192)
+    p = _ptr(64, 8192)
+    _same(_ours_radius(x, x, p, p, 0.05, 64, True), refc.radius(x, x, p, p, 0.05, 64, True))
 
 
 # ---- 16-bit inputs: the reference instantiates knn for c10::Half and radius for c10::Half and
