@@ -56,6 +56,11 @@ const char *b200c_last_error(void);
 int b200c_segment_ptr(const int64_t *batch, int64_t n, int64_t num_segments,
                       int64_t *ptr, b200c_stream_t stream);
 
+/* info[0] = number of segments (last id + 1), info[1] = rows of the largest segment of a sorted batch
+ * vector (int64 [2], device).  The first replaces the `batch.max()` reduction of
+ * torch_cluster/knn.py:62-69; the second is the max_segment_rows hint of b200c_knn. */
+int b200c_batch_info(const int64_t *batch, int64_t n, int64_t *info, b200c_stream_t stream);
+
 /* Exclusive prefix sum of per-query edge counts:
  *   offsets[0] = 0, offsets[i + 1] = offsets[i] + counts[i];  offsets[m] = E.
  * Replaces the mask + masked_select compaction of csrc/cuda/radius_cuda.cu:94-95
@@ -109,15 +114,25 @@ int b200c_exclusive_scan_static(const int32_t *counts, int64_t m, int64_t *offse
  *
  * workspace: b200c_knn_workspace_bytes(...) bytes (may be 0).  The cosine distance needs one (the
  * rows' norms) and so do the 16-bit types (float copies of x and y); for these the full reported
- * size is required.  For fp32 features (32 <= dim <= 128, dim % 8 == 0, k <= 32) the full size
- * additionally enables the tensor-core candidate path; without it the exact kernels run. */
+ * size is required.  For fp32 the full size additionally enables the faster paths — for features
+ * (32 <= dim <= 128, dim % 8 == 0, k <= 32) the tensor-core candidate path, for up to 8 features
+ * (k <= 64, segments of 1024 points and more on average) the scan over Morton-ordered copies of x
+ * and y that the call builds in the workspace; without it the plain exact kernels run.  All paths
+ * return the same arrays.
+ *
+ * max_segment_rows: an upper bound of the row count of any segment of x or y, 0 when unknown (then
+ * n and m are taken).  It only limits how many sorting passes the Morton-ordered path enqueues.
+ *
+ * The Morton-ordered path moves its chunks with bulk asynchronous copies whose waits are
+ * bounded; if one ever runs out, 2^62 is added to *num_valid and the output is not valid. */
 size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t k,
                                  int dtype, int cosine, int64_t num_segments);
 int b200c_knn(const void *x, const void *y, const int64_t *ptr_x,
               const int64_t *ptr_y, int64_t num_segments, int64_t n, int64_t m,
               int64_t dim, int64_t k, int dtype, int cosine,
               int64_t *edge_padded, int32_t *counts, int64_t *num_valid,
-              void *workspace, size_t workspace_bytes, b200c_stream_t stream);
+              int64_t max_segment_rows, void *workspace, size_t workspace_bytes,
+              b200c_stream_t stream);
 
 /* Drops the -1 slots: edge_index (int64 [2, num_edges]) receives, for each
  * query q, its counts[q] valid slots at offsets[q].. (csrc/cuda/knn_cuda.cu:133-134). */
@@ -150,10 +165,17 @@ int b200c_knn_graph_tail_write(const int64_t *edge_padded, const int32_t *counts
  * number of queries that do not have that shape (segments of fewer than k + 1 points; rows
  * pushed out of their own list by k + 1 exact duplicates); their slots are left unwritten.  When
  * it is 0 the result is final, otherwise run b200c_knn and the tail entry points instead.
- * Returns B200C_ERR_UNSUPPORTED for more than 8 features and for the 16-bit types. */
+ * Returns B200C_ERR_UNSUPPORTED for more than 8 features and for the 16-bit types.
+ *
+ * workspace (optional): b200c_knn_graph_workspace_bytes(...) bytes enable the scan over a
+ * Morton-ordered copy of x for fp32 (see b200c_knn; max_segment_rows as there).  Should one of
+ * that path's bounded waits run out, 2^30 is added to *irregular. */
+size_t b200c_knn_graph_workspace_bytes(int64_t n, int64_t dim, int64_t k, int dtype,
+                                       int64_t num_segments);
 int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n,
                     int64_t dim, int64_t k, int dtype, int source_to_target,
-                    int64_t *edge_index, int32_t *irregular, b200c_stream_t stream);
+                    int64_t *edge_index, int32_t *irregular, int64_t max_segment_rows,
+                    void *workspace, size_t workspace_bytes, b200c_stream_t stream);
 
 /* The same for a part of a larger point set, so that a host can cut one knn_graph call into
  * groups of whole segments and overlap their copies with the search of the next group: x, ptr,
@@ -164,7 +186,8 @@ int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_segments, int
 int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n,
                          int64_t dim, int64_t k, int dtype, int source_to_target,
                          int64_t index_base, int64_t *edge_row0, int64_t row_stride,
-                         int32_t *irregular, b200c_stream_t stream);
+                         int32_t *irregular, int64_t max_segment_rows, void *workspace,
+                         size_t workspace_bytes, b200c_stream_t stream);
 
 /* Fixed-radius search — replaces radius_kernel and its -1 padded output
  * (csrc/cuda/radius_cuda.cu:9-42, 75-95) by count -> exclusive scan -> fill.

@@ -48,13 +48,15 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_version.restype = i32
     lib.b200c_last_error.restype = ctypes.c_char_p
     lib.b200c_segment_ptr.argtypes = [p, i64, i64, p, p]
+    lib.b200c_batch_info.argtypes = [p, i64, p, p]
+    lib.b200c_batch_info.restype = i32
     lib.b200c_scan_workspace_bytes.argtypes = [i64]
     lib.b200c_scan_workspace_bytes.restype = sz
     lib.b200c_exclusive_scan.argtypes = [p, i64, p, p, sz, p]
     lib.b200c_exclusive_scan_static.argtypes = [p, i64, p, p]
     lib.b200c_knn_workspace_bytes.argtypes = [i64, i64, i64, i64, i32, i32, i64]
     lib.b200c_knn_workspace_bytes.restype = sz
-    lib.b200c_knn.argtypes = [p, p, p, p, i64, i64, i64, i64, i64, i32, i32, p, p, p, p, sz, p]
+    lib.b200c_knn.argtypes = [p, p, p, p, i64, i64, i64, i64, i64, i32, i32, p, p, p, i64, p, sz, p]
     lib.b200c_knn_compact.argtypes = [p, p, p, i64, i64, i64, p, p]
     lib.b200c_knn_graph_tail_count.argtypes = [p, p, i64, i64, i32, p, p]
     lib.b200c_knn_graph_tail_write.argtypes = [p, p, p, i64, i64, i32, i32, i64, p, p]
@@ -72,9 +74,11 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_radius_count_masks_part.restype = i32
     lib.b200c_radius_fill_masks_part.argtypes = [p, p, i64, i64, i64, i64, i32, i32, p, p, i64, p, p, p]
     lib.b200c_radius_fill_masks_part.restype = i32
-    lib.b200c_knn_graph.argtypes = [p, p, i64, i64, i64, i64, i32, i32, p, p, p]
+    lib.b200c_knn_graph_workspace_bytes.argtypes = [i64, i64, i64, i32, i64]
+    lib.b200c_knn_graph_workspace_bytes.restype = sz
+    lib.b200c_knn_graph.argtypes = [p, p, i64, i64, i64, i64, i32, i32, p, p, i64, p, sz, p]
     lib.b200c_knn_graph.restype = i32
-    lib.b200c_knn_graph_part.argtypes = [p, p, i64, i64, i64, i64, i32, i32, i64, p, i64, p, p]
+    lib.b200c_knn_graph_part.argtypes = [p, p, i64, i64, i64, i64, i32, i32, i64, p, i64, p, i64, p, sz, p]
     lib.b200c_knn_graph_part.restype = i32
     lib.b200c_radius_mask_workspace_bytes.argtypes = [p, p, i64, i64, i64, i64, i32]
     lib.b200c_radius_mask_workspace_bytes.restype = sz

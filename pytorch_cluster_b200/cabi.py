@@ -38,7 +38,7 @@ def exclusive_scan(counts):
     return offsets
 
 
-def knn_padded_nosync(x, y, k, ptr_x=None, ptr_y=None, cosine=False, workspace=True):
+def knn_padded_nosync(x, y, k, ptr_x=None, ptr_y=None, cosine=False, workspace=True, max_segment_rows=0):
     """-> (edge_padded int64 [2, m*k], counts int32 [m], num_valid int64 [1]); nothing is read back.
     workspace=False withholds the optional workspace, which selects the kernels that need none."""
     lib = _native.cabi()
@@ -50,20 +50,21 @@ def knn_padded_nosync(x, y, k, ptr_x=None, ptr_y=None, cosine=False, workspace=T
     nbytes = lib.b200c_knn_workspace_bytes(n, m, dim, k, _dtype(x), int(cosine), nseg) if (workspace or cosine or x.element_size() == 2) else 0
     ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
     _native.check(lib.b200c_knn(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, k, _dtype(x),
-                                int(cosine), _p(padded), _p(counts), _p(nvalid), _p(ws), nbytes, _stream()))
+                                int(cosine), _p(padded), _p(counts), _p(nvalid), max_segment_rows, _p(ws), nbytes,
+                                _stream()))
     return padded, counts, nvalid
 
 
-def knn_padded(x, y, k, ptr_x=None, ptr_y=None, cosine=False, workspace=True):
+def knn_padded(x, y, k, ptr_x=None, ptr_y=None, cosine=False, workspace=True, max_segment_rows=0):
     """-> (edge_padded int64 [2, m*k], counts int32 [m], num_valid int)"""
-    padded, counts, nvalid = knn_padded_nosync(x, y, k, ptr_x, ptr_y, cosine, workspace)
+    padded, counts, nvalid = knn_padded_nosync(x, y, k, ptr_x, ptr_y, cosine, workspace, max_segment_rows)
     return padded, counts, int(nvalid.item())
 
 
-def knn(x, y, k, ptr_x=None, ptr_y=None, cosine=False):
+def knn(x, y, k, ptr_x=None, ptr_y=None, cosine=False, workspace=True, max_segment_rows=0):
     """Compacted edge_index through b200c_knn (+ scan + compact when needed)."""
     lib = _native.cabi()
-    padded, counts, nvalid = knn_padded(x, y, k, ptr_x, ptr_y, cosine)
+    padded, counts, nvalid = knn_padded(x, y, k, ptr_x, ptr_y, cosine, workspace, max_segment_rows)
     m = y.shape[0]
     if nvalid == m * k:
         return padded
@@ -136,15 +137,23 @@ def fps(src, ptr, out_ptr, start=None):
     return out
 
 
-def knn_graph(x, k, ptr=None, source_to_target=True):
-    """-> (edge_index int64 [2, n*k], irregular int): b200c_knn_graph; edge_index is final iff irregular == 0."""
+def knn_graph_nosync(x, k, ptr=None, source_to_target=True, workspace=True, max_segment_rows=0):
+    """-> (edge_index int64 [2, n*k], irregular int32 [1]): b200c_knn_graph, nothing read back."""
     lib = _native.cabi()
     n, dim = x.shape
     nseg = 1 if ptr is None else ptr.numel() - 1
     out = torch.empty(2, n * k, dtype=torch.long, device=x.device)
     irregular = torch.empty(1, dtype=torch.int32, device=x.device)
+    nbytes = lib.b200c_knn_graph_workspace_bytes(n, dim, k, _dtype(x), nseg) if workspace else 0
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
     _native.check(lib.b200c_knn_graph(_p(x), _p(ptr), nseg, n, dim, k, _dtype(x), int(source_to_target), _p(out),
-                                      _p(irregular), _stream()))
+                                      _p(irregular), max_segment_rows, _p(ws) if nbytes else None, nbytes, _stream()))
+    return out, irregular
+
+
+def knn_graph(x, k, ptr=None, source_to_target=True, workspace=True, max_segment_rows=0):
+    """-> (edge_index int64 [2, n*k], irregular int): b200c_knn_graph; edge_index is final iff irregular == 0."""
+    out, irregular = knn_graph_nosync(x, k, ptr, source_to_target, workspace, max_segment_rows)
     return out, int(irregular.item())
 
 

@@ -84,6 +84,9 @@ extern "C" size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, i
   // 16-bit types: float copies; cosine: |row| of every x and y row
   const size_t exact = widen_bytes(n, m, dim, dtype) +
                        (cosine ? align256((size_t)n * elem) + align256((size_t)m * elem) : 0);
+  // Morton-ordered copies for the low-dimensional fp32 scan (x == y cannot be known here: both copies)
+  if (dtype == B200C_F32 && !cosine && knn_spatial_applicable(n, m, (int)dim, (int)k, num_segments))
+    return knn_spatial_workspace_bytes(n, m, (int)dim, num_segments, false);
   // tensor-core candidate path: norms, candidate lists (and normalised copies for cosine)
   if (dtype == B200C_F32 && num_segments >= 1 &&
       knn_tensor_applicable(n, m, (int)dim, (int)k, num_segments, nullptr, nullptr)) {
@@ -96,7 +99,7 @@ extern "C" size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, i
 extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
                          int64_t num_segments, int64_t n, int64_t m, int64_t dim, int64_t k, int dtype,
                          int cosine, int64_t *edge_padded, int32_t *counts, int64_t *num_valid,
-                         void *workspace, size_t workspace_bytes, b200c_stream_t stream_) {
+                         int64_t max_segment_rows, void *workspace, size_t workspace_bytes, b200c_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   int st = check_common(x, y, ptr_x, ptr_y, num_segments, n, m, dim, dtype);
   if (st != B200C_OK) return st;
@@ -153,7 +156,12 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
     if (st != B200C_OK) return st;
     return f32 ? launch_knn_generic_f32(a) : launch_knn_generic_f64(a);
   }
-  if (dim <= 8) return f32 ? launch_knn_lowd_f32(a) : launch_knn_lowd_f64(a);
+  if (dim <= 8) {
+    if (f32 && workspace != nullptr && knn_spatial_applicable(n, m, (int)dim, (int)k, num_segments) &&
+        workspace_bytes >= knn_spatial_workspace_bytes(n, m, (int)dim, num_segments, x == y && ptr_x == ptr_y && n == m))
+      return launch_knn_spatial_f32(a, workspace, max_segment_rows);
+    return f32 ? launch_knn_lowd_f32(a) : launch_knn_lowd_f64(a);
+  }
   return f32 ? launch_knn_generic_f32(a) : launch_knn_generic_f64(a);
 }
 
@@ -161,6 +169,7 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
 extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
                                     int64_t k, int dtype, int source_to_target, int64_t index_base,
                                     int64_t *edge_row0, int64_t row_stride, int32_t *irregular,
+                                    int64_t max_segment_rows, void *workspace, size_t workspace_bytes,
                                     b200c_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   int st = check_common(x, x, ptr, ptr, num_segments, n, n, dim, dtype);
@@ -183,14 +192,24 @@ extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t n
   a.graph_index_base = index_base;
   a.graph_s2t = source_to_target;
   a.graph_irregular = (int *)irregular;
+  if (dtype == B200C_F32 && workspace != nullptr && knn_spatial_applicable(n, n, (int)dim, (int)(k + 1), num_segments) &&
+      workspace_bytes >= knn_spatial_workspace_bytes(n, n, (int)dim, num_segments, true))
+    return launch_knn_spatial_f32(a, workspace, max_segment_rows);
   return dtype == B200C_F32 ? launch_knn_lowd_f32(a) : launch_knn_lowd_f64(a);
+}
+
+extern "C" size_t b200c_knn_graph_workspace_bytes(int64_t n, int64_t dim, int64_t k, int dtype, int64_t num_segments) {
+  if (dtype == B200C_F32 && knn_spatial_applicable(n, n, (int)dim, (int)(k + 1), num_segments))
+    return knn_spatial_workspace_bytes(n, n, (int)dim, num_segments, true);
+  return 0;
 }
 
 extern "C" int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
                                int64_t k, int dtype, int source_to_target, int64_t *edge_index, int32_t *irregular,
+                               int64_t max_segment_rows, void *workspace, size_t workspace_bytes,
                                b200c_stream_t stream) {
   return b200c_knn_graph_part(x, ptr, num_segments, n, dim, k, dtype, source_to_target, 0, edge_index, n * k,
-                              irregular, stream);
+                              irregular, max_segment_rows, workspace, workspace_bytes, stream);
 }
 
 // One-pass mode keeps a row of max_num_neighbors int32 slots per query; it is used when that

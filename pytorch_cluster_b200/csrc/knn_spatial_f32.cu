@@ -1,0 +1,84 @@
+// Instantiations and host side of the Morton-ordered kNN scan (knn_spatial.cuh).
+#include "knn_spatial.cuh"
+#include "launchers.h"
+
+namespace b200c {
+
+template <int DIM, int KP>
+static int launch_knn_spatial_one(const KnnSpatialArgs &a, int64_t tiles, cudaStream_t stream) {
+  using Cfg = KnnSpatial<DIM, KP>;
+  auto kern = knn_spatial_kernel<DIM, KP>;
+  static unsigned long long configured = 0ull;  // devices on which the shared-memory opt-in is done
+  B200C_CUDA(opt_in_shared_memory(kern, Cfg::SMEM_BYTES, configured));
+  kern<<<(unsigned)tiles, KS_THREADS, Cfg::SMEM_BYTES, stream>>>(a);
+  B200C_LAUNCH_CHECK("knn_spatial_kernel");
+  return B200C_OK;
+}
+
+template <int DIM>
+static int launch_knn_spatial_dim(const KnnSpatialArgs &a, int64_t tiles, cudaStream_t stream) {
+  return a.k <= 32 ? launch_knn_spatial_one<DIM, 32>(a, tiles, stream)
+                   : launch_knn_spatial_one<DIM, 64>(a, tiles, stream);
+}
+
+bool knn_spatial_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_segments) {
+  // enough points per segment for the ordering to pay (a chunk is 256 points), and within the
+  // instantiated selection widths
+  return dim >= 1 && dim <= SP_MAX_DIM && k <= 64 && num_segments >= 1 && m >= 1 && n >= 2048 &&
+         n / num_segments >= 1024 && n <= 0x7fffffffLL - (int64_t)num_segments * SP_CHUNK;
+}
+
+size_t knn_spatial_workspace_bytes(int64_t n, int64_t m, int dim, int64_t num_segments, bool same_set) {
+  size_t bytes = spatial_view_bytes(n, dim, num_segments, true);
+  if (!same_set) bytes += spatial_view_bytes(m, dim, num_segments, false);
+  return bytes;
+}
+
+int launch_knn_spatial_f32(const KnnArgs &a, void *workspace, int64_t max_segment_rows) {
+  const bool same_set = a.x == a.y && a.ptr_x == a.ptr_y && a.n == a.m;
+  KnnSpatialArgs s{};
+  size_t off = spatial_view_carve(&s.xv, workspace, a.n, a.dim, a.num_segments, true);
+  int st = launch_spatial_sort((const float *)a.x, a.ptr_x, a.num_segments, a.n, a.dim, nullptr, true,
+                               max_segment_rows, &s.xv, a.stream);
+  if (st != B200C_OK) return st;
+  int64_t padded_queries;
+  if (same_set) {
+    s.yv = s.xv;
+    padded_queries = s.xv.cap;
+  } else {
+    spatial_view_carve(&s.yv, (char *)workspace + off, a.m, a.dim, a.num_segments, false);
+    // queries are keyed in the boxes of the points they are searched in; their segments are padded
+    // to chunks as well, which keeps every tile of 64 inside one segment
+    st = launch_spatial_sort((const float *)a.y, a.ptr_y, a.num_segments, a.m, a.dim, s.xv.box, false, 0, &s.yv,
+                             a.stream);
+    if (st != B200C_OK) return st;
+    padded_queries = s.yv.cap;
+  }
+  s.y = (const float *)a.y;
+  s.num_segments = a.num_segments;
+  s.k = a.k;
+  s.out_row = a.out_row;
+  s.out_col = a.out_col;
+  s.counts = a.counts;
+  s.num_valid = a.num_valid;
+  s.graph_out = a.graph_out;
+  s.graph_row_stride = a.graph_row_stride;
+  s.graph_index_base = a.graph_index_base;
+  s.graph_s2t = a.graph_s2t;
+  s.graph_irregular = a.graph_irregular;
+  const int64_t tiles = padded_queries / SP_TILE;  // an upper bound: blocks past the last segment leave at once
+  switch (a.dim) {
+    case 1: return launch_knn_spatial_dim<1>(s, tiles, a.stream);
+    case 2: return launch_knn_spatial_dim<2>(s, tiles, a.stream);
+    case 3: return launch_knn_spatial_dim<3>(s, tiles, a.stream);
+    case 4: return launch_knn_spatial_dim<4>(s, tiles, a.stream);
+    case 5: return launch_knn_spatial_dim<5>(s, tiles, a.stream);
+    case 6: return launch_knn_spatial_dim<6>(s, tiles, a.stream);
+    case 7: return launch_knn_spatial_dim<7>(s, tiles, a.stream);
+    case 8: return launch_knn_spatial_dim<8>(s, tiles, a.stream);
+  }
+  set_error("Morton-ordered kNN called with dim=%d", a.dim);
+  return B200C_ERR_INVALID;
+}
+
+}  // namespace b200c

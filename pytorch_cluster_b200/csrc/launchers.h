@@ -85,4 +85,11 @@ int launch_knn_tensor_f32(const KnnArgs &a, void *workspace);
 int launch_knn_rerank_f32(const KnnArgs &a, const int32_t *cand, const int32_t *cand_count, const int *error_flag,
                           const float *norms_x, const float *norms_y);
 
+// Morton-ordered scan for fp32 points of up to 8 features (knn_spatial.cuh): applicable sizes, the
+// workspace it needs (same_set: the queries are the points themselves, one sorted copy serves both),
+// and the launch (sorting passes + scan).  max_segment_rows: upper bound of a segment's row count, 0 = unknown.
+bool knn_spatial_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_segments);
+size_t knn_spatial_workspace_bytes(int64_t n, int64_t m, int dim, int64_t num_segments, bool same_set);
+int launch_knn_spatial_f32(const KnnArgs &a, void *workspace, int64_t max_segment_rows);
+
 }  // namespace b200c

@@ -26,6 +26,29 @@ __global__ void segment_ptr_kernel(const int64_t *__restrict__ batch, int64_t n,
   ptr[i] = lo;
 }
 
+// info[0] = batch[n - 1] + 1 (the ids are sorted, so the last is the largest), info[1] = rows of the
+// longest run of equal ids.  The thread at the last row of a run bisects for the run's first row.
+__global__ void batch_info_kernel(const int64_t *__restrict__ batch, int64_t n, unsigned long long *__restrict__ info) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  unsigned long long best = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int64_t id = batch[i];
+    if (i + 1 < n && batch[i + 1] == id) continue;
+    int64_t lo = 0, hi = i;
+    while (lo < hi) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (batch[mid] < id)
+        lo = mid + 1;
+      else
+        hi = mid;
+    }
+    const unsigned long long run = (unsigned long long)(i + 1 - lo);
+    best = run > best ? run : best;
+    if (i == n - 1) info[0] = (unsigned long long)(id + 1);
+  }
+  if (best) atomicMax(info + 1, best);
+}
+
 // ---- exclusive scan, int32 counts -> int64 offsets --------------------------------------------------
 constexpr int SCAN_THREADS = 256;
 constexpr int SCAN_ITEMS = 8;
@@ -279,6 +302,18 @@ extern "C" int b200c_segment_ptr(const int64_t *batch, int64_t n, int64_t num_se
   segment_ptr_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(
       batch, n, num_segments, ptr);
   B200C_LAUNCH_CHECK("segment_ptr_kernel");
+  return B200C_OK;
+}
+
+extern "C" int b200c_batch_info(const int64_t *batch, int64_t n, int64_t *info, b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  B200C_CHECK_ARG(n >= 0 && info != nullptr && (batch != nullptr || n == 0), "Input mismatch");
+  B200C_CUDA(cudaMemsetAsync(info, 0, 2 * sizeof(int64_t), stream));
+  if (n == 0) return B200C_OK;
+  const int64_t want = (n + 255) / 256;
+  batch_info_kernel<<<(unsigned)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(batch, n,
+                                                                                  (unsigned long long *)info);
+  B200C_LAUNCH_CHECK("batch_info_kernel");
   return B200C_OK;
 }
 

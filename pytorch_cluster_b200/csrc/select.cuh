@@ -60,9 +60,12 @@ __device__ __forceinline__ void knn_reset(Key<T> *keys, int lane) {
 // Cold start (nothing known yet, more hits than the queue holds): the k-th smallest of the 32
 // per-lane minima is an upper bound of the k-th smallest of all 32 NR candidates, so it is used
 // as a first filter instead of merging group after group.
-template <typename T, int KP, int NR, bool NONNEG>
-__device__ __forceinline__ void knn_offer(Key<T> *keys, int *cnt_s, T &bound, const T (&dist)[NR],
-                                          uint32_t idx0, int k, int lane) {
+//
+// knn_offer_at is the general form: `index_of(r)` gives the x index of the lane's candidate r;
+// knn_offer is the common case index_of(r) = idx0 + 32 r.
+template <typename T, int KP, int NR, bool NONNEG, typename IndexOf>
+__device__ __forceinline__ void knn_offer_at(Key<T> *keys, int *cnt_s, T &bound, const T (&dist)[NR],
+                                             IndexOf index_of, int k, int lane) {
   using K = Key<T>;
   int cnt = *cnt_s;
   T limit = bound;  // candidates must be < limit
@@ -108,7 +111,7 @@ __device__ __forceinline__ void knn_offer(Key<T> *keys, int *cnt_s, T &bound, co
             mask = __ballot_sync(FULL_MASK, hit);
             nh = __popc(mask);
           }
-          if (hit) keys[KP + cnt + __popc(mask & lt_mask)] = K::make(dist[r], idx0 + 32u * r);
+          if (hit) keys[KP + cnt + __popc(mask & lt_mask)] = K::make(dist[r], index_of(r));
           cnt += nh;
         }
       }
@@ -126,12 +129,19 @@ __device__ __forceinline__ void knn_offer(Key<T> *keys, int *cnt_s, T &bound, co
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
       if (dist[r] < limit) {
-        keys[p] = K::make(dist[r], idx0 + 32u * r);
+        keys[p] = K::make(dist[r], index_of(r));
         ++p;
       }
     }
   }
   __syncwarp();
+}
+
+template <typename T, int KP, int NR, bool NONNEG>
+__device__ __forceinline__ void knn_offer(Key<T> *keys, int *cnt_s, T &bound, const T (&dist)[NR],
+                                          uint32_t idx0, int k, int lane) {
+  knn_offer_at<T, KP, NR, NONNEG>(keys, cnt_s, bound, dist, [idx0](int r) { return idx0 + 32u * (uint32_t)r; }, k,
+                                  lane);
 }
 
 // Out-of-line form of knn_offer for hot loops that must stay small: the distances travel by

@@ -1,0 +1,64 @@
+// Spatially ordered copies of low-dimensional fp32 point sets, the input of the kNN scan of
+// knn_spatial.cuh.
+//
+// Brute-force kNN evaluates every (query, point) pair whatever the order of the points, and its
+// result does not depend on that order (candidates are ranked by (distance, original index)).
+// The order decides how fast a query's bound — its k-th best distance so far — falls, and
+// with it how often the scan has to leave its hit-free inner loop.  So each segment's points are
+// sorted along a Morton curve of the segment's bounding box; queries sorted the same way then
+// start their scan at the chunk of points around them and have their final bound after a few
+// chunks.
+//
+// Layout of a sorted set ("view") in the caller's workspace, all arrays indexed by the padded
+// sorted position p (every segment starts at a multiple of SP_CHUNK and is padded to one):
+//   ctr   [DIM][cap]  coordinates minus the centre of the segment's bounding box (padding: +inf)
+//   w     [cap]       squared norm of the centred point                          (padding: +inf)
+//   idx   [cap]       original row of the point, int32                            (padding: -1)
+//   org   [DIM][cap]  original coordinates (read only when a candidate is re-evaluated exactly)
+//   key   [cap]       Morton key, uint32                                (padding: 0xffffffff)
+//   sptr  [B + 1]     first padded position of every segment, int64
+//   box   [B][2 DIM]  bounding box (min, max per feature) of every segment's points
+//   stat  [B][2]      largest w of the segment (float bits of a non-negative value), spare
+#pragma once
+
+#include "common.cuh"
+
+namespace b200c {
+
+constexpr int SP_CHUNK = 256;         // points per chunk of the scan: 32 lanes x 8 points
+constexpr int SP_TILE = 64;           // queries per thread block of the scan
+constexpr int SP_SORT_BLOCK = 16384;  // keys one thread block sorts in shared memory
+constexpr int SP_MAX_DIM = 8;
+
+struct SpatialView {
+  float *ctr;       // [dim][cap]
+  float *w;         // [cap]
+  int32_t *idx;     // [cap]
+  float *org;       // [dim][cap]
+  uint32_t *key;    // [cap]
+  int64_t *sptr;    // [B + 1]
+  float *box;       // [B][2 * dim]
+  uint32_t *stat;   // [B][2]
+  int64_t cap;      // positions allocated: rows + B * (SP_CHUNK - 1), rounded up to SP_CHUNK
+  // scratch of the sort: 64-bit (key, local row) pairs, every segment padded to a power of two
+  uint64_t *pairs;  // [pairs_cap]
+  int64_t *pptr;    // [B + 1] first pair of every segment
+  int64_t *lptr;    // [B + 1] sort blocks (SP_SORT_BLOCK pairs) of the segments above one block, before each segment
+  int64_t pairs_cap;
+};
+
+// Bytes of workspace one view needs (points: with coordinates; queries: order and keys only).
+size_t spatial_view_bytes(int64_t rows, int dim, int64_t num_segments, bool points);
+// Carves a view out of `workspace` (256-byte aligned pieces); returns the bytes used.
+size_t spatial_view_carve(SpatialView *v, void *workspace, int64_t rows, int dim, int64_t num_segments, bool points);
+
+// Sorts the rows of `pts` ([rows, dim] fp32, segments ptr / num_segments) into `v`.  box_from:
+// nullptr to use the bounding boxes of these rows (written to v->box), else the boxes of another
+// view (queries are keyed in the box of the points they are searched in).  points: also write the
+// coordinate arrays.  max_segment_rows: an upper bound of any segment's row count (rows when
+// unknown); it only limits how many sorting passes are enqueued.
+int launch_spatial_sort(const float *pts, const int64_t *ptr, int64_t num_segments, int64_t rows, int dim,
+                        const float *box_from, bool points, int64_t max_segment_rows, SpatialView *v,
+                        cudaStream_t stream);
+
+}  // namespace b200c

@@ -92,9 +92,16 @@ Prepared prepare(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> 
 
 }  // namespace
 
-torch::Tensor knn(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
-                  std::optional<torch::Tensor> ptr_y, int64_t k, bool cosine, int64_t num_workers) {
-  (void)num_workers;  // no effect on the GPU, as in the reference
+namespace {
+
+// A bounded wait of the Morton-ordered scan ran out (see b200_cluster.h): never expected, never silent.
+constexpr int64_t kKnnWaitError = (int64_t)1 << 62;
+constexpr int32_t kGraphWaitError = 1 << 30;
+
+// knn with a hint: max_segment_rows bounds the row count of every segment (0 = unknown); it saves
+// empty sorting passes on inputs of many small segments.
+torch::Tensor knn_hinted(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
+                         std::optional<torch::Tensor> ptr_y, int64_t k, bool cosine, int64_t max_segment_rows) {
   Prepared p = prepare(x, y, ptr_x, ptr_y);
   TORCH_CHECK(k <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
   TORCH_CHECK(k >= 1, "`k` needs to be positive");
@@ -113,9 +120,10 @@ torch::Tensor knn(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor>
 
   check_status(b200c_knn(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, k, p.dtype,
                          cosine ? 1 : 0, padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(),
-                         num_valid.data_ptr<int64_t>(), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                         num_valid.data_ptr<int64_t>(), max_segment_rows, ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
                          stream.stream()));
   const int64_t total = num_valid.item<int64_t>();  // the one host sync: the output size
+  TORCH_CHECK(total < kKnnWaitError, "b200_cluster: a bounded wait of the kNN scan ran out");
   if (total == m * k) return padded;
 
   // some query had fewer than k admissible points: drop the -1 slots
@@ -131,12 +139,20 @@ torch::Tensor knn(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor>
   return out;
 }
 
+}  // namespace
+
+torch::Tensor knn(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
+                  std::optional<torch::Tensor> ptr_y, int64_t k, bool cosine, int64_t num_workers) {
+  (void)num_workers;  // no effect on the GPU, as in the reference
+  return knn_hinted(x, y, ptr_x, ptr_y, k, cosine, 0);
+}
+
 namespace {
 
 // knn_graph in one operator: kNN of x in x, then self-match removal, padding removal and flow
 // orientation on the device (torch_cluster/knn.py:131-144), with a single host sync for the size.
 torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr, int64_t k, bool loop,
-                              bool source_to_target, bool cosine) {
+                              bool source_to_target, bool cosine, int64_t max_segment_rows) {
   const int64_t k1 = loop ? k : k + 1;
   Prepared p = prepare(x, x, ptr, ptr);
   TORCH_CHECK(k1 <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
@@ -154,9 +170,14 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
     // else is detected there and takes the general route below
     auto out = torch::empty({2, n * k}, lopts);
     auto irregular = torch::empty({1}, iopts);
+    const size_t gws_bytes = b200c_knn_graph_workspace_bytes(n, dim, k, p.dtype, p.num_segments);
+    auto gws = torch::empty({(int64_t)gws_bytes}, x.options().dtype(torch::kByte));
     check_status(b200c_knn_graph(p.x.data_ptr(), p.px, p.num_segments, n, dim, k, p.dtype, source_to_target ? 1 : 0,
-                                 out.data_ptr<int64_t>(), irregular.data_ptr<int32_t>(), stream.stream()));
-    if (irregular.item<int32_t>() == 0) return out;  // the one host sync
+                                 out.data_ptr<int64_t>(), irregular.data_ptr<int32_t>(), max_segment_rows,
+                                 gws_bytes ? gws.data_ptr() : nullptr, gws_bytes, stream.stream()));
+    const int32_t odd = irregular.item<int32_t>();  // the one host sync
+    TORCH_CHECK(odd < kGraphWaitError, "b200_cluster: a bounded wait of the kNN scan ran out");
+    if (odd == 0) return out;
   }
 
   auto padded = torch::empty({2, n * k1}, lopts);
@@ -166,7 +187,7 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
   auto ws = torch::empty({(int64_t)ws_bytes}, x.options().dtype(torch::kByte));
   check_status(b200c_knn(p.x.data_ptr(), p.x.data_ptr(), p.px, p.px, p.num_segments, n, n, dim, k1, p.dtype,
                          cosine ? 1 : 0, padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(),
-                         num_valid.data_ptr<int64_t>(), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                         num_valid.data_ptr<int64_t>(), max_segment_rows, ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
                          stream.stream()));
   auto kept = torch::empty({n}, iopts);
   check_status(b200c_knn_graph_tail_count(padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(), n, k1,
@@ -176,7 +197,10 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
   auto scan_ws = torch::empty({(int64_t)scan_bytes}, x.options().dtype(torch::kByte));
   check_status(b200c_exclusive_scan(kept.data_ptr<int32_t>(), n, offsets.data_ptr<int64_t>(), scan_ws.data_ptr(),
                                     scan_bytes, stream.stream()));
-  const int64_t total = offsets[n].item<int64_t>();  // the one host sync: the output size
+  // the output size and the search's own count travel together: one host sync
+  auto sizes = torch::stack({offsets[n], num_valid[0]}).cpu();
+  const int64_t total = sizes[0].item<int64_t>();
+  TORCH_CHECK(sizes[1].item<int64_t>() < kKnnWaitError, "b200_cluster: a bounded wait of the kNN scan ran out");
   auto out = torch::empty({2, total}, lopts);
   check_status(b200c_knn_graph_tail_write(padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(),
                                           offsets.data_ptr<int64_t>(), n, k1, loop ? 0 : 1,
@@ -266,6 +290,23 @@ torch::Tensor radius(torch::Tensor x, torch::Tensor y, std::optional<torch::Tens
 }
 
 namespace {
+
+// [number of segments, rows of the largest segment] of a sorted batch vector (one host sync): what the
+// Python wrappers need to size the segment pointers (torch_cluster/knn.py:62-69 reads batch.max()),
+// plus the hint that saves empty sorting passes.
+std::vector<int64_t> batch_info(torch::Tensor batch) {
+  CHECK_CUDA(batch);
+  CHECK_INPUT(batch.dim() == 1);
+  TORCH_CHECK(batch.scalar_type() == at::kLong, "batch must be an int64 tensor");
+  if (batch.numel() == 0) return {0, 0};
+  batch = batch.contiguous();
+  c10::cuda::CUDAGuard guard(batch.device());
+  auto info = torch::empty({2}, batch.options());
+  check_status(b200c_batch_info(batch.data_ptr<int64_t>(), batch.numel(), info.data_ptr<int64_t>(),
+                                at::cuda::getCurrentCUDAStream().stream()));
+  auto host = info.cpu();
+  return {host[0].item<int64_t>(), host[1].item<int64_t>()};
+}
 
 // Device-side construction of the segment pointers from a sorted batch vector
 // (what torch_cluster/knn.py:77-79 does with torch.bucketize).
@@ -475,6 +516,15 @@ int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool sourc
   auto x_dev = torch::empty({n, dim}, dopts.dtype(x.scalar_type()));
   auto edges_dev = torch::empty({2, total}, dopts.dtype(torch::kLong));
   auto flags_dev = torch::empty({groups}, dopts.dtype(torch::kInt));
+  // every group's search may build a Morton-ordered copy of its points: one workspace per group
+  std::vector<size_t> ws_off(groups + 1, 0);
+  for (int64_t g = 0; g < groups; ++g) {
+    const size_t need = b200c_knn_graph_workspace_bytes(p[cut[g + 1]] - p[cut[g]], dim, k, dtype, cut[g + 1] - cut[g]);
+    ws_off[g + 1] = ws_off[g] + (need + 255) / 256 * 256;
+  }
+  auto ws_dev = torch::empty({(int64_t)ws_off[groups]}, dopts.dtype(torch::kByte));
+  int64_t max_rows = 0;
+  for (int64_t b = 0; b < segs; ++b) max_rows = std::max(max_rows, p[b + 1] - p[b]);
   auto ptr_dev = torch::empty({segs + groups}, dopts.dtype(torch::kLong));
   // every group's own pointers (starting at 0), back to back, and the flags coming back: pinned
   auto small = torch::empty({segs + groups + groups}, torch::TensorOptions().dtype(torch::kLong).pinned_memory(true));
@@ -503,7 +553,9 @@ int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool sourc
                                    cudaMemcpyHostToDevice, st));
     check_status(b200c_knn_graph_part(xd + r0 * dim * elem, ptr_dev.data_ptr<int64_t>() + off, nseg, r1 - r0, dim, k,
                                       dtype, source_to_target ? 1 : 0, r0, ed + r0 * k, total,
-                                      flags_dev.data_ptr<int32_t>() + g, st));
+                                      flags_dev.data_ptr<int32_t>() + g, max_rows,
+                                      ws_off[g + 1] > ws_off[g] ? (char *)ws_dev.data_ptr() + ws_off[g] : nullptr,
+                                      ws_off[g + 1] - ws_off[g], st));
     C10_CUDA_CHECK(cudaMemcpyAsync(oh + r0 * k, ed + r0 * k, (size_t)(r1 - r0) * k * 8, cudaMemcpyDeviceToHost, st));
     C10_CUDA_CHECK(cudaMemcpyAsync(oh + total + r0 * k, ed + total + r0 * k, (size_t)(r1 - r0) * k * 8,
                                    cudaMemcpyDeviceToHost, st));
@@ -519,6 +571,7 @@ int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool sourc
   for (auto &s : streams) s.synchronize();
   int64_t irregular = 0;
   for (int64_t g = 0; g < groups; ++g) irregular += flags_host[g];
+  TORCH_CHECK(irregular < kGraphWaitError, "b200_cluster: a bounded wait of the kNN scan ran out");
   return irregular;
 }
 
@@ -526,6 +579,8 @@ int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool sourc
 
 static auto registry = torch::RegisterOperators()
                            .op("torch_cluster::knn", &knn)
+                           .op("torch_cluster::knn_hinted", &knn_hinted)
+                           .op("torch_cluster::batch_info", &batch_info)
                            .op("torch_cluster::radius", &radius)
                            .op("torch_cluster::radius_part", &radius_part)
                            .op("torch_cluster::fps_ptr_list", &fps_ptr_list)

@@ -1,27 +1,33 @@
 """``knn`` / ``knn_graph`` with the reference's signatures (torch_cluster/knn.py:6-15, 85-94),
 TorchScript-able, on top of ``torch.ops.torch_cluster.knn``."""
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
 
-def _num_segments(rows: int, batch: Optional[torch.Tensor]) -> int:
-    # `batch` is sorted (a documented precondition, torch_cluster/knn.py:27), so its largest
-    # id is its last entry: one element crosses to the host instead of a reduction.
+def _batch_info(rows: int, batch: Optional[torch.Tensor]) -> List[int]:
+    # [number of segments, rows of the largest one].  `batch` is sorted (a documented precondition,
+    # torch_cluster/knn.py:27), so its largest id is its last entry; one small kernel finds both
+    # numbers and they cross to the host together (the reference reads batch.max()).
     if batch is None:
-        return 1
+        return [1, rows]
     assert rows == batch.numel()
-    return int(batch[-1]) + 1
+    return torch.ops.torch_cluster.batch_info(batch)
 
 
 def _segment_ptrs(x: torch.Tensor, y: torch.Tensor, batch_x: Optional[torch.Tensor],
                   batch_y: Optional[torch.Tensor],
-                  batch_size: Optional[int]) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+                  batch_size: Optional[int]) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor], int]:
     """Segment boundaries of x and y rows (torch_cluster/knn.py:62-79): B is inferred from the
-    batch vectors unless given, and pointers are only built for B > 1."""
+    batch vectors unless given, and pointers are only built for B > 1.  Third result: an upper bound
+    of any segment's row count, 0 when it is not known (B was given)."""
     num_segments = 1
+    max_rows = 0
     if batch_size is None:
-        num_segments = max(_num_segments(x.size(0), batch_x), _num_segments(y.size(0), batch_y))
+        info_x = _batch_info(x.size(0), batch_x)
+        info_y = _batch_info(y.size(0), batch_y)
+        num_segments = max(info_x[0], info_y[0])
+        max_rows = max(info_x[1], info_y[1])
     else:
         num_segments = batch_size
     assert num_segments > 0
@@ -32,15 +38,19 @@ def _segment_ptrs(x: torch.Tensor, y: torch.Tensor, batch_x: Optional[torch.Tens
         assert batch_y is not None
         ptr_x = torch.ops.torch_cluster.segment_ptr(batch_x, num_segments)
         ptr_y = torch.ops.torch_cluster.segment_ptr(batch_y, num_segments)
-    return ptr_x, ptr_y
+    return ptr_x, ptr_y, max_rows
 
 
 def _graph_ptr(x: torch.Tensor, batch: Optional[torch.Tensor],
-               batch_size: Optional[int]) -> Optional[torch.Tensor]:
-    """Segment boundaries when x is searched in itself: one pointer vector serves both sides."""
+               batch_size: Optional[int]) -> Tuple[Optional[torch.Tensor], int]:
+    """Segment boundaries when x is searched in itself: one pointer vector serves both sides.
+    Second result: an upper bound of any segment's row count, 0 when it is not known."""
     num_segments = 1
+    max_rows = 0
     if batch_size is None:
-        num_segments = _num_segments(x.size(0), batch)
+        info = _batch_info(x.size(0), batch)
+        num_segments = info[0]
+        max_rows = info[1]
     else:
         num_segments = batch_size
     assert num_segments > 0
@@ -48,7 +58,7 @@ def _graph_ptr(x: torch.Tensor, batch: Optional[torch.Tensor],
     if num_segments > 1:
         assert batch is not None
         ptr = torch.ops.torch_cluster.segment_ptr(batch, num_segments)
-    return ptr
+    return ptr, max_rows
 
 
 def knn(
@@ -77,8 +87,9 @@ def knn(
         y = y.view(-1, 1)
     x = x.contiguous()
     y = y.contiguous()
-    ptr_x, ptr_y = _segment_ptrs(x, y, batch_x, batch_y, batch_size)
-    return torch.ops.torch_cluster.knn(x, y, ptr_x, ptr_y, k, cosine, num_workers)
+    ptr_x, ptr_y, max_rows = _segment_ptrs(x, y, batch_x, batch_y, batch_size)
+    # the operator torch_cluster::knn with one more argument: the largest segment, when known
+    return torch.ops.torch_cluster.knn_hinted(x, y, ptr_x, ptr_y, k, cosine, max_rows)
 
 
 def knn_graph(
@@ -103,6 +114,6 @@ def knn_graph(
     if x.dim() == 1:
         x = x.view(-1, 1)
     x = x.contiguous()
-    ptr = _graph_ptr(x, batch, batch_size)
+    ptr, max_rows = _graph_ptr(x, batch, batch_size)
     # one operator: search, self-match and padding removal, flow orientation (one host sync)
-    return torch.ops.torch_cluster.knn_graph_edges(x, ptr, k, loop, flow == 'source_to_target', cosine)
+    return torch.ops.torch_cluster.knn_graph_edges(x, ptr, k, loop, flow == 'source_to_target', cosine, max_rows)

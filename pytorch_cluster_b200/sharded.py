@@ -85,6 +85,15 @@ class ShardPlan:
                                 torch.tensor(py, dtype=torch.long, device=device))
         return self._local[key]
 
+    def max_rows(self, rank: int) -> int:
+        """Rows of the rank's largest segment (x or y side); 0 for a single segment (not known here)."""
+        if self.ptr_x is None:
+            return 0
+        _, _, _, _, s0, s1 = self.ranges[rank]
+        sizes = [self.ptr_x[b + 1] - self.ptr_x[b] for b in range(s0, s1)]
+        sizes += [self.ptr_y[b + 1] - self.ptr_y[b] for b in range(s0, s1)]
+        return max(sizes) if sizes else 0
+
 
 def _host_ptrs(batch_x, batch_y, batch_size):
     """Segment pointers of both sides as host lists: ONE device-to-host transfer."""
@@ -135,12 +144,12 @@ class _DeviceOps:
     """The single-GPU operators a rank runs on its slice."""
 
     @staticmethod
-    def knn(x, y, ptr_x, ptr_y, k, cosine):
-        return torch.ops.torch_cluster.knn(x, y, ptr_x, ptr_y, k, cosine, 1)
+    def knn(x, y, ptr_x, ptr_y, k, cosine, max_rows=0):
+        return torch.ops.torch_cluster.knn_hinted(x, y, ptr_x, ptr_y, k, cosine, max_rows)
 
     @staticmethod
-    def knn_graph(x, ptr, k, loop, source_to_target, cosine):
-        return torch.ops.torch_cluster.knn_graph_edges(x, ptr, k, loop, source_to_target, cosine)
+    def knn_graph(x, ptr, k, loop, source_to_target, cosine, max_rows=0):
+        return torch.ops.torch_cluster.knn_graph_edges(x, ptr, k, loop, source_to_target, cosine, max_rows)
 
     @staticmethod
     def radius(x, y, ptr_x, ptr_y, r, max_num_neighbors, ignore_same_index, query_index_base, swap_rows):
@@ -232,7 +241,7 @@ def knn_sharded(x: torch.Tensor, y: torch.Tensor, k: int, batch_x: Optional[torc
     x_lo, x_hi, y_lo, y_hi, _, _ = plan.ranges[rank]
     if y_hi > y_lo and x_hi > x_lo:
         px, py = plan.local_ptrs(rank, x.device)
-        local = _shift(ops.knn(x[x_lo:x_hi], y[y_lo:y_hi], px, py, k, cosine), y_lo, x_lo)
+        local = _shift(ops.knn(x[x_lo:x_hi], y[y_lo:y_hi], px, py, k, cosine, plan.max_rows(rank)), y_lo, x_lo)
     else:
         local = torch.empty(2, 0, dtype=torch.long, device=x.device)
     return _finish(local, group, world, assemble)
@@ -275,7 +284,7 @@ def knn_graph_sharded(x: torch.Tensor, k: int, batch: Optional[torch.Tensor] = N
     elif plan.ptr_x is not None:
         # whole clouds: the slice is searched in itself, both rows shift by the slice's first row
         ptr, _ = plan.local_ptrs(rank, x.device)
-        local = _shift(ops.knn_graph(x[x_lo:x_hi], ptr, k, loop, s2t, cosine), x_lo, x_lo)
+        local = _shift(ops.knn_graph(x[x_lo:x_hi], ptr, k, loop, s2t, cosine, plan.max_rows(rank)), x_lo, x_lo)
     else:
         # one cloud: this rank's rows search all of x; the self match is the one whose shifted
         # query row equals the neighbour (the `row != col` mask of torch_cluster/knn.py:140-142)

@@ -39,7 +39,7 @@ def test_no_compute_entry_point_runs_without_valid_arguments():
     from pytorch_cluster_b200 import _native
 
     lib = _native.cabi()
-    st = lib.b200c_knn(None, None, None, None, 1, 10, 10, 3, 5, 0, 0, None, None, None, None, 0, None)
+    st = lib.b200c_knn(None, None, None, None, 1, 10, 10, 3, 5, 0, 0, None, None, None, 0, None, 0, None)
     assert st == 1 and b"CUDA tensors" in lib.b200c_last_error()
     st = lib.b200c_radius_count(None, None, None, None, 1, 10, 10, 3, 1.0, 32, 0, 0, None, None, 0, None)
     assert st == 1

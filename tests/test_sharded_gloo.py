@@ -21,11 +21,11 @@ class OracleOps:
     """The single-GPU operators of the sharded layer, answered by the CPU oracle."""
 
     @staticmethod
-    def knn(x, y, ptr_x, ptr_y, k, cosine):
+    def knn(x, y, ptr_x, ptr_y, k, cosine, max_rows=0):
         return torch.from_numpy(orc.knn(x.numpy(), y.numpy(), k, _np(ptr_x), _np(ptr_y), cosine))
 
     @staticmethod
-    def knn_graph(x, ptr, k, loop, source_to_target, cosine):
+    def knn_graph(x, ptr, k, loop, source_to_target, cosine, max_rows=0):
         e = orc.knn(x.numpy(), x.numpy(), k if loop else k + 1, _np(ptr), _np(ptr), cosine)
         row, col = (e[1], e[0]) if source_to_target else (e[0], e[1])
         if not loop:
