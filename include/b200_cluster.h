@@ -134,6 +134,23 @@ int b200c_knn(const void *x, const void *y, const int64_t *ptr_x,
               int64_t max_segment_rows, void *workspace, size_t workspace_bytes,
               b200c_stream_t stream);
 
+/* The ordering pass of the Morton-ordered scan on its own (fp32, up to 8 features): every segment's rows
+ * sorted by the Morton key of their cell in the segment's bounding box (ties by row).  No counterpart
+ * in the reference, which scans points in input order.
+ *   first [num_segments + 1]  (int64) first padded position of every segment, a multiple of 256;
+ *                             first[num_segments] <= b200c_morton_order_rows(n, num_segments)
+ *   order [rows]              (int32) the row of x at each position of a segment's range, -1 in the
+ *                             padding between a segment's last row and the next multiple of 256
+ *   keys  [rows]              (uint32) the row's Morton key, 0xffffffff in the padding
+ * Positions at and after first[num_segments] are not written.  workspace:
+ * b200c_morton_order_workspace_bytes(...) bytes; max_segment_rows as for b200c_knn. */
+size_t b200c_morton_order_workspace_bytes(int64_t n, int64_t dim, int64_t num_segments);
+int64_t b200c_morton_order_rows(int64_t n, int64_t num_segments);
+int b200c_morton_order(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n,
+                       int64_t dim, int64_t max_segment_rows, int32_t *order, uint32_t *keys,
+                       int64_t *first, void *workspace, size_t workspace_bytes,
+                       b200c_stream_t stream);
+
 /* Drops the -1 slots: edge_index (int64 [2, num_edges]) receives, for each
  * query q, its counts[q] valid slots at offsets[q].. (csrc/cuda/knn_cuda.cu:133-134). */
 int b200c_knn_compact(const int64_t *edge_padded, const int32_t *counts,

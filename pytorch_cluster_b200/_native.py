@@ -57,6 +57,12 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_knn_workspace_bytes.argtypes = [i64, i64, i64, i64, i32, i32, i64]
     lib.b200c_knn_workspace_bytes.restype = sz
     lib.b200c_knn.argtypes = [p, p, p, p, i64, i64, i64, i64, i64, i32, i32, p, p, p, i64, p, sz, p]
+    lib.b200c_morton_order_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.b200c_morton_order_workspace_bytes.restype = sz
+    lib.b200c_morton_order_rows.argtypes = [i64, i64]
+    lib.b200c_morton_order_rows.restype = i64
+    lib.b200c_morton_order.argtypes = [p, p, i64, i64, i64, i64, p, p, p, p, sz, p]
+    lib.b200c_morton_order.restype = i32
     lib.b200c_knn_compact.argtypes = [p, p, p, i64, i64, i64, p, p]
     lib.b200c_knn_graph_tail_count.argtypes = [p, p, i64, i64, i32, p, p]
     lib.b200c_knn_graph_tail_write.argtypes = [p, p, p, i64, i64, i32, i32, i64, p, p]

@@ -190,3 +190,19 @@ def fps_large_segment(src, seg_lo, seg_points, count, start_offset=0):
     _native.check(lib.b200c_fps_large_segment(_p(src), seg_lo, seg_points, start_offset, count, src.shape[1],
                                               _dtype(src), _p(out), _p(ws), nbytes, _p(status), _stream()))
     return out, int(status.item())
+
+
+def morton_order(x, ptr=None, max_segment_rows=0):
+    """-> (order int32 [rows], keys int32 [rows] (bit pattern of uint32), first int64 [B + 1]): b200c_morton_order."""
+    lib = _native.cabi()
+    n, dim = x.shape
+    nseg = 1 if ptr is None else ptr.numel() - 1
+    rows = lib.b200c_morton_order_rows(n, nseg)
+    order = torch.full((rows,), -2, dtype=torch.int32, device=x.device)
+    keys = torch.zeros(rows, dtype=torch.int32, device=x.device)
+    first = torch.empty(nseg + 1, dtype=torch.long, device=x.device)
+    nbytes = lib.b200c_morton_order_workspace_bytes(n, dim, nseg)
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+    _native.check(lib.b200c_morton_order(_p(x), _p(ptr), nseg, n, dim, max_segment_rows, _p(order), _p(keys), _p(first),
+                                         _p(ws), nbytes, _stream()))
+    return order, keys, first

@@ -6,6 +6,7 @@
 
 #include "common.cuh"
 #include "launchers.h"
+#include "spatial.cuh"
 
 namespace b200c {
 
@@ -210,6 +211,44 @@ extern "C" int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_se
                                b200c_stream_t stream) {
   return b200c_knn_graph_part(x, ptr, num_segments, n, dim, k, dtype, source_to_target, 0, edge_index, n * k,
                               irregular, max_segment_rows, workspace, workspace_bytes, stream);
+}
+
+// The ordering pass of the Morton-ordered scan on its own: see b200_cluster.h
+extern "C" size_t b200c_morton_order_workspace_bytes(int64_t n, int64_t dim, int64_t num_segments) {
+  if (n < 0 || dim < 1 || dim > SP_MAX_DIM || num_segments < 1) return 0;
+  return spatial_view_bytes(n, (int)dim, num_segments, false);
+}
+
+extern "C" int64_t b200c_morton_order_rows(int64_t n, int64_t num_segments) {
+  if (n < 0 || num_segments < 1) return 0;
+  const int64_t raw = n + num_segments * (SP_CHUNK - 1);
+  return (raw + SP_CHUNK - 1) / SP_CHUNK * SP_CHUNK;
+}
+
+extern "C" int b200c_morton_order(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
+                                  int64_t max_segment_rows, int32_t *order, uint32_t *keys, int64_t *first,
+                                  void *workspace, size_t workspace_bytes, b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int st = check_common(x, x, ptr, ptr, num_segments, n, n, dim, B200C_F32);
+  if (st != B200C_OK) return st;
+  B200C_CHECK_ARG(dim <= SP_MAX_DIM, "the Morton order covers up to 8 features");
+  B200C_CHECK_ARG(order != nullptr && keys != nullptr && first != nullptr, "null output pointer");
+  const size_t need = b200c_morton_order_workspace_bytes(n, dim, num_segments);
+  if (workspace == nullptr || workspace_bytes < need) {
+    set_error("Morton order workspace too small: %zu < %zu", workspace_bytes, need);
+    return B200C_ERR_WORKSPACE;
+  }
+  if ((st = check_device()) != B200C_OK) return st;
+  SpatialView v;
+  spatial_view_carve(&v, workspace, n, (int)dim, num_segments, false);
+  if ((st = launch_spatial_sort((const float *)x, ptr, num_segments, n, (int)dim, nullptr, false, max_segment_rows, &v,
+                                stream)) != B200C_OK)
+    return st;
+  const int64_t rows = b200c_morton_order_rows(n, num_segments);
+  B200C_CUDA(cudaMemcpyAsync(order, v.idx, (size_t)rows * 4, cudaMemcpyDeviceToDevice, stream));
+  B200C_CUDA(cudaMemcpyAsync(keys, v.key, (size_t)rows * 4, cudaMemcpyDeviceToDevice, stream));
+  B200C_CUDA(cudaMemcpyAsync(first, v.sptr, (size_t)(num_segments + 1) * 8, cudaMemcpyDeviceToDevice, stream));
+  return B200C_OK;
 }
 
 // One-pass mode keeps a row of max_num_neighbors int32 slots per query; it is used when that

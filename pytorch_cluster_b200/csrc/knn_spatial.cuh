@@ -40,23 +40,26 @@ namespace b200c {
 constexpr int KS_STAGES = 4;
 constexpr int KS_SPIN_LIMIT = 1 << 14;      // polls of a wait; each may sleep up to KS_WAIT_NS
 constexpr unsigned KS_WAIT_NS = 100000u;    // suspend-time hint of one poll (about 1.6 s in all)
-constexpr int KS_THREADS = CTA_THREADS + 32;  // eight scanning warps and the warp that issues the copies
+#ifndef KS_WARPS
+#define KS_WARPS 8
+#endif
+#ifndef KS_MINBLOCKS
+#define KS_MINBLOCKS 3
+#endif
+#define KS_PRAGMA_(x) _Pragma(#x)
+#define KS_UNROLL(n) KS_PRAGMA_(unroll n)
+constexpr int KS_TILE = 8 * KS_WARPS;            // queries per thread block
+constexpr int KS_THREADS = 32 * (KS_WARPS + 1);  // the scanning warps and the warp that issues the copies
 constexpr float KS_MARGIN = 7.62939453125e-6f;  // 2^-17
 constexpr unsigned long long KS_ERROR_COUNT = 1ull << 62;  // added to *num_valid when a wait ran out
 constexpr int KS_ERROR_IRREGULAR = 1 << 30;                // added to *graph_irregular likewise
-#ifndef KS_EAGER_STEPS
-#define KS_EAGER_STEPS 6  // scan steps during which any queued key is merged at once; later ...
-#endif
-#ifndef KS_LAZY_FILL
-#define KS_LAZY_FILL 12  // ... only a queue holding this many keys is
-#endif
 
 template <int DIM, int KP>
 struct KnnSpatial {
   using K = Key<float>;
   static constexpr int R = SP_CHUNK / 32;  // points per lane per chunk
   static_assert(R == 8, "the lane layout below takes two float4 per array");
-  static constexpr int QW = SP_TILE / WARPS_PER_CTA;
+  static constexpr int QW = 8;
   // arrays of a staged chunk: centred coordinates, w, idx, original coordinates
   static constexpr int P_W = DIM, P_IDX = DIM + 1, P_ORG = DIM + 2, PLANES = 2 * DIM + 2;
   static constexpr int STAGE_ELEMS = PLANES * SP_CHUNK;
@@ -68,10 +71,10 @@ struct KnnSpatial {
   static constexpr int QCAP = KP;
   static constexpr size_t OFF_BAR = (size_t)KS_STAGES * STAGE_BYTES;
   static constexpr size_t OFF_REC = OFF_BAR + 2 * KS_STAGES * 8;
-  static constexpr size_t OFF_QI = OFF_REC + (size_t)SP_TILE * REC * 4;
-  static constexpr size_t OFF_KEYS = OFF_QI + (size_t)SP_TILE * QI * 4;
-  static constexpr size_t OFF_CNT = OFF_KEYS + (size_t)SP_TILE * (KP + QCAP) * sizeof(K);
-  static constexpr size_t SMEM_BYTES = OFF_CNT + (size_t)SP_TILE * 2 * 4;  // fill, and fill before the chunk
+  static constexpr size_t OFF_QI = OFF_REC + (size_t)KS_TILE * REC * 4;
+  static constexpr size_t OFF_KEYS = OFF_QI + (size_t)KS_TILE * QI * 4;
+  static constexpr size_t OFF_CNT = OFF_KEYS + (size_t)KS_TILE * (KP + QCAP) * sizeof(K);
+  static constexpr size_t SMEM_BYTES = OFF_CNT + (size_t)KS_TILE * 2 * 4;  // fill, and fill before the chunk
 };
 
 __device__ __forceinline__ unsigned ks_smem(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -205,8 +208,11 @@ __device__ __noinline__ void ks_offer_chunk(const float *buf, float *rec, float 
   // Nothing known yet and far more candidates than the queue holds: the k-th smallest of the 32
   // lane minima is an upper bound of the k-th smallest key overall, so it filters first.
   if (KP == 32 && kth == ks_no_bound().v) {
-    const K cap = warp_sort32(lane_min, lane).shfl(k - 1);
-    if (cap.v < kth) kth = cap.v + 1;  // "<= cap" as a strict bound
+    // non-negative floats order like their bit patterns; an empty key's distance word sorts last
+    const uint32_t cap = __shfl_sync(FULL_MASK, warp_sort32_u32((uint32_t)(lane_min.v >> 32), lane), k - 1);
+    // every key with a distance word <= cap; fewer than k lanes with a candidate give an empty cap
+    const uint64_t below = cap == 0xffffffffu ? ~0ull : ((uint64_t)cap + 1u) << 32;
+    if (below < kth) kth = below;
   }
 #pragma unroll
   for (int r = 0; r < 8; ++r) {
@@ -245,10 +251,16 @@ struct KnnSpatialArgs {
   int64_t graph_row_stride, graph_index_base;
   int graph_s2t;
   int *graph_irregular;
+  // queue policy: during the first eager_steps scan steps any queued key is merged at once (the bound
+  // is still falling fast); later only a queue holding lazy_fill keys is
+  int eager_steps, lazy_fill;
 };
 
-template <int DIM, int KP>
-__global__ void __launch_bounds__(KS_THREADS, KP == 32 ? 3 : 2)
+// ROLLED: the loop over a warp's eight queries stays a loop.  Short segments spend much of their time
+// in the selection code, and the instruction caches then hold it better next to a small scan loop;
+// long segments live in the scan loop and want it unrolled.
+template <int DIM, int KP, bool ROLLED>
+__global__ void __launch_bounds__(KS_THREADS, KP == 32 ? KS_MINBLOCKS : 2)
 knn_spatial_kernel(const KnnSpatialArgs a) {
   using Cfg = KnnSpatial<DIM, KP>;
   using K = Key<float>;
@@ -265,7 +277,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int segs = a.num_segments;
-  const int64_t pos0 = (int64_t)blockIdx.x * SP_TILE;  // first padded query position of this tile
+  const int64_t pos0 = (int64_t)blockIdx.x * KS_TILE;  // first padded query position of this tile
   if (pos0 >= a.yv.sptr[segs]) return;
   int b;
   {
@@ -284,7 +296,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
   const float wmax = __uint_as_float(a.xv.stat[2 * b]);
   const bool screen = wmax < 1e30f;  // false also for NaN
 
-  const bool producer = warp == WARPS_PER_CTA;  // the ninth warp only moves chunks
+  const bool producer = warp == KS_WARPS;  // the ninth warp only moves chunks
   const int cwarp = producer ? 0 : warp;
   float *my_recs = recs + cwarp * QW * REC;
   float *my_qi = qinfos + cwarp * QW * QI;
@@ -295,7 +307,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
   // ---- queries of this warp: padded positions pos0 + warp + 8 qi; lane qi prepares query qi ----
   int64_t my_row = -1;  // lane qi < QW: original row of query qi, -1 for padding
   if (lane < QW && !producer) {
-    my_row = a.yv.idx[pos0 + warp + WARPS_PER_CTA * lane];
+    my_row = a.yv.idx[pos0 + warp + KS_WARPS * lane];
     float *rec = my_recs + lane * REC, *qi = my_qi + lane * QI;
     const float *box = a.xv.box + (int64_t)b * 2 * DIM;
     if (my_row >= 0) {
@@ -339,7 +351,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
       seed = (int)((pos0 - xs_lo) / SP_CHUNK);  // the queries are these points
     } else {
       // the sorted points are bisected for the key of the tile's middle query
-      uint32_t key = a.yv.key[pos0 + SP_TILE / 2];
+      uint32_t key = a.yv.key[pos0 + KS_TILE / 2];
       if (key == 0xffffffffu) key = a.yv.key[pos0];
       const uint32_t *xk = a.xv.key + xs_lo;
       int lo = 0, hi = nch * SP_CHUNK;
@@ -359,7 +371,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
   if (tid == 0) {
     for (int s = 0; s < KS_STAGES; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ks_smem(full + s)) : "memory");
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ks_smem(empty + s)), "r"(WARPS_PER_CTA)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ks_smem(empty + s)), "r"(KS_WARPS)
                    : "memory");
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -373,14 +385,8 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(ks_smem(full + slot)),
                  "r"(Cfg::STAGE_BYTES)
                  : "memory");
-#pragma unroll
-    for (int d = 0; d < DIM; ++d) {
-      ks_bulk_load(dst + d * SP_CHUNK, a.xv.ctr + (int64_t)d * a.xv.cap + pos, SP_CHUNK * 4, full + slot);
-      ks_bulk_load(dst + (Cfg::P_ORG + d) * SP_CHUNK, a.xv.org + (int64_t)d * a.xv.cap + pos, SP_CHUNK * 4,
-                   full + slot);
-    }
-    ks_bulk_load(dst + Cfg::P_W * SP_CHUNK, a.xv.w + pos, SP_CHUNK * 4, full + slot);
-    ks_bulk_load(dst + Cfg::P_IDX * SP_CHUNK, a.xv.idx + pos, SP_CHUNK * 4, full + slot);
+    // the chunk's arrays lie back to back in the sorted copy, in the order of the stage: one copy
+    ks_bulk_load(dst, a.xv.blob + (pos / SP_CHUNK) * Cfg::STAGE_ELEMS, Cfg::STAGE_BYTES, full + slot);
   };
 
   bool failed = false;
@@ -433,8 +439,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
         pw[2 * h] = make_float2(v.x, v.y);
         pw[2 * h + 1] = make_float2(v.z, v.w);
       }
-#pragma unroll
-      for (int qi = 0; qi < QW; ++qi) {
+      auto screen_query = [&](int qi) {
         const float *rec = my_recs + qi * REC;
         float4 rv[REC / 4];
 #pragma unroll
@@ -453,12 +458,19 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
         if (m < f[2 * DIM])
           ks_push<DIM, KP>(s[0].x, s[0].y, s[1].x, s[1].y, s[2].x, s[2].y, s[3].x, s[3].y, buf, rec, my_qi + qi * QI,
                            my_keys + qi * (KP + Cfg::QCAP) + KP, my_cnt + qi);
+      };
+      if constexpr (ROLLED) {
+#pragma unroll 1
+        for (int qi = 0; qi < QW; ++qi) screen_query(qi);
+      } else {
+#pragma unroll
+        for (int qi = 0; qi < QW; ++qi) screen_query(qi);
       }
       __syncwarp();
       // the queues after this chunk: overflowed ones are rolled back and the chunk offered again by
       // the whole warp; filled ones are merged, which tightens the bound
       const int fill = lane < QW ? my_cnt[lane] : 0;
-      const int want = step < KS_EAGER_STEPS ? 1 : KS_LAZY_FILL;
+      const int want = step < a.eager_steps ? 1 : a.lazy_fill;
       unsigned todo = __ballot_sync(FULL_MASK, fill >= want);
       const unsigned over = __ballot_sync(FULL_MASK, fill > Cfg::QCAP);
       while (todo) {

@@ -1,13 +1,15 @@
 // Instantiations and host side of the Morton-ordered kNN scan (knn_spatial.cuh).
+#include <cstdlib>
+
 #include "knn_spatial.cuh"
 #include "launchers.h"
 
 namespace b200c {
 
-template <int DIM, int KP>
+template <int DIM, int KP, bool ROLLED>
 static int launch_knn_spatial_one(const KnnSpatialArgs &a, int64_t tiles, cudaStream_t stream) {
   using Cfg = KnnSpatial<DIM, KP>;
-  auto kern = knn_spatial_kernel<DIM, KP>;
+  auto kern = knn_spatial_kernel<DIM, KP, ROLLED>;
   static unsigned long long configured = 0ull;  // devices on which the shared-memory opt-in is done
   B200C_CUDA(opt_in_shared_memory(kern, Cfg::SMEM_BYTES, configured));
   kern<<<(unsigned)tiles, KS_THREADS, Cfg::SMEM_BYTES, stream>>>(a);
@@ -16,9 +18,10 @@ static int launch_knn_spatial_one(const KnnSpatialArgs &a, int64_t tiles, cudaSt
 }
 
 template <int DIM>
-static int launch_knn_spatial_dim(const KnnSpatialArgs &a, int64_t tiles, cudaStream_t stream) {
-  return a.k <= 32 ? launch_knn_spatial_one<DIM, 32>(a, tiles, stream)
-                   : launch_knn_spatial_one<DIM, 64>(a, tiles, stream);
+static int launch_knn_spatial_dim(const KnnSpatialArgs &a, int64_t tiles, bool short_segments, cudaStream_t stream) {
+  if (a.k > 32) return launch_knn_spatial_one<DIM, 64, true>(a, tiles, stream);
+  return short_segments ? launch_knn_spatial_one<DIM, 32, true>(a, tiles, stream)
+                        : launch_knn_spatial_one<DIM, 32, false>(a, tiles, stream);
 }
 
 bool knn_spatial_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_segments) {
@@ -66,16 +69,29 @@ int launch_knn_spatial_f32(const KnnArgs &a, void *workspace, int64_t max_segmen
   s.graph_index_base = a.graph_index_base;
   s.graph_s2t = a.graph_s2t;
   s.graph_irregular = a.graph_irregular;
-  const int64_t tiles = padded_queries / SP_TILE;  // an upper bound: blocks past the last segment leave at once
+  s.eager_steps = 1;
+  s.lazy_fill = a.k <= 32 ? 16 : 32;
+  if (const char *e = getenv("B200C_KS_EAGER")) s.eager_steps = atoi(e);
+  if (const char *e = getenv("B200C_KS_LAZY")) s.lazy_fill = atoi(e);
+  // segments of up to 64 chunks on average count as short (the kernel variant with the rolled query loop)
+  bool short_segments = a.n / a.num_segments <= 64 * SP_CHUNK;
+  if (const char *e = getenv("B200C_KS_ROLLED")) short_segments = atoi(e) != 0;
+  const int64_t tiles = padded_queries / KS_TILE;  // an upper bound: blocks past the last segment leave at once
   switch (a.dim) {
-    case 1: return launch_knn_spatial_dim<1>(s, tiles, a.stream);
-    case 2: return launch_knn_spatial_dim<2>(s, tiles, a.stream);
-    case 3: return launch_knn_spatial_dim<3>(s, tiles, a.stream);
-    case 4: return launch_knn_spatial_dim<4>(s, tiles, a.stream);
-    case 5: return launch_knn_spatial_dim<5>(s, tiles, a.stream);
-    case 6: return launch_knn_spatial_dim<6>(s, tiles, a.stream);
-    case 7: return launch_knn_spatial_dim<7>(s, tiles, a.stream);
-    case 8: return launch_knn_spatial_dim<8>(s, tiles, a.stream);
+#ifdef KS_ONLY_DIM3  // experiments: one instantiation, short compile
+    case 3: return launch_knn_spatial_dim<3>(s, tiles, short_segments, a.stream);
+    default: break;
+  }
+  switch (0) {
+#endif
+    case 1: return launch_knn_spatial_dim<1>(s, tiles, short_segments, a.stream);
+    case 2: return launch_knn_spatial_dim<2>(s, tiles, short_segments, a.stream);
+    case 3: return launch_knn_spatial_dim<3>(s, tiles, short_segments, a.stream);
+    case 4: return launch_knn_spatial_dim<4>(s, tiles, short_segments, a.stream);
+    case 5: return launch_knn_spatial_dim<5>(s, tiles, short_segments, a.stream);
+    case 6: return launch_knn_spatial_dim<6>(s, tiles, short_segments, a.stream);
+    case 7: return launch_knn_spatial_dim<7>(s, tiles, short_segments, a.stream);
+    case 8: return launch_knn_spatial_dim<8>(s, tiles, short_segments, a.stream);
   }
   set_error("Morton-ordered kNN called with dim=%d", a.dim);
   return B200C_ERR_INVALID;

@@ -38,11 +38,7 @@ size_t spatial_view_carve(SpatialView *v, void *workspace, int64_t rows, int dim
   t.stat = (uint32_t *)take((size_t)segs * 2 * 4);
   t.pairs_cap = pairs_small_cap(rows) + 2 * rows + SP_SORT_BLOCK;
   t.pairs = (uint64_t *)take((size_t)t.pairs_cap * 8);
-  if (points) {
-    t.ctr = (float *)take((size_t)cap * dim * 4);
-    t.w = (float *)take((size_t)cap * 4);
-    t.org = (float *)take((size_t)cap * dim * 4);
-  }
+  if (points) t.blob = (float *)take((size_t)cap * (2 * dim + 2) * 4);
   if (v) *v = t;
   return off;
 }
@@ -221,12 +217,101 @@ __device__ __forceinline__ void smem_bitonic(uint64_t *a, int count, int64_t bas
   __syncthreads();
 }
 
+// ---- the same network, sixteen keys per thread in registers ------------------------------------------------
+// For blocks of 1024 keys and more.  A pass loads, per thread, groups of 2^NB keys whose indices
+// differ in NB consecutive bits, runs the NB exchange steps of those strides in registers and stores
+// the keys back: a merge of size 2^s costs ceil(s / 4) passes over shared memory instead of s, and an
+// exchange a compare and two selects per word instead of two loads and two stores.  Keys live at
+// padded positions i + i / 16 so that a thread's run of 16 consecutive keys (the passes over the
+// lowest four bits) does not meet the other lanes' runs in the same banks.
+__device__ __forceinline__ int sp_pad(int i) { return i + (i >> 4); }
+constexpr int SP_SORT_SMEM_KEYS = SP_SORT_BLOCK + SP_SORT_BLOCK / 16;
+
+__device__ __forceinline__ void sp_exchange(uint64_t &x, uint64_t &y, bool asc) {
+  const bool swap = (y < x) == asc;
+  const uint64_t lo = swap ? y : x, hi = swap ? x : y;
+  x = lo;
+  y = hi;
+}
+
+template <int NB>
+__device__ __forceinline__ void bitonic_pass(uint64_t *a, int count, int lowbit, int64_t base, int size_log, int tid,
+                                             int nthreads) {
+  constexpr int G = 1 << NB;
+  const int groups = count >> NB;
+  for (int g = tid; g < groups; g += nthreads) {
+    const int low = g & ((1 << lowbit) - 1);
+    const int i0 = ((g >> lowbit) << (lowbit + NB)) | low;
+    const bool asc = (((base + i0) >> size_log) & 1) == 0;
+    uint64_t v[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) v[j] = a[sp_pad(i0 | (j << lowbit))];
+#pragma unroll
+    for (int b = NB - 1; b >= 0; --b)
+#pragma unroll
+      for (int j = 0; j < G; ++j)
+        if (!(j & (1 << b))) sp_exchange(v[j], v[j | (1 << b)], asc);
+#pragma unroll
+    for (int j = 0; j < G; ++j) a[sp_pad(i0 | (j << lowbit))] = v[j];
+  }
+}
+
+// Merges of sizes 2, 4, 8, 16 of every run of 16 consecutive keys in one pass.
+__device__ __forceinline__ void bitonic_first16(uint64_t *a, int count, int64_t base, int tid, int nthreads) {
+  for (int g = tid; g < (count >> 4); g += nthreads) {
+    const int i0 = g << 4;
+    const bool asc16 = (((base + i0) >> 4) & 1) == 0;
+    uint64_t v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = a[sp_pad(i0 | j)];
+#pragma unroll
+    for (int s = 1; s <= 4; ++s)
+#pragma unroll
+      for (int b = s - 1; b >= 0; --b)
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (!(j & (1 << b))) sp_exchange(v[j], v[j | (1 << b)], s < 4 ? ((j >> s) & 1) == 0 : asc16);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) a[sp_pad(i0 | j)] = v[j];
+  }
+}
+
+// a: 2^p keys at padded positions (4 <= p), base as in smem_bitonic.  Runs the merges of sizes
+// 2^first_log .. 2^last_log (first_log == 1: from scratch); of a merge larger than the block only the
+// strides inside it.
+__device__ __forceinline__ void smem_bitonic_blocked(uint64_t *a, int p, int64_t base, int first_log, int last_log,
+                                                     int tid, int nthreads) {
+  const int count = 1 << p;
+  int s = first_log;
+  if (s == 1) {
+    __syncthreads();
+    bitonic_first16(a, count, base, tid, nthreads);
+    s = 5;
+  }
+  for (; s <= last_log; ++s) {
+    int top = (s < p ? s : p) - 1;  // highest stride bit inside the block
+    const int rem = (top + 1) & 3;
+    __syncthreads();
+    if (rem == 1) bitonic_pass<1>(a, count, top, base, s, tid, nthreads);
+    if (rem == 2) bitonic_pass<2>(a, count, top - 1, base, s, tid, nthreads);
+    if (rem == 3) bitonic_pass<3>(a, count, top - 2, base, s, tid, nthreads);
+    top -= rem;
+    for (; top >= 3; top -= 4) {
+      __syncthreads();
+      bitonic_pass<4>(a, count, top - 3, base, s, tid, nthreads);
+    }
+  }
+  __syncthreads();
+}
+
 // ---- sorted arrays of one position -----------------------------------------------------------------------
 template <int DIM>
 __device__ __forceinline__ float emit_position(const SpatialView &v, const float *__restrict__ pts, int64_t x_lo,
                                                int64_t pos, uint64_t pair, bool valid, bool points,
                                                const float *centre) {
   float wv = 0.f;
+  // the position's slot in its chunk's block of 2 DIM + 2 arrays
+  float *chunk = points ? v.blob + (pos / SP_CHUNK) * ((2 * DIM + 2) * SP_CHUNK) + (pos % SP_CHUNK) : nullptr;
   if (valid) {
     const int64_t row = x_lo + (int64_t)(uint32_t)pair;
     v.idx[pos] = (int32_t)row;
@@ -237,11 +322,12 @@ __device__ __forceinline__ float emit_position(const SpatialView &v, const float
       for (int d = 0; d < DIM; ++d) {
         const float p = pts[row * DIM + d];
         const float c = p - centre[d];
-        v.org[(int64_t)d * v.cap + pos] = p;
-        v.ctr[(int64_t)d * v.cap + pos] = c;
+        chunk[(DIM + 2 + d) * SP_CHUNK] = p;
+        chunk[d * SP_CHUNK] = c;
         acc = __fmaf_rn(c, c, acc);
       }
-      v.w[pos] = acc;
+      chunk[DIM * SP_CHUNK] = acc;
+      chunk[(DIM + 1) * SP_CHUNK] = __int_as_float((int32_t)row);
       wv = acc;
     }
   } else {
@@ -251,10 +337,11 @@ __device__ __forceinline__ float emit_position(const SpatialView &v, const float
     if (points) {
 #pragma unroll
       for (int d = 0; d < DIM; ++d) {
-        v.org[(int64_t)d * v.cap + pos] = inf;
-        v.ctr[(int64_t)d * v.cap + pos] = inf;
+        chunk[(DIM + 2 + d) * SP_CHUNK] = inf;
+        chunk[d * SP_CHUNK] = inf;
       }
-      v.w[pos] = inf;
+      chunk[DIM * SP_CHUNK] = inf;
+      chunk[(DIM + 1) * SP_CHUNK] = __int_as_float(-1);
     }
   }
   return wv;
@@ -335,6 +422,7 @@ sp_small_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, 
   float lo[DIM], scale[DIM], centre[DIM];
   box_scale<DIM>(box_s, lo, scale, centre);
 
+  const bool blocked = p2 >= 1024;  // sixteen keys per thread, padded positions
   for (int i = tid; i < p2; i += SP_THREADS) {
     uint64_t pair = ~0ull;
     if (i < nb) {
@@ -343,17 +431,25 @@ sp_small_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, 
       for (int d = 0; d < DIM; ++d) p[d] = pts[(x_lo + i) * DIM + d];
       pair = ((uint64_t)morton_key<DIM>(p, lo, scale) << 32) | (uint32_t)i;
     }
-    pairs[i] = pair;
+    pairs[blocked ? sp_pad(i) : i] = pair;
   }
-  if (p2 > 1) smem_bitonic(pairs, p2, 0, 2, p2, tid, SP_THREADS);
-  else __syncthreads();
+  if (blocked) {
+    int plog = 10;
+    while ((1 << plog) < p2) ++plog;
+    smem_bitonic_blocked(pairs, plog, 0, 1, plog, tid, SP_THREADS);
+  } else if (p2 > 1) {
+    smem_bitonic(pairs, p2, 0, 2, p2, tid, SP_THREADS);
+  } else {
+    __syncthreads();
+  }
 
   const int64_t s_lo = v.sptr[b];
   const int padded = (nb + SP_CHUNK - 1) / SP_CHUNK * SP_CHUNK;
   float wmax = 0.f;
   bool bad = false;
   for (int j = tid; j < padded; j += SP_THREADS) {
-    const float wv = emit_position<DIM>(v, pts, x_lo, s_lo + j, j < nb ? pairs[j] : 0ull, j < nb, points != 0, centre);
+    const float wv = emit_position<DIM>(v, pts, x_lo, s_lo + j, j < nb ? pairs[blocked ? sp_pad(j) : j] : 0ull, j < nb,
+                                        points != 0, centre);
     bad |= !(wv < 1e30f);
     wmax = fmaxf(wmax, wv);
   }
@@ -458,12 +554,17 @@ sp_sort_block_kernel(SpatialView v, int segs, int64_t size) {
   const int64_t jb = j - v.lptr[b], p2 = (v.lptr[b + 1] - v.lptr[b]) * SP_SORT_BLOCK;
   if (size > p2) return;
   uint64_t *g = v.pairs + v.pptr[b] + jb * SP_SORT_BLOCK;
-  for (int i = threadIdx.x; i < SP_SORT_BLOCK; i += SP_THREADS) a[i] = g[i];
-  if (size == 0)
-    smem_bitonic(a, SP_SORT_BLOCK, jb * SP_SORT_BLOCK, 2, SP_SORT_BLOCK, threadIdx.x, SP_THREADS);
-  else
-    smem_bitonic(a, SP_SORT_BLOCK, jb * SP_SORT_BLOCK, size, size, threadIdx.x, SP_THREADS);
-  for (int i = threadIdx.x; i < SP_SORT_BLOCK; i += SP_THREADS) g[i] = a[i];
+  constexpr int PLOG = 14;
+  static_assert((1 << PLOG) == SP_SORT_BLOCK, "block size and its logarithm");
+  for (int i = threadIdx.x; i < SP_SORT_BLOCK; i += SP_THREADS) a[sp_pad(i)] = g[i];
+  if (size == 0) {
+    smem_bitonic_blocked(a, PLOG, jb * SP_SORT_BLOCK, 1, PLOG, threadIdx.x, SP_THREADS);
+  } else {
+    int slog = PLOG;
+    while (((int64_t)1 << slog) < size) ++slog;
+    smem_bitonic_blocked(a, PLOG, jb * SP_SORT_BLOCK, slog, slog, threadIdx.x, SP_THREADS);
+  }
+  for (int i = threadIdx.x; i < SP_SORT_BLOCK; i += SP_THREADS) g[i] = a[sp_pad(i)];
 }
 
 // One exchange step (stride >= SP_SORT_BLOCK) of the merge of `size` over all large segments.
@@ -513,7 +614,7 @@ sp_emit_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, i
 template <int DIM>
 static int spatial_sort_dim(const float *pts, const int64_t *ptr, int64_t segs, int64_t rows, const float *box_from,
                             bool points, int64_t max_segment_rows, SpatialView *v, cudaStream_t stream) {
-  const size_t sort_smem = (size_t)SP_SORT_BLOCK * 8;
+  const size_t sort_smem = (size_t)SP_SORT_SMEM_KEYS * 8;
   static unsigned long long done_small = 0ull, done_block = 0ull;
   B200C_CUDA(opt_in_shared_memory(sp_small_kernel<DIM>, sort_smem, done_small));
   sp_layout_kernel<<<1, SP_THREADS, 0, stream>>>(ptr, (int)segs, rows, pairs_small_cap(rows), DIM, v->sptr, v->pptr,

@@ -9,12 +9,14 @@
 // start their scan at the chunk of points around them and have their final bound after a few
 // chunks.
 //
-// Layout of a sorted set ("view") in the caller's workspace, all arrays indexed by the padded
-// sorted position p (every segment starts at a multiple of SP_CHUNK and is padded to one):
-//   ctr   [DIM][cap]  coordinates minus the centre of the segment's bounding box (padding: +inf)
-//   w     [cap]       squared norm of the centred point                          (padding: +inf)
+// Layout of a sorted set ("view") in the caller's workspace, indexed by the padded sorted position p
+// (every segment starts at a multiple of SP_CHUNK and is padded to one):
+//   blob  [cap / SP_CHUNK][2 DIM + 2][SP_CHUNK]  per chunk of 256 positions, back to back so that one
+//         bulk copy moves a chunk: DIM arrays of coordinates minus the centre of the segment's
+//         bounding box (padding: +inf), the squared norms of those (padding: +inf), the original rows
+//         as int32 (padding: -1), DIM arrays of original coordinates (read when a candidate is
+//         re-evaluated exactly)
 //   idx   [cap]       original row of the point, int32                            (padding: -1)
-//   org   [DIM][cap]  original coordinates (read only when a candidate is re-evaluated exactly)
 //   key   [cap]       Morton key, uint32                                (padding: 0xffffffff)
 //   sptr  [B + 1]     first padded position of every segment, int64
 //   box   [B][2 DIM]  bounding box (min, max per feature) of every segment's points
@@ -31,10 +33,8 @@ constexpr int SP_SORT_BLOCK = 16384;  // keys one thread block sorts in shared m
 constexpr int SP_MAX_DIM = 8;
 
 struct SpatialView {
-  float *ctr;       // [dim][cap]
-  float *w;         // [cap]
+  float *blob;      // [cap / SP_CHUNK][2 dim + 2][SP_CHUNK], points only
   int32_t *idx;     // [cap]
-  float *org;       // [dim][cap]
   uint32_t *key;    // [cap]
   int64_t *sptr;    // [B + 1]
   float *box;       // [B][2 * dim]
