@@ -10,7 +10,7 @@
 //   * Per (query, chunk) a lane screens its 8 points with s = |p'|^2 - 2 p'.q' (p', q' relative to
 //     the centre of the segment's bounding box; |p'|^2 comes with the sorted copy) against
 //     c = bound - |q'|^2 + margin, the margin covering the rounding of both sides.  A lane whose
-//     smallest s is below c — and only that lane, no vote — re-evaluates its screened points with
+//     smallest s is at or below c — and only that lane, no vote — re-evaluates its screened points with
 //     the reference's arithmetic, fma(x_d - y_d, x_d - y_d, acc) over ascending d on the original
 //     coordinates (csrc/cuda/knn_cuda.cu:61-64), and appends those that beat the query's k-th best
 //     (distance, index) key to the query's queue in shared memory.
@@ -28,7 +28,9 @@
 // most u ((2D + 8) bound + (5D + 5) |q'|^2 + (4D + 2) max|p'|^2) for every pair whose reference distance
 // is at most `bound` (rounding of the centred copies, of |p'|^2, |q'|^2, the D-term chains and of
 // the reference distance itself); the kernel uses 2^-17 (bound + |q'|^2 + max|p'|^2), at least
-// twice that for D <= 8.  Segments whose centred norms are not finite (or above 1e30) are
+// twice that for D <= 8, plus a few steps of the subnormal grid, where rounding errors are absolute;
+// the test is s <= c, so that a candidate at exactly the bound's distance (which wins with a lower
+// index) passes even where the margin rounds to nothing.  Segments whose centred norms are not finite (or above 1e30) are
 // searched without the screen.
 #pragma once
 
@@ -51,6 +53,7 @@ constexpr unsigned KS_WAIT_NS = 100000u;    // suspend-time hint of one poll (ab
 constexpr int KS_TILE = 8 * KS_WARPS;            // queries per thread block
 constexpr int KS_THREADS = 32 * (KS_WARPS + 1);  // the scanning warps and the warp that issues the copies
 constexpr float KS_MARGIN = 7.62939453125e-6f;  // 2^-17
+constexpr float KS_MARGIN_ABS = 2e-43f;         // about 140 steps of the subnormal grid: rounding there is absolute
 constexpr unsigned long long KS_ERROR_COUNT = 1ull << 62;  // added to *num_valid when a wait ran out
 constexpr int KS_ERROR_IRREGULAR = 1 << 30;                // added to *graph_irregular likewise
 
@@ -144,7 +147,7 @@ __device__ __noinline__ void ks_push(float s0, float s1, float s2, float s3, flo
   const int32_t *idx_plane = reinterpret_cast<const int32_t *>(buf + Cfg::P_IDX * SP_CHUNK);
 #pragma unroll
   for (int r = 0; r < 8; ++r) {
-    if (s[r] < c) {
+    if (s[r] <= c) {
       const int slot = ks_slot(lane, r);
       const int32_t idx = idx_plane[slot];
       const float d = ks_exact<DIM, KP>(buf, slot, qinfo);
@@ -175,7 +178,7 @@ __device__ __forceinline__ void ks_update_bound(const Key<float> *keys, float *r
     if (!(kth.v < ks_no_bound().v)) kth = ks_no_bound();  // fewer than k known yet
     *reinterpret_cast<uint64_t *>(qinfo + Cfg::QI_KTH) = kth.v;
     const float bound = kth.dist(), nq2 = qinfo[DIM];
-    rec[2 * DIM] = (bound - nq2) + KS_MARGIN * (bound + nq2 + wmax);
+    rec[2 * DIM] = ((bound - nq2) + KS_MARGIN * (bound + nq2 + wmax)) + KS_MARGIN_ABS;
   }
   __syncwarp();
 }
@@ -323,7 +326,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
       }
       qi[DIM] = nq2;
       *reinterpret_cast<uint64_t *>(qi + Cfg::QI_KTH) = ks_no_bound().v;
-      rec[2 * DIM] = (1e10f - nq2) + KS_MARGIN * (1e10f + nq2 + wmax);
+      rec[2 * DIM] = ((1e10f - nq2) + KS_MARGIN * (1e10f + nq2 + wmax)) + KS_MARGIN_ABS;
     } else {
 #pragma unroll
       for (int d = 0; d < DIM; ++d) {
@@ -455,7 +458,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
         // fminf drops a NaN operand; eight NaN give NaN, which is below nothing
         const float m0 = fminf(fminf(s[0].x, s[0].y), s[1].x), m1 = fminf(fminf(s[1].y, s[2].x), s[2].y);
         const float m = fminf(fminf(m0, m1), fminf(s[3].x, s[3].y));
-        if (m < f[2 * DIM])
+        if (m <= f[2 * DIM])
           ks_push<DIM, KP>(s[0].x, s[0].y, s[1].x, s[1].y, s[2].x, s[2].y, s[3].x, s[3].y, buf, rec, my_qi + qi * QI,
                            my_keys + qi * (KP + Cfg::QCAP) + KP, my_cnt + qi);
       };

@@ -294,7 +294,7 @@ def test_argument_errors():
     cnt = torch.empty(10, dtype=torch.int32, device=DEV)
     nv = torch.empty(1, dtype=torch.long, device=DEV)
     st = lib.b200c_knn(x.data_ptr(), x.data_ptr(), None, None, 1, 10, 10, 3, 101, 0, 0, out.data_ptr(),
-                       cnt.data_ptr(), nv.data_ptr(), None, 0, None)
+                       cnt.data_ptr(), nv.data_ptr(), 0, None, 0, None)
     assert st == 1 and b"smaller than or equal to 100" in lib.b200c_last_error()
 
 
