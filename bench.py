@@ -1,6 +1,6 @@
 """Benchmark of the neighbour-graph path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extra]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference|reference-cuda] [--no-extra]
     python bench.py --only NAME [--steps K]     (one workload through the C ABI, for profilers)
 
 Headline workload (``knn_graph_batched``): 32 clouds x 4096 points, 3-D fp32 ~ N(0,1), sorted
@@ -10,14 +10,19 @@ the whole batch.  Printed: ONE JSON line with
   e2e         the same result from pinned host buffers to a pinned host buffer
               (``knn_graph_host``): upload of x, search and download of edge_index inside the
               timed region, overlapped across 8 groups of clouds, one stream each
-  roofline    of the dominant kernel (knn_lowd_kernel, FP32-pipe bound): 8 flop per
-              (query, point) pair / its CUDA-event time when launched alone through the C ABI
+  roofline    of the dominant kernel (knn_spatial_kernel, FP32-pipe bound): 8 flop per
+              (query, point) pair / its own duration, CUDA events recorded around that kernel on its
+              stream (b200c_profile_knn_scan); beside the nominal FP32 peak the rate a pure-FFMA
+              kernel reaches in the same run
   cpu_baseline  the reference's own CPU path (oracle/_ref: kd-tree search, single thread)
   extra       the other configurations (single cloud, large bipartite kNN, 64-D feature kNN with and
-              without cosine, radius_graph with and without truncation), kernel/API times and rates
+              without cosine, radius_graph with and without truncation, its passes in GB/s)
+  strong      (N > 1) fixed total work sharded over the ranks, checked against the single-GPU result
 
-``--impl reference`` times the reference's CPU implementation on the same workload instead.
-With N > 1 (torchrun) every rank runs the workload on its own clouds (weak scaling, no
+``--impl reference`` times the reference's CPU implementation on the same workload instead;
+``--impl reference-cuda`` the reference's own CUDA kernels (oracle/_ref, compiled for sm_100a)
+beside this library's on the same device tensors.
+With N > 1 (torchrun) every rank runs the headline workload on its own clouds (weak scaling, no
 data-path collective); the time is the max over ranks.
 """
 from __future__ import annotations
@@ -37,8 +42,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FP32_LANES_PER_SM = 128
-KNN_LOWD_CFG2_DRAM_BYTES = 2511360  # ncu: dram__bytes_read.sum 1,638,656 + dram__bytes_write.sum 872,704 (profiles/)
+# ncu, one launch of knn_spatial_kernel on the headline workload (profiles/): dram__bytes_read.sum +
+# dram__bytes_write.sum; the sorted copy is read once, most of the output still sits in L2 at the end
+KNN_SCAN_DRAM_BYTES = 5924096 + 267776
 L2_FLUSH_BYTES = 256 << 20
+WORKLOAD = "knn_graph_batched: 32 clouds x 4096 points, 3-D fp32 N(0,1), k=20, loop=False"
+# identical in both arms; the L2 remark concerns the GPU arm, the reference arm works from host memory
+CONFIG = {"workload": WORKLOAD, "per_gpu": True, "l2": "GPU arm: 256 MiB buffer rewritten between timed steps"}
 
 
 # ---- workloads -----------------------------------------------------------------------------------
@@ -169,7 +179,101 @@ def fp32_peak_tf(props, peaks):
     return props.multi_processor_count * FP32_LANES_PER_SM * 2 * sm_max * 1e6 / 1e12
 
 
-def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank):
+def scan_kernel_ms(cabi, fn, reps=5):
+    """Average duration of the kNN scan kernel alone inside `fn` (CUDA events around that kernel)."""
+    from pytorch_cluster_b200 import _native
+
+    lib = _native.cabi()
+    lib.b200c_profile_knn_scan(1)
+    total = 0.0
+    try:
+        fn()
+        for _ in range(reps):
+            fn()
+            total += lib.b200c_profile_knn_scan_ms()
+    finally:
+        lib.b200c_profile_knn_scan(0)
+    return total / reps
+
+
+def measured_fp32_tf(dev):
+    """TFLOP/s of a kernel of independent FFMA chains over the whole device (about a millisecond)."""
+    import ctypes
+
+    from pytorch_cluster_b200 import _native
+
+    lib = _native.cabi()
+    scratch = torch.zeros(1, device=dev)
+    flops = ctypes.c_double(0.0)
+    stream = torch.cuda.current_stream().cuda_stream
+    iters = 40000
+    _native.check(lib.b200c_probe_fp32(iters, scratch.data_ptr(), ctypes.byref(flops), stream))
+    best = 0.0
+    for _ in range(3):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        _native.check(lib.b200c_probe_fp32(iters, scratch.data_ptr(), ctypes.byref(flops), stream))
+        b.record()
+        b.synchronize()
+        best = max(best, flops.value / (a.elapsed_time(b) * 1e-3) / 1e12)
+    return best
+
+
+def radius_passes(cabi, x, ptr, r, max_nn, ms_of, peaks):
+    """The passes of one radius_graph call through the C ABI: the scan that counts (and parks the hits
+    or their bits), and the HBM-bound pass that writes the edges, with its bytes per second against the
+    measured copy bandwidth.  Algorithmic bytes of the write pass: 16 per edge written, 4 per count and 8
+    per offset read, plus what it reads per edge (4-byte parked hits, or the hit bits)."""
+    from pytorch_cluster_b200 import _native
+
+    lib = _native.cabi()
+    n, dim = x.shape
+    nseg = ptr.numel() - 1
+    dt = _native.B200C_F32
+    stream = torch.cuda.current_stream().cuda_stream
+    counts = torch.empty(n, dtype=torch.int32, device=x.device)
+    hbm = (peaks.get("hbm_gbs") or 6650.0)
+    if max_nn <= 256:
+        nbytes = lib.b200c_radius_workspace_bytes(n, n, dim, max_nn, dt)
+        ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+        count = lambda: _native.check(lib.b200c_radius_count(x.data_ptr(), x.data_ptr(), ptr.data_ptr(), ptr.data_ptr(),
+                                                             nseg, n, n, dim, float(r), max_nn, 1, dt, counts.data_ptr(),
+                                                             ws.data_ptr(), nbytes, stream))
+        count()
+        offsets = cabi.exclusive_scan(counts)
+        total = int(offsets[-1].item())
+        out = torch.empty(2, total, dtype=torch.long, device=x.device)
+        fill = lambda: _native.check(lib.b200c_radius_fill(x.data_ptr(), x.data_ptr(), ptr.data_ptr(), ptr.data_ptr(), nseg,
+                                                           n, n, dim, float(r), max_nn, 1, dt, counts.data_ptr(),
+                                                           offsets.data_ptr(), total, out.data_ptr(), ws.data_ptr(), nbytes,
+                                                           stream))
+        read_per_edge, kernel = 4, "radius_direct_compact_kernel"
+        extra_read = 0
+    else:
+        hp = ptr.cpu()
+        nbytes = lib.b200c_radius_mask_workspace_bytes(hp.data_ptr(), hp.data_ptr(), nseg, n, n, dim, dt)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+        count = lambda: _native.check(lib.b200c_radius_count_masks(x.data_ptr(), x.data_ptr(), ptr.data_ptr(),
+                                                                   ptr.data_ptr(), hp.data_ptr(), hp.data_ptr(), nseg, n, n,
+                                                                   dim, float(r), max_nn, 1, dt, counts.data_ptr(),
+                                                                   ws.data_ptr(), nbytes, stream))
+        count()
+        offsets = cabi.exclusive_scan(counts)
+        total = int(offsets[-1].item())
+        out = torch.empty(2, total, dtype=torch.long, device=x.device)
+        fill = lambda: _native.check(lib.b200c_radius_fill_masks(ptr.data_ptr(), ptr.data_ptr(), nseg, n, n, dim, dt,
+                                                                 counts.data_ptr(), offsets.data_ptr(), total, out.data_ptr(),
+                                                                 ws.data_ptr(), stream))
+        read_per_edge, kernel = 0, "radius_mask_fill_kernel"
+        extra_read = nbytes
+    t_count, t_fill = ms_of(count), ms_of(fill)
+    fill_bytes = 16 * total + 12 * n + read_per_edge * total + extra_read
+    return {"count_scan_ms": t_count, "write_pass_ms": t_fill, "write_pass_kernel": kernel,
+            "write_pass_bytes": fill_bytes, "write_pass_gbs": fill_bytes / (t_fill * 1e-3) / 1e9,
+            "write_pass_frac_of_measured_hbm": fill_bytes / (t_fill * 1e-3) / 1e9 / hbm}
+
+
+def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank, peaks):
     """The other configurations, a few repetitions each: kernel time through the C ABI and call time
     through the public API, with the rates they imply."""
     reps, warm = 5, 2
@@ -189,11 +293,13 @@ def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank):
     x, y = w["x"].to(dev), w["y"].to(dev)
     bx, by = w["batch_x"].to(dev), w["batch_y"].to(dev)
     px, py = torch.ops.torch_cluster.segment_ptr(bx, 8), torch.ops.torch_cluster.segment_ptr(by, 8)
-    tk = ms_of(lambda: cabi.knn_padded_nosync(x, y, 32, px, py))
+    tk = ms_of(lambda: cabi.knn_padded_nosync(x, y, 32, px, py, max_segment_rows=131072))
+    tscan = scan_kernel_ms(cabi, lambda: cabi.knn_padded_nosync(x, y, 32, px, py, max_segment_rows=131072))
     ta = ms_of(lambda: pc.knn(x, y, 32, bx, by))
     out["knn_bipartite_8x131072x8192_k32"] = {
-        "kernel_ms": tk, "api_ms": ta, "queries_per_s": w["queries"] / (ta * 1e-3),
-        "fp32_frac": 8.0 * w["pairs"] / (tk * 1e-3) / 1e12 / peak_tf}
+        "kernels_ms": tk, "scan_kernel_ms": tscan, "api_ms": ta, "queries_per_s": w["queries"] / (ta * 1e-3),
+        "fp32_frac": 8.0 * w["pairs"] / (tk * 1e-3) / 1e12 / peak_tf,
+        "fp32_frac_scan_kernel": 8.0 * w["pairs"] / (tscan * 1e-3) / 1e12 / peak_tf}
     del x, y
 
     # feature-space kNN: 16 clouds x 2048 points x 64 features, k = 20
@@ -210,11 +316,13 @@ def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank):
     # radius_graph on a clustered density: 64 clouds x 8192 points, r = 0.05
     w = make_radius_mixture()
     xr, br = w["x"].to(dev), w["batch"].to(dev)
+    pr = torch.ops.torch_cluster.segment_ptr(br, 64)
     for max_nn in (64, 8192):
         e = pc.radius_graph(xr, w["r"], br, max_num_neighbors=max_nn)
         ta = ms_of(lambda: pc.radius_graph(xr, w["r"], br, max_num_neighbors=max_nn))
         rec = {"api_ms": ta, "edges": int(e.shape[1]), "edges_per_s": e.shape[1] / (ta * 1e-3),
                "fp32_frac": 8.0 * w["pairs"] / (ta * 1e-3) / 1e12 / peak_tf}
+        rec.update(radius_passes(cabi, xr, pr, w["r"], max_nn, ms_of, peaks))
         out[f"radius_graph_64x8192x3_r0.05_max{max_nn}"] = rec
 
     # the operators either side of the path: farthest point sampling (25 % of every cloud, first
@@ -323,24 +431,97 @@ def run_reference(args, rank, world):
     if not rc.available():
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref (reference CPU path) is not built"}))
         return
-    for _ in range(max(1, min(args.warmup, 1))):
-        reference_knn_graph_cpu(w["x"], w["k"], w["batch"], w["clouds"])
+    # The reference's kd-tree path takes about 13 ms per cloud on one core.  A step is a bounded sample of
+    # the workload — the first c of its 32 clouds, the same c every step — with c chosen so that the K
+    # timed steps end within about a minute; with K <= 140 every step is the whole workload.
+    clouds = max(1, min(w["clouds"], int(60.0 / (max(1, args.steps) * 0.0135))))
+    rows = clouds * w["points"]
+    xs, bs = w["x"][:rows].contiguous(), w["batch"][:rows].contiguous()
+    for _ in range(max(1, min(args.warmup, 2))):
+        reference_knn_graph_cpu(xs, w["k"], bs, clouds)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        reference_knn_graph_cpu(w["x"], w["k"], w["batch"], w["clouds"])
+        reference_knn_graph_cpu(xs, w["k"], bs, clouds)
     dt = time.perf_counter() - t0
-    value = w["queries"] * args.steps / dt
+    steps = args.steps
+    value = rows * steps / dt
     line = {
         "impl": "reference", "metric": "knn_graph queries/s", "value": value, "unit": "queries/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "knn_graph_batched: 32 clouds x 4096 points, 3-D fp32 N(0,1), k=20, loop=False"},
+        "config": CONFIG,
         "cpu_baseline": {"value": value, "unit": "queries/s", "cores": 1, "kind": "reference",
-                         "sample": "the full workload each step; the reference's CPU path ignores num_workers "
-                                   "(csrc/cpu/knn_cpu.cpp:10), so it runs on one core"},
+                         "sample": f"{clouds} of the 32 clouds per step ({rows} queries); the reference's CPU path "
+                                   "ignores num_workers (csrc/cpu/knn_cpu.cpp:10), so it runs on one core"},
         "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
+
+
+# ---- the reference's CUDA kernels beside this library (same GPU, same tensors) ---------------------------------
+
+def run_reference_cuda(args):
+    """Operator-level time (CUDA events, whole operator call incl. its compaction) of the reference's CUDA
+    path, compiled unmodified for sm_100a (oracle/_ref), and of this library on the same device tensors at
+    the sizes of the benchmark's workloads; results are checked to be identical first.  One JSON line."""
+    from oracle import reference_cuda as refc
+
+    if not refc.available():
+        print(json.dumps({"impl": "reference-cuda", "unavailable": "oracle/_ref/ref_cluster_cuda.so is not built"}))
+        return
+    import pytorch_cluster_b200  # noqa: F401
+
+    dev = torch.device("cuda", 0)
+    ops = torch.ops.torch_cluster
+    rep = {}
+
+    def ms(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    def both(name, ref_fn, our_fn, ref_reps=3):
+        assert torch.equal(our_fn(), ref_fn()), name
+        rep[name] = {"reference_cuda_ms": round(ms(ref_fn, ref_reps), 4), "this_library_ms": round(ms(our_fn, 5), 4)}
+        rep[name]["ratio"] = round(rep[name]["reference_cuda_ms"] / rep[name]["this_library_ms"], 2)
+
+    def ptr(clouds, per):
+        return torch.arange(clouds + 1, device=dev) * per
+
+    w = make_knn_graph_batched()
+    x, p = w["x"].to(dev), ptr(32, 4096)
+    both("knn_32x4096x3_k21", lambda: refc.knn(x, x, p, p, 21), lambda: ops.knn_hinted(x, x, p, p, 21, False, 4096))
+    w = make_knn_bipartite()
+    xb, yb, pxb, pyb = w["x"].to(dev), w["y"].to(dev), ptr(8, 131072), ptr(8, 8192)
+    both("knn_8x131072x8192x3_k32", lambda: refc.knn(xb, yb, pxb, pyb, 32),
+         lambda: ops.knn_hinted(xb, yb, pxb, pyb, 32, False, 131072), 1)
+    del xb, yb
+    xf = torch.randn(32768, 64, generator=torch.Generator().manual_seed(4)).to(dev)
+    pf = ptr(16, 2048)
+    for cosine in (False, True):
+        both(f"knn_16x2048x64_k21_cosine{int(cosine)}", lambda: refc.knn(xf, xf, pf, pf, 21, cosine),
+             lambda: ops.knn(xf, xf, pf, pf, 21, cosine, 1))
+    xr, pr = make_radius_mixture()["x"].to(dev), ptr(64, 8192)
+    both("radius_64x8192x3_r0.05_max64", lambda: refc.radius(xr, xr, pr, pr, 0.05, 64, True),
+         lambda: ops.radius(xr, xr, pr, pr, 0.05, 64, 1, True))
+    # a cap of 8192 on all 64 clouds would make the reference allocate 2 x 34 GB of padded output: 8 clouds
+    xs, ps = xr[: 8 * 8192].contiguous(), ptr(8, 8192)
+    both("radius_8x8192x3_r0.05_max8192", lambda: refc.radius(xs, xs, ps, ps, 0.05, 8192, True),
+         lambda: ops.radius(xs, xs, ps, ps, 0.05, 8192, 1, True))
+    ys, pys = torch.cat([xr[c * 8192: c * 8192 + 2048] for c in range(64)]).contiguous(), ptr(64, 2048)
+    both("nearest_64x8192_to_2048x3", lambda: refc.nearest(xr, ys, pr, pys), lambda: ops.nearest(xr, ys, pr, pys))
+    ratio = torch.tensor(0.25, device=dev)
+    both("fps_64x8192x3_ratio0.25", lambda: refc.fps(xr, pr, ratio, False), lambda: ops.fps(xr, pr, ratio, False), 1)
+    xl = torch.rand(1 << 20, 3, generator=torch.Generator().manual_seed(6)).to(dev)
+    pl, rl = torch.tensor([0, 1 << 20], device=dev), torch.tensor(1024 / (1 << 20) - 1e-9, device=dev)
+    both("fps_1x1048576x3_1024_samples", lambda: refc.fps(xl, pl, rl, False), lambda: ops.fps(xl, pl, rl, False), 1)
+    print(json.dumps({"impl": "reference-cuda", "unit": "ms per operator call", "workloads": rep}))
 
 
 # ---- single workloads for profilers --------------------------------------------------------------------------
@@ -357,12 +538,12 @@ def run_only(args):
     if name == "knn_graph_batched":            # the headline kernel: 32 x 4096 x 3, k = 20 (+1)
         w = make_knn_graph_batched()
         x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 32)
-        fn = lambda: cabi.knn_padded_nosync(x, x, 21, ptr, ptr)
+        fn = lambda: cabi.knn_padded_nosync(x, x, 21, ptr, ptr, max_segment_rows=4096)
     elif name == "knn_bipartite_small":        # 2 of the 8 clouds of the large bipartite search
         w = make_knn_bipartite(clouds=2)
         x, y = w["x"].to(dev), w["y"].to(dev)
         px, py = seg(w["batch_x"].to(dev), 2), seg(w["batch_y"].to(dev), 2)
-        fn = lambda: cabi.knn_padded_nosync(x, y, 32, px, py)
+        fn = lambda: cabi.knn_padded_nosync(x, y, 32, px, py, max_segment_rows=131072)
     elif name == "knn_features":               # 16 x 2048 x 64, k = 20 (+1): tensor-core candidates + re-rank
         g = torch.Generator().manual_seed(4)
         x = torch.randn(32768, 64, generator=g).to(dev)
@@ -379,7 +560,7 @@ def run_only(args):
     elif name == "knn_graph_one_kernel":       # the headline call's kernel in its graph-output mode
         w = make_knn_graph_batched()
         x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 32)
-        fn = lambda: cabi.knn_graph(x, 20, ptr, True)
+        fn = lambda: cabi.knn_graph_nosync(x, 20, ptr, True, True, 4096)
     elif name in ("fps_small", "nearest_small"):  # 16 of the 64 clouds; 25 % samples, then assignment
         w = make_radius_mixture(clouds=16)
         x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 16)
@@ -441,12 +622,14 @@ def run_ours(args, rank, world, local_rank):
         if world > 1:
             dist.barrier()
         ms_e2e = max_over_ranks(timed_steps(step_e2e, args.steps, args.warmup, flush), world)
-        # dominant kernel alone, through the C ABI (memset of one counter + one kernel launch)
-        ms_kernel = timed_steps(lambda: _cabi.knn_padded_nosync(x, x, k + 1, ptr, ptr), args.steps, args.warmup,
-                                flush)
-        ms_kernel = max_over_ranks(ms_kernel, world)
+        # the kernels of one call through the C ABI (ordering passes + scan), and the scan kernel alone
+        ksteps = min(args.steps, 200)
+        graph_call = lambda: _cabi.knn_graph_nosync(x, k, ptr, True, True, w["points"])
+        ms_kernels = max_over_ranks(timed_steps(graph_call, ksteps, args.warmup, flush) / ksteps, world)
+        ms_scan = max_over_ranks(scan_kernel_ms(_cabi, graph_call, reps=min(ksteps, 50)), world)
+        fp32_measured = measured_fp32_tf(dev)
         extra = {} if args.no_extra else extra_workloads(pc, _cabi, dev, flush, fp32_peak_tf(props, load_peaks()),
-                                                         world, rank)
+                                                         world, rank, peaks)
         strong = strong_scaling(pc, dev, flush, world, rank) if (world > 1 and not args.no_extra) else None
 
     if rank != 0:
@@ -455,29 +638,30 @@ def run_ours(args, rank, world, local_rank):
     sm_max = peaks.get("sm_max_mhz") or 1965.0
     fp32_peak = fp32_peak_tf(props, peaks)
     flops = 8.0 * w["pairs"]
-    achieved = flops / (ms_kernel / args.steps * 1e-3) / 1e12
+    achieved = flops / (ms_scan * 1e-3) / 1e12
     line = {
         "metric": "knn_graph queries/s", "value": total_queries * args.steps / (ms * 1e-3), "unit": "queries/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "knn_graph_batched: 32 clouds x 4096 points per GPU, 3-D fp32 N(0,1), k=20, "
-                               "loop=False", "l2": "256 MiB buffer rewritten between timed steps"},
+        "config": CONFIG,
         "e2e": {"value": total_queries * args.steps / (ms_e2e * 1e-3), "unit": "queries/s",
                 # the points and the per-group segment pointers go up (the batch vector is only read on the
                 # host), the edge rows and one flag per group come down
                 "h2d_bytes_per_step": hx.numel() * 4 + (w["clouds"] + 8) * 8,
                 "d2h_bytes_per_step": 2 * edges * 8 + 8 * 4},
-        # per knn_graph call: segment_ptr and the kNN kernel, which writes the final edge rows itself
-        "gpu_launches": 2 * args.steps,
+        # per knn_graph call: batch_info, segment_ptr, the layout and sort kernels of the ordering pass and
+        # the scan kernel, which writes the final edge rows itself
+        "gpu_launches": 5 * args.steps,
         "clocks": clocks.summary(),
-        "roofline": {"bound": "fp32", "kernel": "knn_lowd_kernel<float,3,32>", "achieved": achieved,
+        "roofline": {"bound": "fp32", "kernel": "knn_spatial_kernel<3,32,rolled>", "achieved": achieved,
                      "peak": fp32_peak, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
                      "peak_source": f"nominal: {props.multi_processor_count} SMs x 128 lanes x 2 flop x "
-                                    f"{sm_max:.0f} MHz (MEASURED_PEAKS.json holds no fp32 figure)",
-                     "flops_per_launch": flops, "ms_per_launch": ms_kernel / args.steps,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu, profiles/): the 1.6 MB
-                     # input is read once; the 44 MB of output mostly still sits in L2 when the kernel ends
-                     "traffic": KNN_LOWD_CFG2_DRAM_BYTES},
+                                    f"{sm_max:.0f} MHz (MEASURED_PEAKS.json holds no fp32 figure); frac uses it",
+                     "peak_measured_ffma": fp32_measured, "frac_of_measured_ffma": achieved / fp32_measured,
+                     "flops_per_launch": flops, "ms_per_launch": ms_scan,
+                     "ms_all_kernels_of_the_call": ms_kernels,
+                     "frac_all_kernels_of_the_call": flops / (ms_kernels * 1e-3) / 1e12 / fp32_peak,
+                     "traffic": KNN_SCAN_DRAM_BYTES},
         "extra": extra,
     }
     if strong is not None:
@@ -500,9 +684,9 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--only", default=None, help="run one named workload through the C ABI (for profilers)")
@@ -516,6 +700,10 @@ def main():
         return
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.impl == "reference-cuda":
+        if rank == 0:
+            run_reference_cuda(args)
         return
     if world > 1:
         import torch.distributed as dist

@@ -151,6 +151,18 @@ int b200c_morton_order(const void *x, const int64_t *ptr, int64_t num_segments, 
                        int64_t *first, void *workspace, size_t workspace_bytes,
                        b200c_stream_t stream);
 
+/* Measurement aids (no counterpart in the reference).
+ * b200c_profile_knn_scan(1): later calls of the Morton-ordered kNN path record CUDA events around
+ * their scan kernel on the call's stream; b200c_profile_knn_scan_ms() waits for the last such kernel
+ * and returns its duration in milliseconds (-1 if none was recorded).  One call of the path launches
+ * the ordering passes and the scan; a roofline figure wants the scan alone.  Not thread safe.
+ * b200c_probe_fp32: a kernel of nothing but independent fused multiply-adds over the whole device
+ * (scratch: one float, device); *flops (host) receives the operations it performs, so that a caller
+ * timing it has the FP32 rate this device sustains beside the nominal one. */
+int b200c_profile_knn_scan(int enable);
+float b200c_profile_knn_scan_ms(void);
+int b200c_probe_fp32(int64_t iters, float *scratch, double *flops, b200c_stream_t stream);
+
 /* Drops the -1 slots: edge_index (int64 [2, num_edges]) receives, for each
  * query q, its counts[q] valid slots at offsets[q].. (csrc/cuda/knn_cuda.cu:133-134). */
 int b200c_knn_compact(const int64_t *edge_padded, const int32_t *counts,

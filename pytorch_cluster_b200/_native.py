@@ -63,6 +63,12 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_morton_order_rows.restype = i64
     lib.b200c_morton_order.argtypes = [p, p, i64, i64, i64, i64, p, p, p, p, sz, p]
     lib.b200c_morton_order.restype = i32
+    lib.b200c_profile_knn_scan.argtypes = [i32]
+    lib.b200c_profile_knn_scan.restype = i32
+    lib.b200c_profile_knn_scan_ms.argtypes = []
+    lib.b200c_profile_knn_scan_ms.restype = ctypes.c_float
+    lib.b200c_probe_fp32.argtypes = [i64, p, ctypes.POINTER(ctypes.c_double), p]
+    lib.b200c_probe_fp32.restype = i32
     lib.b200c_knn_compact.argtypes = [p, p, p, i64, i64, i64, p, p]
     lib.b200c_knn_graph_tail_count.argtypes = [p, p, i64, i64, i32, p, p]
     lib.b200c_knn_graph_tail_write.argtypes = [p, p, p, i64, i64, i32, i32, i64, p, p]

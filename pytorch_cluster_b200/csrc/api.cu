@@ -213,6 +213,9 @@ extern "C" int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_se
                               irregular, max_segment_rows, workspace, workspace_bytes, stream);
 }
 
+extern "C" int b200c_profile_knn_scan(int enable) { return knn_spatial_scan_timing(enable); }
+extern "C" float b200c_profile_knn_scan_ms(void) { return knn_spatial_last_scan_ms(); }
+
 // The ordering pass of the Morton-ordered scan on its own: see b200_cluster.h
 extern "C" size_t b200c_morton_order_workspace_bytes(int64_t n, int64_t dim, int64_t num_segments) {
   if (n < 0 || dim < 1 || dim > SP_MAX_DIM || num_segments < 1) return 0;

@@ -24,6 +24,28 @@ static int launch_knn_spatial_dim(const KnnSpatialArgs &a, int64_t tiles, bool s
                         : launch_knn_spatial_one<DIM, 32, false>(a, tiles, stream);
 }
 
+// ---- optional timing of the scan kernel alone (for benchmarks: roofline figures want the kernel's
+// own duration, and one call of the path launches the ordering passes as well) ----
+static bool g_scan_timing = false;
+static cudaEvent_t g_scan_begin = nullptr, g_scan_end = nullptr;
+
+int knn_spatial_scan_timing(int enable) {
+  if (enable && g_scan_begin == nullptr) {
+    B200C_CUDA(cudaEventCreate(&g_scan_begin));
+    B200C_CUDA(cudaEventCreate(&g_scan_end));
+  }
+  g_scan_timing = enable != 0;
+  return B200C_OK;
+}
+
+float knn_spatial_last_scan_ms() {
+  float ms = -1.f;
+  if (g_scan_begin == nullptr || cudaEventSynchronize(g_scan_end) != cudaSuccess ||
+      cudaEventElapsedTime(&ms, g_scan_begin, g_scan_end) != cudaSuccess)
+    return -1.f;
+  return ms;
+}
+
 bool knn_spatial_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_segments) {
   // enough points per segment for the ordering to pay (a chunk is 256 points), and within the
   // instantiated selection widths
@@ -77,24 +99,21 @@ int launch_knn_spatial_f32(const KnnArgs &a, void *workspace, int64_t max_segmen
   bool short_segments = a.n / a.num_segments <= 64 * SP_CHUNK;
   if (const char *e = getenv("B200C_KS_ROLLED")) short_segments = atoi(e) != 0;
   const int64_t tiles = padded_queries / KS_TILE;  // an upper bound: blocks past the last segment leave at once
-  switch (a.dim) {
-#ifdef KS_ONLY_DIM3  // experiments: one instantiation, short compile
-    case 3: return launch_knn_spatial_dim<3>(s, tiles, short_segments, a.stream);
-    default: break;
-  }
-  switch (0) {
-#endif
-    case 1: return launch_knn_spatial_dim<1>(s, tiles, short_segments, a.stream);
-    case 2: return launch_knn_spatial_dim<2>(s, tiles, short_segments, a.stream);
-    case 3: return launch_knn_spatial_dim<3>(s, tiles, short_segments, a.stream);
-    case 4: return launch_knn_spatial_dim<4>(s, tiles, short_segments, a.stream);
-    case 5: return launch_knn_spatial_dim<5>(s, tiles, short_segments, a.stream);
-    case 6: return launch_knn_spatial_dim<6>(s, tiles, short_segments, a.stream);
-    case 7: return launch_knn_spatial_dim<7>(s, tiles, short_segments, a.stream);
-    case 8: return launch_knn_spatial_dim<8>(s, tiles, short_segments, a.stream);
-  }
+  if (g_scan_timing) B200C_CUDA(cudaEventRecord(g_scan_begin, a.stream));
   set_error("Morton-ordered kNN called with dim=%d", a.dim);
-  return B200C_ERR_INVALID;
+  st = B200C_ERR_INVALID;
+  switch (a.dim) {
+    case 1: st = launch_knn_spatial_dim<1>(s, tiles, short_segments, a.stream); break;
+    case 2: st = launch_knn_spatial_dim<2>(s, tiles, short_segments, a.stream); break;
+    case 3: st = launch_knn_spatial_dim<3>(s, tiles, short_segments, a.stream); break;
+    case 4: st = launch_knn_spatial_dim<4>(s, tiles, short_segments, a.stream); break;
+    case 5: st = launch_knn_spatial_dim<5>(s, tiles, short_segments, a.stream); break;
+    case 6: st = launch_knn_spatial_dim<6>(s, tiles, short_segments, a.stream); break;
+    case 7: st = launch_knn_spatial_dim<7>(s, tiles, short_segments, a.stream); break;
+    case 8: st = launch_knn_spatial_dim<8>(s, tiles, short_segments, a.stream); break;
+  }
+  if (st == B200C_OK && g_scan_timing) B200C_CUDA(cudaEventRecord(g_scan_end, a.stream));
+  return st;
 }
 
 }  // namespace b200c

@@ -91,5 +91,7 @@ int launch_knn_rerank_f32(const KnnArgs &a, const int32_t *cand, const int32_t *
 bool knn_spatial_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_segments);
 size_t knn_spatial_workspace_bytes(int64_t n, int64_t m, int dim, int64_t num_segments, bool same_set);
 int launch_knn_spatial_f32(const KnnArgs &a, void *workspace, int64_t max_segment_rows);
+int knn_spatial_scan_timing(int enable);  // record CUDA events around the scan kernel of later calls
+float knn_spatial_last_scan_ms();         // duration of the last timed scan kernel (waits for it), -1 if none
 
 }  // namespace b200c

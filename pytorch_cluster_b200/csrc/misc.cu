@@ -270,6 +270,24 @@ radius_mask_base_kernel(const int64_t *__restrict__ ptr_x, const int64_t *__rest
   }
 }
 
+// FP32 throughput probe: 16 independent chains of fused multiply-adds per thread, `iters` rounds.
+constexpr int PROBE_CHAINS = 16, PROBE_THREADS = 256, PROBE_CTAS_PER_SM = 8;
+__global__ void __launch_bounds__(PROBE_THREADS)
+probe_fp32_kernel(int64_t iters, float seed, float *__restrict__ out) {
+  float v[PROBE_CHAINS];
+#pragma unroll
+  for (int i = 0; i < PROBE_CHAINS; ++i) v[i] = seed + (float)(threadIdx.x + i);
+  const float a = 1.0000001f, b = seed;
+  for (int64_t it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int i = 0; i < PROBE_CHAINS; ++i) v[i] = __fmaf_rn(v[i], a, b);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < PROBE_CHAINS; ++i) s += v[i];
+  if (s == 12345.678f) out[0] = s;  // keeps the chains alive; practically never true
+}
+
 int launch_radius_mask_base(const int64_t *ptr_x, const int64_t *ptr_y, int num_segments, int64_t n, int64_t m,
                             int chunk, int64_t *base, cudaStream_t stream) {
   radius_mask_base_kernel<<<1, MASK_BASE_THREADS, 0, stream>>>(ptr_x, ptr_y, num_segments, n, m, chunk, base);
@@ -314,6 +332,18 @@ extern "C" int b200c_batch_info(const int64_t *batch, int64_t n, int64_t *info, 
   batch_info_kernel<<<(unsigned)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(batch, n,
                                                                                   (unsigned long long *)info);
   B200C_LAUNCH_CHECK("batch_info_kernel");
+  return B200C_OK;
+}
+
+extern "C" int b200c_probe_fp32(int64_t iters, float *scratch, double *flops, b200c_stream_t stream) {
+  B200C_CHECK_ARG(iters >= 1 && scratch != nullptr && flops != nullptr, "Input mismatch");
+  int dev = 0, sms = 0;
+  B200C_CUDA(cudaGetDevice(&dev));
+  B200C_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int ctas = sms * PROBE_CTAS_PER_SM;
+  probe_fp32_kernel<<<ctas, PROBE_THREADS, 0, (cudaStream_t)stream>>>(iters, 0.5f, scratch);
+  B200C_LAUNCH_CHECK("probe_fp32_kernel");
+  *flops = 2.0 * (double)iters * PROBE_CHAINS * PROBE_THREADS * (double)ctas;
   return B200C_OK;
 }
 
