@@ -257,6 +257,9 @@ struct KnnSpatialArgs {
   // queue policy: during the first eager_steps scan steps any queued key is merged at once (the bound
   // is still falling fast); later only a queue holding lazy_fill keys is
   int eager_steps, lazy_fill;
+  // x-split: thread blocks per query tile, and their lists ([padded query][part][KP] keys) when > 1
+  int parts;
+  Key<float> *part_keys;
 };
 
 // ROLLED: the loop over a warp's eight queries stays a loop.  Short segments spend much of their time
@@ -280,7 +283,11 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int segs = a.num_segments;
-  const int64_t pos0 = (int64_t)blockIdx.x * KS_TILE;  // first padded query position of this tile
+  // With parts > 1 the points of a tile's segment are shared out over `parts` thread blocks: block
+  // `part` takes the scan steps part, part + parts, ... of the common outward order and leaves its
+  // list for knn_spatial_merge_kernel.
+  const int parts = a.parts, part = (int)(blockIdx.x % (unsigned)parts);
+  const int64_t pos0 = (int64_t)(blockIdx.x / (unsigned)parts) * KS_TILE;  // first padded query position of this tile
   if (pos0 >= a.yv.sptr[segs]) return;
   int b;
   {
@@ -295,7 +302,8 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
     b = lo;
   }
   const int64_t xs_lo = a.xv.sptr[b];
-  const int nch = (int)((a.xv.sptr[b + 1] - xs_lo) / SP_CHUNK);
+  const int nch_all = (int)((a.xv.sptr[b + 1] - xs_lo) / SP_CHUNK);
+  const int nch = nch_all > part ? (nch_all - part + parts - 1) / parts : 0;  // scan steps of this block
   const float wmax = __uint_as_float(a.xv.stat[2 * b]);
   const bool screen = wmax < 1e30f;  // false also for NaN
 
@@ -349,7 +357,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
 
   // ---- first chunk: the one around the tile's queries ----
   int seed = 0;
-  if (nch > 0) {
+  if (nch_all > 0) {
     if (a.yv.idx == a.xv.idx) {
       seed = (int)((pos0 - xs_lo) / SP_CHUNK);  // the queries are these points
     } else {
@@ -357,7 +365,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
       uint32_t key = a.yv.key[pos0 + KS_TILE / 2];
       if (key == 0xffffffffu) key = a.yv.key[pos0];
       const uint32_t *xk = a.xv.key + xs_lo;
-      int lo = 0, hi = nch * SP_CHUNK;
+      int lo = 0, hi = nch_all * SP_CHUNK;
       while (lo < hi) {
         const int m2 = (lo + hi) >> 1;
         if (xk[m2] < key)
@@ -367,7 +375,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
       }
       seed = lo / SP_CHUNK;
     }
-    if (seed > nch - 1) seed = nch - 1;
+    if (seed > nch_all - 1) seed = nch_all - 1;
   }
 
   // ---- stage ring ----
@@ -383,7 +391,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
 
   auto issue = [&](int step) {  // thread 0: bulk copies of the chunk of scan step `step`
     const int slot = step % KS_STAGES;
-    const int64_t pos = xs_lo + (int64_t)ks_chunk_at(step, seed, nch) * SP_CHUNK;
+    const int64_t pos = xs_lo + (int64_t)ks_chunk_at(part + step * parts, seed, nch_all) * SP_CHUNK;
     float *dst = stages + slot * Cfg::STAGE_ELEMS;
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(ks_smem(full + slot)),
                  "r"(Cfg::STAGE_BYTES)
@@ -513,6 +521,17 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
   }
 
   // ---- output ----
+  if (parts > 1) {
+    // this block's list of every query, sorted, KP keys each, for the merge kernel
+#pragma unroll 1
+    for (int qi = 0; qi < QW; ++qi) {
+      K *keys = my_keys + qi * (KP + Cfg::QCAP);
+      if (my_cnt[qi] > 0) ks_merge<KP>(keys, my_cnt[qi], a.k);
+      K *dst = a.part_keys + ((pos0 + warp + KS_WARPS * qi) * parts + part) * KP;
+      for (int e = lane; e < KP; e += 32) dst[e] = keys[e];
+    }
+    return;
+  }
   int my_valid = 0, my_irregular = 0;
 #pragma unroll
   for (int qi = 0; qi < QW; ++qi) {
@@ -529,6 +548,44 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
     if (lane == 0) {
       a.counts[q] = valid;
       my_valid += valid;
+    }
+  }
+  if (lane == 0 && my_valid) atomicAdd(a.num_valid, (unsigned long long)my_valid);
+  if (lane == 0 && my_irregular) atomicAdd(a.graph_irregular, my_irregular);
+}
+
+// Merges the `parts` lists of every query that an x-split scan left and writes the output as the scan
+// kernel itself would have: one warp per padded query position.
+template <int KP>
+__global__ void __launch_bounds__(CTA_THREADS)
+knn_spatial_merge_kernel(const KnnSpatialArgs a, int64_t padded_queries) {
+  using K = Key<float>;
+  __shared__ K keys_s[WARPS_PER_CTA][2 * KP];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t qpos = (int64_t)blockIdx.x * WARPS_PER_CTA + warp;
+  int my_valid = 0, my_irregular = 0;
+  if (qpos < padded_queries && qpos < a.yv.sptr[a.num_segments]) {
+    const int64_t q = a.yv.idx[qpos];
+    if (q >= 0) {
+      K *keys = keys_s[warp];
+      const K *src = a.part_keys + qpos * a.parts * KP;
+      for (int e = lane; e < KP; e += 32) keys[e] = src[e];
+      for (int p = 1; p < a.parts; ++p) {
+        for (int e = lane; e < KP; e += 32) keys[KP + e] = src[(int64_t)p * KP + e];
+        knn_merge<float, KP>(keys, KP, a.k, lane);  // empty keys sort to the end
+      }
+      __syncwarp();
+      if (a.graph_out != nullptr) {
+        if (!knn_finish_graph<float, KP>(keys, 0, a.k, q, a.graph_row_stride, a.graph_index_base, a.graph_out,
+                                         a.graph_s2t != 0, lane))
+          ++my_irregular;
+      } else {
+        const int valid = knn_finish<float, KP>(keys, 0, a.k, q, a.out_row, a.out_col, lane);
+        if (lane == 0) {
+          a.counts[q] = valid;
+          my_valid = valid;
+        }
+      }
     }
   }
   if (lane == 0 && my_valid) atomicAdd(a.num_valid, (unsigned long long)my_valid);

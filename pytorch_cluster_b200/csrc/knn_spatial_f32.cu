@@ -12,9 +12,39 @@ static int launch_knn_spatial_one(const KnnSpatialArgs &a, int64_t tiles, cudaSt
   auto kern = knn_spatial_kernel<DIM, KP, ROLLED>;
   static unsigned long long configured = 0ull;  // devices on which the shared-memory opt-in is done
   B200C_CUDA(opt_in_shared_memory(kern, Cfg::SMEM_BYTES, configured));
-  kern<<<(unsigned)tiles, KS_THREADS, Cfg::SMEM_BYTES, stream>>>(a);
+  kern<<<(unsigned)(tiles * a.parts), KS_THREADS, Cfg::SMEM_BYTES, stream>>>(a);
   B200C_LAUNCH_CHECK("knn_spatial_kernel");
+  if (a.parts > 1) {
+    const int64_t padded = tiles * KS_TILE;
+    knn_spatial_merge_kernel<KP><<<(unsigned)((padded + WARPS_PER_CTA - 1) / WARPS_PER_CTA), CTA_THREADS, 0, stream>>>(
+        a, padded);
+    B200C_LAUNCH_CHECK("knn_spatial_merge_kernel");
+  }
   return B200C_OK;
+}
+
+// Thread blocks per query tile.  One block per tile fills the device from about one block per SM on;
+// below that the points of every tile's segment are shared out over three blocks (five for very few
+// tiles), as long as each keeps a few dozen chunks to scan.  Odd counts: the scan alternates sides, and
+// an even count would hand a block chunks of one side only (measured slower).
+static int knn_spatial_parts(int64_t n, int64_t padded_queries, int64_t num_segments) {
+  int sms = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t tiles = padded_queries / KS_TILE;
+  const int64_t chunks = n / num_segments / SP_CHUNK;  // of an average segment
+  int parts = 1;
+  if (tiles * 5 <= 2 * sms && chunks >= 5 * 32)
+    parts = 5;
+  else if (tiles * 5 <= 6 * sms && chunks >= 3 * 32)
+    parts = 3;
+  if (const char *e = getenv("B200C_KS_PARTS")) parts = atoi(e);
+  return parts < 1 ? 1 : parts;
+}
+
+static int64_t padded_rows(int64_t rows, int64_t segs) {
+  const int64_t raw = rows + segs * (SP_CHUNK - 1);
+  return (raw + SP_CHUNK - 1) / SP_CHUNK * SP_CHUNK;
 }
 
 template <int DIM>
@@ -56,6 +86,10 @@ bool knn_spatial_applicable(int64_t n, int64_t m, int dim, int k, int64_t num_se
 size_t knn_spatial_workspace_bytes(int64_t n, int64_t m, int dim, int64_t num_segments, bool same_set) {
   size_t bytes = spatial_view_bytes(n, dim, num_segments, true);
   if (!same_set) bytes += spatial_view_bytes(m, dim, num_segments, false);
+  // lists of an x-split scan: at most 8 parts of 64 keys per padded query, and only for few queries
+  const int64_t padded = padded_rows(same_set ? n : m, num_segments);
+  const int parts = knn_spatial_parts(n, padded, num_segments);
+  if (parts > 1) bytes += (size_t)padded * parts * 64 * sizeof(uint64_t) + 256;
   return bytes;
 }
 
@@ -78,6 +112,12 @@ int launch_knn_spatial_f32(const KnnArgs &a, void *workspace, int64_t max_segmen
                              a.stream);
     if (st != B200C_OK) return st;
     padded_queries = s.yv.cap;
+  }
+  s.parts = knn_spatial_parts(a.n, padded_queries, a.num_segments);
+  s.part_keys = nullptr;
+  if (s.parts > 1) {
+    if (!same_set) off += spatial_view_bytes(a.m, a.dim, a.num_segments, false);
+    s.part_keys = (Key<float> *)((char *)workspace + (off + 255) / 256 * 256);
   }
   s.y = (const float *)a.y;
   s.num_segments = a.num_segments;
