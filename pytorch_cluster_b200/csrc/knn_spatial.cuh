@@ -42,16 +42,11 @@ namespace b200c {
 constexpr int KS_STAGES = 4;
 constexpr int KS_SPIN_LIMIT = 1 << 14;      // polls of a wait; each may sleep up to KS_WAIT_NS
 constexpr unsigned KS_WAIT_NS = 100000u;    // suspend-time hint of one poll (about 1.6 s in all)
-#ifndef KS_WARPS
-#define KS_WARPS 8
-#endif
-#ifndef KS_MINBLOCKS
-#define KS_MINBLOCKS 3
-#endif
-#define KS_PRAGMA_(x) _Pragma(#x)
-#define KS_UNROLL(n) KS_PRAGMA_(unroll n)
+constexpr int KS_WARPS = WARPS_PER_CTA;          // scanning warps per thread block
+constexpr int KS_MINBLOCKS = 3;                  // thread blocks per SM the register budget is set for
 constexpr int KS_TILE = 8 * KS_WARPS;            // queries per thread block
 constexpr int KS_THREADS = 32 * (KS_WARPS + 1);  // the scanning warps and the warp that issues the copies
+static_assert(KS_TILE == SP_TILE, "the sorted copies pad query segments to whole tiles of this size");
 constexpr float KS_MARGIN = 7.62939453125e-6f;  // 2^-17
 constexpr float KS_MARGIN_ABS = 2e-43f;         // about 140 steps of the subnormal grid: rounding there is absolute
 constexpr unsigned long long KS_ERROR_COUNT = 1ull << 62;  // added to *num_valid when a wait ran out

@@ -1,6 +1,4 @@
 // Instantiations and host side of the Morton-ordered kNN scan (knn_spatial.cuh).
-#include <cstdlib>
-
 #include "knn_spatial.cuh"
 #include "launchers.h"
 
@@ -38,7 +36,6 @@ static int knn_spatial_parts(int64_t n, int64_t padded_queries, int64_t num_segm
     parts = 5;
   else if (tiles * 5 <= 6 * sms && chunks >= 3 * 32)
     parts = 3;
-  if (const char *e = getenv("B200C_KS_PARTS")) parts = atoi(e);
   return parts < 1 ? 1 : parts;
 }
 
@@ -133,11 +130,8 @@ int launch_knn_spatial_f32(const KnnArgs &a, void *workspace, int64_t max_segmen
   s.graph_irregular = a.graph_irregular;
   s.eager_steps = 1;
   s.lazy_fill = a.k <= 32 ? 16 : 32;
-  if (const char *e = getenv("B200C_KS_EAGER")) s.eager_steps = atoi(e);
-  if (const char *e = getenv("B200C_KS_LAZY")) s.lazy_fill = atoi(e);
   // segments of up to 64 chunks on average count as short (the kernel variant with the rolled query loop)
-  bool short_segments = a.n / a.num_segments <= 64 * SP_CHUNK;
-  if (const char *e = getenv("B200C_KS_ROLLED")) short_segments = atoi(e) != 0;
+  const bool short_segments = a.n / a.num_segments <= 64 * SP_CHUNK;
   const int64_t tiles = padded_queries / KS_TILE;  // an upper bound: blocks past the last segment leave at once
   if (g_scan_timing) B200C_CUDA(cudaEventRecord(g_scan_begin, a.stream));
   set_error("Morton-ordered kNN called with dim=%d", a.dim);
