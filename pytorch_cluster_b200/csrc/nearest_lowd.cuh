@@ -27,7 +27,7 @@ struct NearestLowD {
 
 // pts / ptr_p: the points searched (the reference's y); rows / ptr_r: the rows assigned (its x).
 template <typename T, int DIM>
-__global__ void __launch_bounds__(CTA_THREADS, 3)
+__global__ void __launch_bounds__(CTA_THREADS, 2)
 nearest_lowd_kernel(const T *__restrict__ pts, const T *__restrict__ rows, const int64_t *__restrict__ ptr_p,
                     const int64_t *__restrict__ ptr_r, int num_segments, int64_t n_pts, int64_t n_rows,
                     int64_t *__restrict__ out) {

@@ -244,9 +244,16 @@ static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask
   const uint32_t *row = mask_words + mask_base[b] + (q - y_lo) * row_words;
   const int64_t o = offsets[q];
   int run = 0;
-  for (int64_t w0 = 0; w0 < row_words && run < count; w0 += 32) {
-    uint32_t word = w0 + lane < row_words ? row[w0 + lane] : 0u;
-    const int mine = __popc(word);
+  // 64 words (2048 points) per step: lane l takes words 2 l and 2 l + 1 in one 8-byte load (a row holds a
+  // whole number of chunks, i.e. a multiple of four words, and starts at such a multiple: the pair is aligned)
+  for (int64_t w0 = 0; w0 < row_words && run < count; w0 += 64) {
+    const int64_t w = w0 + 2 * lane;
+    uint2 pair = make_uint2(0u, 0u);
+    if (w + 1 < row_words)
+      pair = *reinterpret_cast<const uint2 *>(row + w);
+    else if (w < row_words)
+      pair.x = row[w];
+    const int mine = __popc(pair.x) + __popc(pair.y);
     // hits of lower lanes
     int incl = mine;
 #pragma unroll
@@ -255,10 +262,11 @@ static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask
       if (lane >= d) incl += t;
     }
     int pos = run + incl - mine;
-    const int64_t idx0 = x_lo + (w0 + lane) * 32;
-    while (word != 0u && pos < count) {
-      const int bit = __ffs(word) - 1;
-      word &= word - 1u;
+    const int64_t idx0 = x_lo + w * 32;
+    uint64_t bits = ((uint64_t)pair.y << 32) | pair.x;
+    while (bits != 0ull && pos < count) {
+      const int bit = __ffsll((long long)bits) - 1;
+      bits &= bits - 1ull;
       out_row[o + pos] = q;
       out_col[o + pos] = idx0 + bit;
       ++pos;
@@ -268,20 +276,47 @@ static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask
 }
 
 // Compaction after a DIRECT pass: copies the first counts[q] int32 slots of every query's row to
-// offsets[q].. of the int64 edge rows.  One warp per query.
+// offsets[q].. of the int64 edge rows.  A warp takes four consecutive queries at a time and issues
+// all their loads (counts, offsets, then up to eight slots per lane) before the first store, so that
+// four times as many bytes are in flight per warp as with a query at a time.
 static __global__ void radius_direct_compact_kernel(const int32_t *__restrict__ direct_rows,
                                              const int32_t *__restrict__ counts,
                                              const int64_t *__restrict__ offsets, int64_t m, int64_t max_nn,
                                              int64_t *__restrict__ out_row, int64_t *__restrict__ out_col) {
+  constexpr int G = 4;
   const int lane = threadIdx.x & 31;
-  const int64_t q = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (q >= m) return;
-  const int c = counts[q];
-  const int64_t o = offsets[q];
-  const int32_t *src = direct_rows + q * max_nn;
-  for (int e = lane; e < c; e += 32) {
-    out_row[o + e] = q;
-    out_col[o + e] = src[e];
+  const int64_t q0 = (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * G;
+  if (q0 >= m) return;
+  int c[G];
+  int64_t o[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const bool in = q0 + g < m;
+    c[g] = in ? counts[q0 + g] : 0;
+    o[g] = in ? offsets[q0 + g] : 0;
+  }
+  int mx = 0;
+#pragma unroll
+  for (int g = 0; g < G; ++g) mx = c[g] > mx ? c[g] : mx;
+  for (int e0 = 0; e0 < mx; e0 += 64) {
+    int32_t v[G][2];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int e = e0 + 32 * h + lane;
+        v[g][h] = e < c[g] ? direct_rows[(q0 + g) * max_nn + e] : 0;
+      }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int e = e0 + 32 * h + lane;
+        if (e < c[g]) {
+          out_row[o[g] + e] = q0 + g;
+          out_col[o[g] + e] = v[g][h];
+        }
+      }
   }
 }
 

@@ -44,7 +44,7 @@ static int launch_radius_lowd_dim(const RadiusArgs &a, bool fill) {
     return B200C_OK;
   }
   if (!a.direct_rows) return launch_radius_lowd_one<T, DIM, RADIUS_FILL>(a);
-  const int64_t threads = a.m * 32;
+  const int64_t threads = (a.m + 3) / 4 * 32;  // a warp per four queries
   radius_direct_compact_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, a.stream>>>(
       a.direct_rows, a.counts, a.offsets, a.m, a.max_nn, a.out_row, a.out_col);
   B200C_LAUNCH_CHECK("radius_direct_compact_kernel");
