@@ -84,7 +84,7 @@ def build_ops(force: bool = False, verbose: bool = False) -> str:
     cmd += [f"-I{p}" for p in ce.include_paths()]
     cmd += [f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
     cmd += [f"-L{PKG}", "-lb200cluster", "-Wl,-rpath,$ORIGIN", f"-L{lib_dir}", f"-Wl,-rpath,{lib_dir}",
-            "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch"]
+            "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ldl"]
     _run(cmd, verbose)
     return LIB_OPS
 

@@ -9,6 +9,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <ATen/cuda/CUDAEvent.h>
 #include <torch/script.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <vector>
 
@@ -25,6 +26,15 @@ namespace {
 // the bit-matrix mode when the matrix stays below the byte limit
 constexpr int64_t kRadiusDirectCap = 256;
 constexpr size_t kRadiusMaskMaxBytes = (size_t)8 << 30;
+
+// A named range around an operator call, visible in Nsight Systems timelines (header-only NVTX:
+// a no-op costing a few nanoseconds when no tool is attached).
+struct OpRange {
+  explicit OpRange(const char *name) { nvtxRangePushA(name); }
+  ~OpRange() { nvtxRangePop(); }
+  OpRange(const OpRange &) = delete;
+  OpRange &operator=(const OpRange &) = delete;
+};
 
 void check_status(int status) {
   TORCH_CHECK(status == B200C_OK, "b200_cluster: ", b200c_last_error());
@@ -102,6 +112,7 @@ constexpr int32_t kGraphWaitError = 1 << 30;
 // empty sorting passes on inputs of many small segments.
 torch::Tensor knn_hinted(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
                          std::optional<torch::Tensor> ptr_y, int64_t k, bool cosine, int64_t max_segment_rows) {
+  OpRange range("torch_cluster::knn");
   Prepared p = prepare(x, y, ptr_x, ptr_y);
   TORCH_CHECK(k <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
   TORCH_CHECK(k >= 1, "`k` needs to be positive");
@@ -153,6 +164,7 @@ namespace {
 // orientation on the device (torch_cluster/knn.py:131-144), with a single host sync for the size.
 torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr, int64_t k, bool loop,
                               bool source_to_target, bool cosine, int64_t max_segment_rows) {
+  OpRange range("torch_cluster::knn_graph_edges");
   const int64_t k1 = loop ? k : k + 1;
   Prepared p = prepare(x, x, ptr, ptr);
   TORCH_CHECK(k1 <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
@@ -216,6 +228,7 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
 torch::Tensor radius_part(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> ptr_x,
                           std::optional<torch::Tensor> ptr_y, double r, int64_t max_num_neighbors,
                           bool ignore_same_index, int64_t query_index_base, bool swap_rows) {
+  OpRange range("torch_cluster::radius");
   Prepared p = prepare(x, y, ptr_x, ptr_y);
   TORCH_CHECK(query_index_base >= 0, "Input mismatch");
 
@@ -327,6 +340,7 @@ torch::Tensor segment_ptr(torch::Tensor batch, int64_t num_segments) {
 
 // nearest: torch_cluster::nearest of csrc/nearest.cpp:22-36; host side of csrc/cuda/nearest_cuda.cu:63-88.
 torch::Tensor nearest(torch::Tensor x, torch::Tensor y, torch::Tensor ptr_x, torch::Tensor ptr_y) {
+  OpRange range("torch_cluster::nearest");
   CHECK_CUDA(x);
   CHECK_CUDA(y);
   CHECK_CUDA(ptr_x);
@@ -388,6 +402,7 @@ torch::Tensor fps_segment_classes(torch::Tensor ptr, torch::Tensor out_ptr, int6
 // per-segment sample counts are formed exactly as there (degree in ratio's dtype, times ratio,
 // ceil, cumulative sum); one host read gives the output size.
 torch::Tensor fps(torch::Tensor src, torch::Tensor ptr, torch::Tensor ratio, bool random_start) {
+  OpRange range("torch_cluster::fps");
   CHECK_CUDA(src);
   CHECK_CUDA(ptr);
   CHECK_CUDA(ratio);
@@ -483,6 +498,7 @@ namespace {
 // (pinned).  Returns the number of irregular queries (see b200c_knn_graph): 0 means `out` is final.
 int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool source_to_target, torch::Tensor out,
                        int64_t num_groups, int64_t device_index) {
+  OpRange range("torch_cluster::knn_graph_host");
   TORCH_CHECK(!x.is_cuda() && !ptr.is_cuda() && !out.is_cuda(), "knn_graph_host expects host tensors");
   CHECK_CONTIGUOUS(x);
   CHECK_INPUT(x.dim() == 2 && ptr.dim() == 1 && ptr.numel() >= 2);
