@@ -374,7 +374,7 @@ def strong_scaling(pc, dev, flush, world, rank):
         out[name] = {"ms_1gpu": t1, "ms_sharded": ts, "ms_assembled": ta, "speedup_sharded": t1 / ts,
                      "speedup_assembled": t1 / ta, unit_name + "_per_s_sharded": units_n / (ts * 1e-3),
                      unit_name + "_per_s_assembled": units_n / (ta * 1e-3),
-                     "assembly": {"collective": "all-gather of the edge rows (NCCL), one per row",
+                     "assembly": {"collective": "one all-gather of the padded [2, width] slices (NCCL) + copies into place",
                                   "bytes_received_per_rank": gather_bytes(want) * (world - 1) // world,
                                   "ms": ta - ts}}
 

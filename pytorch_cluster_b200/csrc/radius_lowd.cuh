@@ -244,16 +244,14 @@ static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask
   const uint32_t *row = mask_words + mask_base[b] + (q - y_lo) * row_words;
   const int64_t o = offsets[q];
   int run = 0;
-  // 64 words (2048 points) per step: lane l takes words 2 l and 2 l + 1 in one 8-byte load (a row holds a
-  // whole number of chunks, i.e. a multiple of four words, and starts at such a multiple: the pair is aligned)
-  for (int64_t w0 = 0; w0 < row_words && run < count; w0 += 64) {
-    const int64_t w = w0 + 2 * lane;
-    uint2 pair = make_uint2(0u, 0u);
-    if (w + 1 < row_words)
-      pair = *reinterpret_cast<const uint2 *>(row + w);
-    else if (w < row_words)
-      pair.x = row[w];
-    const int mine = __popc(pair.x) + __popc(pair.y);
+  // 128 words (4096 points) per step: lane l takes words 4 l .. 4 l + 3 in one 16-byte load (a row holds a
+  // whole number of chunks, i.e. a multiple of four words, and starts at such a multiple: the load is aligned
+  // and either wholly inside the row or wholly past its end)
+  for (int64_t w0 = 0; w0 < row_words && run < count; w0 += 128) {
+    const int64_t w = w0 + 4 * lane;
+    uint4 quad = make_uint4(0u, 0u, 0u, 0u);
+    if (w < row_words) quad = *reinterpret_cast<const uint4 *>(row + w);
+    const int mine = __popc(quad.x) + __popc(quad.y) + __popc(quad.z) + __popc(quad.w);
     // hits of lower lanes
     int incl = mine;
 #pragma unroll
@@ -263,12 +261,19 @@ static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask
     }
     int pos = run + incl - mine;
     const int64_t idx0 = x_lo + w * 32;
-    uint64_t bits = ((uint64_t)pair.y << 32) | pair.x;
-    while (bits != 0ull && pos < count) {
-      const int bit = __ffsll((long long)bits) - 1;
-      bits &= bits - 1ull;
+    uint64_t lo = ((uint64_t)quad.y << 32) | quad.x, hi = ((uint64_t)quad.w << 32) | quad.z;
+    while (lo != 0ull && pos < count) {
+      const int bit = __ffsll((long long)lo) - 1;
+      lo &= lo - 1ull;
       out_row[o + pos] = q;
       out_col[o + pos] = idx0 + bit;
+      ++pos;
+    }
+    while (hi != 0ull && pos < count) {
+      const int bit = __ffsll((long long)hi) - 1;
+      hi &= hi - 1ull;
+      out_row[o + pos] = q;
+      out_col[o + pos] = idx0 + 64 + bit;
       ++pos;
     }
     run += __shfl_sync(FULL_MASK, incl, 31);
