@@ -39,6 +39,15 @@ size_t spatial_view_carve(SpatialView *v, void *workspace, int64_t rows, int dim
   t.pairs_cap = pairs_small_cap(rows) + 2 * rows + SP_SORT_BLOCK;
   t.pairs = (uint64_t *)take((size_t)t.pairs_cap * 8);
   if (points) t.blob = (float *)take((size_t)cap * (2 * dim + 2) * 4);
+  const int64_t large_blocks = 2 * rows / SP_SORT_BLOCK + 2;
+  t.pairs2 = (uint64_t *)take((size_t)rows * 8);
+  t.split = (uint64_t *)take((size_t)large_blocks * SP_MAX_BUCKETS * 8);
+  t.bcount = (int32_t *)take((size_t)large_blocks * SP_MAX_BUCKETS * 4);
+  t.boffset = (int32_t *)take((size_t)large_blocks * (SP_MAX_BUCKETS + 1) * 4);
+  t.bcursor = (int32_t *)take((size_t)large_blocks * SP_MAX_BUCKETS * 4);
+  t.table_cap = rows / SP_BUCKET_TARGET + rows / SP_SORT_BLOCK + 2 * large_blocks + 8;
+  t.table = (int32_t *)take((size_t)t.table_cap * 4 * 4);
+  t.table_count = (int32_t *)take(4);
   if (v) *v = t;
   return off;
 }
@@ -129,9 +138,11 @@ __device__ __forceinline__ void atomic_max_float(float *addr, float v) {
 __global__ void __launch_bounds__(SP_THREADS)
 sp_layout_kernel(const int64_t *__restrict__ ptr, int segs, int64_t rows, int64_t small_cap, int dim,
                  int64_t *__restrict__ sptr, int64_t *__restrict__ pptr, int64_t *__restrict__ lptr,
-                 float *__restrict__ box, uint32_t *__restrict__ stat, int reset_box) {
+                 float *__restrict__ box, uint32_t *__restrict__ stat, int reset_box,
+                 int32_t *__restrict__ table_count) {
   __shared__ int64_t run[3][SP_THREADS];
   const int t = threadIdx.x;
+  if (t == 0) *table_count = 0;
   const int per = (segs + SP_THREADS - 1) / SP_THREADS;
   const int lo = t * per < segs ? t * per : segs;
   const int hi = lo + per < segs ? lo + per : segs;
@@ -610,6 +621,215 @@ sp_emit_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, i
   if (points) publish_wmax(wmax, bad, v.stat + 2 * b, red);
 }
 
+// ---- bucket sort of the segments above one sort block (up to SP_BUCKET_MAX_ROWS points) ---------------------
+// Instead of log^2 exchange passes over the whole segment: a sample of its (key, row) pairs is sorted by
+// one thread block and gives up to 255 splitters; every pair is counted into, then scattered to, the
+// bucket between two splitters (pairs are unique, so even equal keys spread evenly); each bucket — about
+// 4096 pairs — is sorted in shared memory by its own thread block, which also writes the sorted copy.
+// Six launches whatever the size, and as many blocks at work as there are buckets.  A bucket that comes out
+// larger than a sort block (a sample that misled) is cut into pieces that are sorted on their own: the
+// order is then not quite the Morton order, which costs the scan time, never correctness.
+constexpr int SP_SAMPLE = 8192;
+
+__device__ __forceinline__ int bucket_count_of(int64_t nb) {
+  const int64_t want = (nb + SP_BUCKET_TARGET - 1) / SP_BUCKET_TARGET;
+  return (int)(want < 2 ? 2 : (want > SP_MAX_BUCKETS ? SP_MAX_BUCKETS : want));
+}
+
+// bucket of a pair: number of splitters <= pair
+__device__ __forceinline__ int bucket_of(const uint64_t *split_s, int nsplit, uint64_t pair) {
+  int lo = 0, hi = nsplit;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (split_s[mid] <= pair)
+      lo = mid + 1;
+    else
+      hi = mid;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(SP_THREADS)
+sp_sample_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
+  extern __shared__ __align__(16) unsigned char sp_smem[];
+  uint64_t *a = reinterpret_cast<uint64_t *>(sp_smem);
+  const int b = blockIdx.x, tid = threadIdx.x;
+  if (!large_segment(v, b)) return;
+  int64_t x_lo, x_hi;
+  seg_rows_clamped(ptr, rows, b, x_lo, x_hi);
+  const int64_t nb = x_hi - x_lo;
+  const uint64_t *src = v.pairs + v.pptr[b];
+  // 32 samples per bucket (a power of two between 1024 and SP_SAMPLE): one pair from every stretch of
+  // nb / samples pairs, at a position that varies from stretch to stretch
+  const int nbk = bucket_count_of(nb);
+  int slog = 10;
+  while ((1 << slog) < 32 * nbk && (1 << slog) < SP_SAMPLE) ++slog;
+  const int samples = 1 << slog;
+  for (int i = tid; i < samples; i += SP_THREADS) {
+    const int64_t lo = nb * i / samples, hi = nb * (i + 1) / samples;
+    const int64_t span = hi > lo ? hi - lo : 1;
+    a[sp_pad(i)] = src[lo + (int64_t)((uint32_t)i * 2654435761u % (uint64_t)span)];
+  }
+  smem_bitonic_blocked(a, slog, 0, 1, slog, tid, SP_THREADS);
+  const int64_t li = v.lptr[b];
+  for (int j = tid; j < SP_MAX_BUCKETS; j += SP_THREADS) {
+    if (j < nbk - 1) v.split[li * SP_MAX_BUCKETS + j] = a[sp_pad((int)((int64_t)(j + 1) * samples / nbk))];
+    v.bcount[li * SP_MAX_BUCKETS + j] = 0;
+  }
+}
+
+__global__ void __launch_bounds__(SP_THREADS)
+sp_count_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
+  __shared__ uint64_t split_s[SP_MAX_BUCKETS];
+  __shared__ int hist[SP_MAX_BUCKETS];
+  const int b = blockIdx.y, tid = threadIdx.x;
+  if (!large_segment(v, b)) return;
+  int64_t x_lo, x_hi;
+  seg_rows_clamped(ptr, rows, b, x_lo, x_hi);
+  const int64_t nb = x_hi - x_lo, li = v.lptr[b];
+  const int nbk = bucket_count_of(nb);
+  for (int j = tid; j < SP_MAX_BUCKETS; j += SP_THREADS) {
+    if (j < nbk - 1) split_s[j] = v.split[li * SP_MAX_BUCKETS + j];
+    hist[j] = 0;
+  }
+  __syncthreads();
+  const uint64_t *src = v.pairs + v.pptr[b];
+  for (int64_t i = (int64_t)blockIdx.x * SP_THREADS + tid; i < nb; i += (int64_t)gridDim.x * SP_THREADS)
+    atomicAdd(&hist[bucket_of(split_s, nbk - 1, src[i])], 1);
+  __syncthreads();
+  for (int j = tid; j < nbk; j += SP_THREADS)
+    if (hist[j]) atomicAdd(&v.bcount[li * SP_MAX_BUCKETS + j], hist[j]);
+}
+
+// One block per segment: bucket offsets, scatter cursors, and the segment's entries of the bucket table.
+__global__ void __launch_bounds__(SP_MAX_BUCKETS)
+sp_offsets_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
+  __shared__ int scan[SP_MAX_BUCKETS], entries[SP_MAX_BUCKETS];
+  __shared__ int table_base;
+  const int b = blockIdx.x, t = threadIdx.x;
+  if (!large_segment(v, b)) return;
+  int64_t x_lo, x_hi;
+  seg_rows_clamped(ptr, rows, b, x_lo, x_hi);
+  const int64_t nb = x_hi - x_lo, li = v.lptr[b];
+  const int nbk = bucket_count_of(nb);
+  const int mine = t < nbk ? v.bcount[li * SP_MAX_BUCKETS + t] : 0;
+  const int pieces = (mine + SP_SORT_BLOCK - 1) / SP_SORT_BLOCK;  // 0 for an empty bucket, 1 as a rule
+  scan[t] = mine;
+  entries[t] = pieces;
+  __syncthreads();
+  for (int o = 1; o < SP_MAX_BUCKETS; o <<= 1) {
+    const int a0 = t >= o ? scan[t - o] : 0, a1 = t >= o ? entries[t - o] : 0;
+    __syncthreads();
+    scan[t] += a0;
+    entries[t] += a1;
+    __syncthreads();
+  }
+  if (t == SP_MAX_BUCKETS - 1) table_base = atomicAdd(v.table_count, entries[t]);
+  __syncthreads();
+  const int start = scan[t] - mine;
+  if (t < nbk) {
+    v.boffset[li * (SP_MAX_BUCKETS + 1) + t] = start;
+    v.bcursor[li * SP_MAX_BUCKETS + t] = start;
+  }
+  if (t == 0) v.boffset[li * (SP_MAX_BUCKETS + 1) + nbk] = (int)nb;
+  int e = table_base + entries[t] - pieces;
+  for (int p = 0; p < pieces; ++p, ++e) {
+    if (e >= v.table_cap) break;  // cannot happen: the table is sized for every bucket and every piece
+    const int first = start + p * SP_SORT_BLOCK;
+    const int size = mine - p * SP_SORT_BLOCK < SP_SORT_BLOCK ? mine - p * SP_SORT_BLOCK : SP_SORT_BLOCK;
+    v.table[4 * e + 0] = b;
+    v.table[4 * e + 1] = first;
+    v.table[4 * e + 2] = size;
+    v.table[4 * e + 3] = first + size == nb ? 1 : 0;
+  }
+}
+
+// Scatter with one global atomic per (thread block, bucket): a block takes stretches of 4096 pairs, ranks
+// them within their buckets in shared memory, reserves a range of every bucket, then writes.
+__global__ void __launch_bounds__(SP_THREADS)
+sp_scatter_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
+  __shared__ uint64_t split_s[SP_MAX_BUCKETS];
+  __shared__ int hist[SP_MAX_BUCKETS], base[SP_MAX_BUCKETS];
+  constexpr int PER = 4;
+  const int b = blockIdx.y, tid = threadIdx.x;
+  if (!large_segment(v, b)) return;
+  int64_t x_lo, x_hi;
+  seg_rows_clamped(ptr, rows, b, x_lo, x_hi);
+  const int64_t nb = x_hi - x_lo, li = v.lptr[b];
+  const int nbk = bucket_count_of(nb);
+  for (int j = tid; j < nbk - 1; j += SP_THREADS) split_s[j] = v.split[li * SP_MAX_BUCKETS + j];
+  const uint64_t *src = v.pairs + v.pptr[b];
+  uint64_t *dst = v.pairs2 + x_lo;  // a segment's scattered pairs take the place of its rows
+  for (int64_t t0 = (int64_t)blockIdx.x * (SP_THREADS * PER); t0 < nb; t0 += (int64_t)gridDim.x * (SP_THREADS * PER)) {
+    for (int j = tid; j < SP_MAX_BUCKETS; j += SP_THREADS) hist[j] = 0;
+    __syncthreads();
+    uint64_t pair[PER];
+    int bucket[PER], rank[PER];
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int64_t i = t0 + u * SP_THREADS + tid;
+      bucket[u] = -1;
+      if (i < nb) {
+        pair[u] = src[i];
+        bucket[u] = bucket_of(split_s, nbk - 1, pair[u]);
+        rank[u] = atomicAdd(&hist[bucket[u]], 1);
+      }
+    }
+    __syncthreads();
+    for (int j = tid; j < nbk; j += SP_THREADS)
+      base[j] = hist[j] ? atomicAdd(&v.bcursor[li * SP_MAX_BUCKETS + j], hist[j]) : 0;
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < PER; ++u)
+      if (bucket[u] >= 0) dst[base[bucket[u]] + rank[u]] = pair[u];
+    __syncthreads();
+  }
+}
+
+// One block per entry of the bucket table: sort the bucket in shared memory, write its part of the sorted copy.
+template <int DIM>
+__global__ void __launch_bounds__(SP_THREADS)
+sp_bucket_sort_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, int64_t rows,
+                      const float *__restrict__ box, int points, SpatialView v) {
+  extern __shared__ __align__(16) unsigned char sp_smem[];
+  uint64_t *a = reinterpret_cast<uint64_t *>(sp_smem);
+  __shared__ float red[32];
+  const int e = blockIdx.x, tid = threadIdx.x;
+  if (e >= *v.table_count || e >= v.table_cap) return;
+  const int b = v.table[4 * e], first = v.table[4 * e + 1], size = v.table[4 * e + 2], last = v.table[4 * e + 3];
+  int64_t x_lo, x_hi;
+  seg_rows_clamped(ptr, rows, b, x_lo, x_hi);
+  const int64_t nb = x_hi - x_lo;
+  const uint64_t *src = v.pairs2 + x_lo + first;
+  int plog = 0;
+  while ((1 << plog) < size) ++plog;
+  const int p2 = 1 << plog;
+  const bool blocked = p2 >= 1024;
+  for (int i = tid; i < p2; i += SP_THREADS) a[blocked ? sp_pad(i) : i] = i < size ? src[i] : ~0ull;
+  if (blocked)
+    smem_bitonic_blocked(a, plog, 0, 1, plog, tid, SP_THREADS);
+  else if (p2 > 1)
+    smem_bitonic(a, p2, 0, 2, p2, tid, SP_THREADS);
+  else
+    __syncthreads();
+  float lo[DIM], scale[DIM], centre[DIM];
+  box_scale<DIM>(box + (int64_t)b * 2 * DIM, lo, scale, centre);
+  const int64_t s_lo = v.sptr[b];
+  float wmax = 0.f;
+  bool bad = false;
+  for (int j = tid; j < size; j += SP_THREADS) {
+    const float wv = emit_position<DIM>(v, pts, x_lo, s_lo + first + j, a[blocked ? sp_pad(j) : j], true, points != 0, centre);
+    bad |= !(wv < 1e30f);
+    wmax = fmaxf(wmax, wv);
+  }
+  if (last) {
+    const int64_t padded = (nb + SP_CHUNK - 1) / SP_CHUNK * SP_CHUNK;
+    for (int64_t j = nb + tid; j < padded; j += SP_THREADS)
+      (void)emit_position<DIM>(v, pts, x_lo, s_lo + j, 0ull, false, points != 0, centre);
+  }
+  if (points) publish_wmax(wmax, bad, v.stat + 2 * b, red);
+}
+
 // ---- host side -------------------------------------------------------------------------------------------
 template <int DIM>
 static int spatial_sort_dim(const float *pts, const int64_t *ptr, int64_t segs, int64_t rows, const float *box_from,
@@ -618,7 +838,7 @@ static int spatial_sort_dim(const float *pts, const int64_t *ptr, int64_t segs, 
   static unsigned long long done_small = 0ull, done_block = 0ull;
   B200C_CUDA(opt_in_shared_memory(sp_small_kernel<DIM>, sort_smem, done_small));
   sp_layout_kernel<<<1, SP_THREADS, 0, stream>>>(ptr, (int)segs, rows, pairs_small_cap(rows), DIM, v->sptr, v->pptr,
-                                                 v->lptr, v->box, v->stat, box_from == nullptr ? 1 : 0);
+                                                 v->lptr, v->box, v->stat, box_from == nullptr ? 1 : 0, v->table_count);
   B200C_LAUNCH_CHECK("sp_layout_kernel");
   sp_small_kernel<DIM><<<(unsigned)segs, SP_THREADS, sort_smem, stream>>>(pts, ptr, (int)segs, rows, box_from,
                                                                            points ? 1 : 0, *v);
@@ -637,6 +857,23 @@ static int spatial_sort_dim(const float *pts, const int64_t *ptr, int64_t segs, 
   }
   sp_keys_kernel<DIM><<<grid, SP_THREADS, 0, stream>>>(pts, ptr, rows, box, *v);
   B200C_LAUNCH_CHECK("sp_keys_kernel");
+  if (max_segment_rows <= SP_BUCKET_MAX_ROWS) {
+    static unsigned long long done_sample = 0ull, done_bucket = 0ull;
+    B200C_CUDA(opt_in_shared_memory(sp_sample_kernel, sort_smem, done_sample));
+    B200C_CUDA(opt_in_shared_memory(sp_bucket_sort_kernel<DIM>, sort_smem, done_bucket));
+    sp_sample_kernel<<<(unsigned)segs, SP_THREADS, sort_smem, stream>>>(ptr, rows, *v);
+    B200C_LAUNCH_CHECK("sp_sample_kernel");
+    sp_count_kernel<<<grid, SP_THREADS, 0, stream>>>(ptr, rows, *v);
+    B200C_LAUNCH_CHECK("sp_count_kernel");
+    sp_offsets_kernel<<<(unsigned)segs, SP_MAX_BUCKETS, 0, stream>>>(ptr, rows, *v);
+    B200C_LAUNCH_CHECK("sp_offsets_kernel");
+    sp_scatter_kernel<<<grid, SP_THREADS, 0, stream>>>(ptr, rows, *v);
+    B200C_LAUNCH_CHECK("sp_scatter_kernel");
+    sp_bucket_sort_kernel<DIM><<<(unsigned)v->table_cap, SP_THREADS, sort_smem, stream>>>(pts, ptr, rows, box,
+                                                                                        points ? 1 : 0, *v);
+    B200C_LAUNCH_CHECK("sp_bucket_sort_kernel");
+    return B200C_OK;
+  }
   const int64_t max_blocks = 2 * rows / SP_SORT_BLOCK + 1;  // padded sizes are below twice the row counts
   sp_sort_block_kernel<<<(unsigned)max_blocks, SP_THREADS, sort_smem, stream>>>(*v, (int)segs, 0);
   B200C_LAUNCH_CHECK("sp_sort_block_kernel");

@@ -45,7 +45,22 @@ struct SpatialView {
   int64_t *pptr;    // [B + 1] first pair of every segment
   int64_t *lptr;    // [B + 1] sort blocks (SP_SORT_BLOCK pairs) of the segments above one block, before each segment
   int64_t pairs_cap;
+  // bucket sort of the segments above one sort block: the pairs scattered into buckets (pairs2), per
+  // such segment up to SP_MAX_BUCKETS - 1 splitters and bucket counts / offsets (indexed by the
+  // segment's lptr), and the table of buckets to sort (segment, first position, size)
+  uint64_t *pairs2;     // [rows]
+  uint64_t *split;      // [large_blocks][SP_MAX_BUCKETS]
+  int32_t *bcount;      // [large_blocks][SP_MAX_BUCKETS]
+  int32_t *boffset;     // [large_blocks][SP_MAX_BUCKETS + 1]
+  int32_t *bcursor;     // [large_blocks][SP_MAX_BUCKETS]
+  int32_t *table;       // [table_cap][4]: segment, first position in the segment, size, last-of-segment flag
+  int32_t *table_count; // [1]
+  int64_t table_cap;
 };
+
+constexpr int SP_MAX_BUCKETS = 256;
+constexpr int SP_BUCKET_TARGET = 2048;          // points per bucket aimed at
+constexpr int64_t SP_BUCKET_MAX_ROWS = 1 << 19; // segments up to this size take the bucket sort (256 buckets of 2048)
 
 // Bytes of workspace one view needs (points: with coordinates; queries: order and keys only).
 size_t spatial_view_bytes(int64_t rows, int dim, int64_t num_segments, bool points);

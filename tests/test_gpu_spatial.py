@@ -167,3 +167,22 @@ def test_spatial_path_through_the_python_api():
         assert np.array_equal(got, orc.knn_graph_api(x.numpy(), 10, batch.numpy(), flow=flow))
     assert torch.ops.torch_cluster.batch_info(batch.to(DEV)) == [3, 9000]
     assert torch.ops.torch_cluster.batch_info(torch.tensor([0, 0, 3, 3, 3, 7], device=DEV)) == [8, 3]
+
+
+def test_large_segments_with_duplicates_and_outliers():
+    """Segments above one sort block go through the bucket sort (sampled splitters): equal keys in bulk (half of a
+    cloud is one point), and a bounding box blown up by a few far outliers so that nearly all points share a cell."""
+    g = torch.Generator().manual_seed(23)
+    x = torch.rand(120000, 3, generator=g)
+    x[:60000] = x[0]
+    x[-3:] = torch.tensor([[1e6, 0., 0.], [0., -1e6, 0.], [0., 0., 1e6]])
+    x = x.to(DEV)
+    order, keys, first = _cabi().morton_order(x)
+    order, keys = order.cpu(), keys.cpu().long() & 0xffffffff
+    assert torch.equal(torch.sort(order[:120000].long()).values, torch.arange(120000))
+    k = keys[:120000]
+    assert bool((k[1:] >= k[:-1]).all())
+    y = x[::97].contiguous()
+    _both(x, y, 16)
+    ptr_x, ptr_y = _ptr([70000, 50000]), _ptr([700, y.shape[0] - 700])
+    _both(x, y, 8, ptr_x, ptr_y, hint=70000)
