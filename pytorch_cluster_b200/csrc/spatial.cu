@@ -1,6 +1,7 @@
 // Morton-ordered copies of low-dimensional fp32 point sets (see spatial.cuh): segment layout,
-// bounding boxes, keys, a bitonic sort of (key, row) pairs — in shared memory for segments of up
-// to SP_SORT_BLOCK points, with global-memory exchange steps above — and the sorted arrays.
+// bounding boxes, keys, a sort of (key, row) pairs — a bitonic network in shared memory for segments
+// of up to SP_SORT_BLOCK points, a bucket sort with sampled splitters above (bitonic exchange passes
+// through global memory for the very largest) — and the sorted arrays.
 // All passes are HBM- or latency-bound and small next to the scan they prepare: 32 bytes are read
 // and about 60 written per point.
 #include "launchers.h"

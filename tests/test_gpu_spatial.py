@@ -33,7 +33,8 @@ def _both(x, y, k, px=None, py=None, hint=0):
     return fast
 
 
-@pytest.mark.parametrize("rows", [1, 7, 300, 1024, 1500, 4096, 16384, 16385, 40000, 200001])
+# up to 16384 rows: one thread block; up to 2^19: bucket sort; above: exchange passes through global memory
+@pytest.mark.parametrize("rows", [1, 7, 300, 1024, 1500, 4096, 16384, 16385, 40000, 200001, 524288, 600001])
 def test_morton_order_one_segment(rows):
     g = torch.Generator().manual_seed(rows)
     x = torch.randn(rows, 3, generator=g).to(DEV)
