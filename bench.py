@@ -233,8 +233,12 @@ def radius_passes(cabi, x, ptr, r, max_nn, ms_of, peaks):
     stream = torch.cuda.current_stream().cuda_stream
     counts = torch.empty(n, dtype=torch.int32, device=x.device)
     hbm = (peaks.get("hbm_gbs") or 6650.0)
-    if max_nn <= 256:
-        nbytes = lib.b200c_radius_workspace_bytes(n, n, dim, max_nn, dt)
+    # the operator's rule for the screened scan: segments of at least 2048 * max_nn points
+    screen_bytes = (lib.b200c_radius_screen_workspace_bytes(n, n, dim, max_nn, dt, nseg)
+                    if n // nseg >= 2048 * max_nn else 0)
+    if screen_bytes > 0 or max_nn <= 256:
+        # the screened scan parks the hits (any cap); without it the plain one-pass mode does for small caps
+        nbytes = max(screen_bytes, lib.b200c_radius_workspace_bytes(n, n, dim, max_nn, dt))
         ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
         count = lambda: _native.check(lib.b200c_radius_count(x.data_ptr(), x.data_ptr(), ptr.data_ptr(), ptr.data_ptr(),
                                                              nseg, n, n, dim, float(r), max_nn, 1, dt, counts.data_ptr(),
@@ -248,6 +252,8 @@ def radius_passes(cabi, x, ptr, r, max_nn, ms_of, peaks):
                                                            offsets.data_ptr(), total, out.data_ptr(), ws.data_ptr(), nbytes,
                                                            stream))
         read_per_edge, kernel = 4, "radius_direct_compact_kernel"
+        if screen_bytes > 0 and max_nn > 256:
+            kernel += " + radius_screen_kernel for queries beyond the parked rows (none here)"
         extra_read = 0
     else:
         hp = ptr.cpu()
@@ -300,6 +306,15 @@ def extra_workloads(pc, cabi, dev, flush, peak_tf, world, rank, peaks):
         "kernels_ms": tk, "scan_kernel_ms": tscan, "api_ms": ta, "queries_per_s": w["queries"] / (ta * 1e-3),
         "fp32_frac": 8.0 * w["pairs"] / (tk * 1e-3) / 1e12 / peak_tf,
         "fp32_frac_scan_kernel": 8.0 * w["pairs"] / (tscan * 1e-3) / 1e12 / peak_tf}
+    # the same clouds as a fixed-radius search with sparse hits (about 15 per query, cap 32): segments of
+    # 131072 >= 2048 * 32 points, so the operator takes the screened scan; beside it the plain scan
+    tr = ms_of(lambda: pc.radius(x, y, 3.0, bx, by, max_num_neighbors=32))
+    edges = int(pc.radius(x, y, 3.0, bx, by, max_num_neighbors=32).shape[1])
+    tplain = ms_of(lambda: cabi.radius(x, y, 3.0, px, py, 32))
+    out["radius_bipartite_8x131072x8192_r3_max32"] = {
+        "api_ms": tr, "edges": edges, "edges_per_s": edges / (tr * 1e-3),
+        "fp32_frac": 8.0 * w["pairs"] / (tr * 1e-3) / 1e12 / peak_tf,
+        "plain_scan_call_ms": tplain, "fp32_frac_plain_scan": 8.0 * w["pairs"] / (tplain * 1e-3) / 1e12 / peak_tf}
     del x, y
 
     # feature-space kNN: 16 clouds x 2048 points x 64 features, k = 20
@@ -549,6 +564,11 @@ def run_only(args):
         x = torch.randn(32768, 64, generator=g).to(dev)
         ptr = torch.arange(0, 32768 + 1, 2048, device=dev)
         fn = lambda: cabi.knn_padded_nosync(x, x, 21, ptr, ptr, args.cosine)
+    elif name in ("radius_mixture_small_screen", "radius_mixture_small_screen_large_cap"):
+        w = make_radius_mixture(clouds=16)     # 16 of the 64 clouds, the screened scan
+        x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 16)
+        max_nn = 8192 if name.endswith("large_cap") else 64
+        fn = lambda: cabi.radius(x, x, w["r"], ptr, ptr, max_nn, True, screen=True)
     elif name in ("radius_mixture_small", "radius_mixture_small_two_scans", "radius_mixture_small_masks"):
         w = make_radius_mixture(clouds=16)     # 16 of the 64 clouds
         x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 16)

@@ -240,6 +240,23 @@ int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t num_segments
  * pass 2).  Give both passes the same workspace, untouched in between. */
 size_t b200c_radius_workspace_bytes(int64_t n, int64_t m, int64_t dim,
                                     int64_t max_num_neighbors, int dtype);
+/* Workspace of the screened scan for fp32 points of up to 8 features (0: not applicable — other
+ * types, tiny inputs, fewer than 512 points per segment on average).  Given at least this many bytes
+ * (it is never less than b200c_radius_workspace_bytes asks for the same call), pass 1 first lays the
+ * points out in chunks of 256 (coordinates relative to the segment's first point, their squared norms,
+ * the original coordinates) and then screens every (query, chunk) pair with `dim` fused multiply-adds per
+ * point against a threshold that covers the rounding of both sides; only chunks with a point at or below
+ * it are evaluated again for that query with the reference's arithmetic (csrc/cuda/radius_cuda.cu:28-33),
+ * so the result is the same.  Worth it when hits are sparse: a screened pair costs about half of an exact
+ * one, a pair with a hit costs both.  Segments of at least 2048 * max_num_neighbors points guarantee that
+ * (a query keeps at most max_num_neighbors hits), which is the rule torch_cluster::radius applies.
+ * Pass 1 parks the hits (up to 64 per query for neighbour caps above 256), pass 2 copies them and scans
+ * again only for queries that found more than were parked.  After pass 1 the first 8 bytes of the
+ * workspace are a status word (int64): non-zero means that a bounded wait inside the scan ran out and the
+ * counts are invalid; read it together with the total of the counts before sizing the output. */
+size_t b200c_radius_screen_workspace_bytes(int64_t n, int64_t m, int64_t dim,
+                                           int64_t max_num_neighbors, int dtype,
+                                           int64_t num_segments);
 int b200c_radius_count(const void *x, const void *y, const int64_t *ptr_x,
                        const int64_t *ptr_y, int64_t num_segments, int64_t n,
                        int64_t m, int64_t dim, double r,

@@ -74,6 +74,8 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_knn_graph_tail_write.argtypes = [p, p, p, i64, i64, i32, i32, i64, p, p]
     lib.b200c_radius_workspace_bytes.argtypes = [i64, i64, i64, i64, i32]
     lib.b200c_radius_workspace_bytes.restype = sz
+    lib.b200c_radius_screen_workspace_bytes.argtypes = [i64, i64, i64, i64, i32, i64]
+    lib.b200c_radius_screen_workspace_bytes.restype = sz
     lib.b200c_radius_count.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, sz, p]
     lib.b200c_radius_fill.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, i64, p, p, sz, p]
     lib.b200c_radius_count_part.argtypes = [p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i64, i32, p, p, sz, p]

@@ -95,13 +95,24 @@ def radius_counts(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_
     return counts
 
 
-def radius(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_index=False, one_pass=True):
+def radius(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_index=False, one_pass=True,
+           screen=False):
+    """count -> scan -> fill.  one_pass: with the workspace of b200c_radius_workspace_bytes; screen: with that
+    of b200c_radius_screen_workspace_bytes (an error where the screened scan does not apply)."""
     lib = _native.cabi()
     n, m, dim = x.shape[0], y.shape[0], x.shape[1]
     nseg = 1 if ptr_x is None else ptr_x.numel() - 1
-    ws, nbytes = _radius_workspace(x, m, dim, max_num_neighbors, one_pass)
+    if screen:
+        nbytes = lib.b200c_radius_screen_workspace_bytes(n, m, dim, max_num_neighbors, _dtype(x), nseg)
+        if nbytes == 0:
+            raise RuntimeError("screened radius scan not applicable")
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    else:
+        ws, nbytes = _radius_workspace(x, m, dim, max_num_neighbors, one_pass)
     counts = radius_counts(x, y, r, ptr_x, ptr_y, max_num_neighbors, ignore_same_index, (ws, nbytes))
     offsets = exclusive_scan(counts)
+    if screen and int(ws[:8].view(torch.long).item()) != 0:
+        raise RuntimeError("a bounded wait of the radius scan ran out")
     total = int(offsets[-1].item())
     out = torch.empty(2, total, dtype=torch.long, device=x.device)
     _native.check(lib.b200c_radius_fill(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, float(r),

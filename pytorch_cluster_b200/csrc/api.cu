@@ -271,6 +271,12 @@ extern "C" size_t b200c_radius_workspace_bytes(int64_t n, int64_t m, int64_t dim
   return radius_direct_bytes(m, dim, max_num_neighbors);
 }
 
+extern "C" size_t b200c_radius_screen_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t max_num_neighbors,
+                                                      int dtype, int64_t num_segments) {
+  if (dtype != B200C_F32 || dim < 1 || dim > 8 || n < 0 || m < 0) return 0;
+  return radius_screen_workspace_bytes(n, m, (int)dim, max_num_neighbors, num_segments);
+}
+
 static int radius_common(const void *x, const void *y, const int64_t *ptr_x, const int64_t *ptr_y,
                          int64_t num_segments, int64_t n, int64_t m, int64_t dim, double r,
                          int64_t max_num_neighbors, int ignore_same_index, int dtype, int32_t *counts,
@@ -294,6 +300,16 @@ static int radius_common(const void *x, const void *y, const int64_t *ptr_x, con
                  ignore_same_index, counts, offsets, out_row, out_col, nullptr, stream};
     a.query_base = query_base;
     return dtype == B200C_F16 ? launch_radius_generic_f16(a, fill) : launch_radius_generic_bf16(a, fill);
+  }
+  if (dtype == B200C_F32 && dim <= 8 && workspace != nullptr) {
+    // the screened scan, when the workspace has room for its chunk arrays (the same decision in both passes)
+    const size_t need = radius_screen_workspace_bytes(n, m, (int)dim, max_num_neighbors, num_segments);
+    if (need > 0 && workspace_bytes >= need) {
+      RadiusArgs a{x, y, ptr_x, ptr_y, (int)num_segments, n, m, (int)dim, r, max_num_neighbors,
+                   ignore_same_index, counts, offsets, out_row, out_col, nullptr, stream};
+      a.query_base = query_base;
+      return launch_radius_screen_f32(a, fill, workspace);
+    }
   }
   const size_t direct_bytes = radius_direct_bytes(m, dim, max_num_neighbors);
   int32_t *direct = (direct_bytes > 0 && workspace != nullptr && workspace_bytes >= direct_bytes)

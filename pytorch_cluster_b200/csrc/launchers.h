@@ -54,6 +54,9 @@ int launch_knn_lowd_f32(const KnnArgs &a);
 int launch_knn_lowd_f64(const KnnArgs &a);
 int launch_radius_lowd_f32(const RadiusArgs &a, bool fill);
 int launch_radius_lowd_f64(const RadiusArgs &a, bool fill);
+// Screened scan for fp32 points of up to 8 features (radius_screen.cuh): workspace (0: not applicable), both passes.
+size_t radius_screen_workspace_bytes(int64_t n, int64_t m, int dim, int64_t max_nn, int64_t num_segments);
+int launch_radius_screen_f32(const RadiusArgs &a, bool fill, void *workspace);
 int radius_lowd_chunk_points(int dim, int dtype);  // points per chunk of the low-dimensional scan: 32 x (mask words per chunk)
 int launch_knn_generic_f32(const KnnArgs &a);
 int launch_knn_generic_f64(const KnnArgs &a);

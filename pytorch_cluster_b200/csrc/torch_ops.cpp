@@ -5,6 +5,7 @@
 // caching allocator, the caller's current stream, and one device-to-host read of the edge
 // count where the output size depends on the data.  There is no CPU branch: a CPU tensor is an
 // error here, not a fallback.
+#include <algorithm>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <ATen/cuda/CUDAEvent.h>
@@ -248,7 +249,14 @@ torch::Tensor radius_part(torch::Tensor x, torch::Tensor y, std::optional<torch:
   // a bit matrix from which the edges are written afterwards.  The matrix's size depends on the segment
   // sizes, so the segment pointers are read to the host (a second small sync of this call).  Pointers
   // that do not describe x and y exactly make the size query answer 0 and take the route below.
-  if (max_num_neighbors > kRadiusDirectCap && dim <= 8 && (p.dtype == B200C_F32 || p.dtype == B200C_F64)) {
+  // The screened scan pays when hits are sparse.  A query keeps at most max_num_neighbors of them, so with
+  // segments of 2048 * max_num_neighbors points on average at most one (query, chunk of 256 points) pair in
+  // eight can hold one: known from the sizes alone.
+  const bool sparse_for_sure = max_num_neighbors <= (1 << 20) && n / p.num_segments >= 2048 * max_num_neighbors;
+  const size_t screen_bytes =
+      sparse_for_sure ? b200c_radius_screen_workspace_bytes(n, m, dim, max_num_neighbors, p.dtype, p.num_segments) : 0;
+  if (screen_bytes == 0 && max_num_neighbors > kRadiusDirectCap && dim <= 8 &&
+      (p.dtype == B200C_F32 || p.dtype == B200C_F64)) {
     torch::Tensor hx, hy;
     const int64_t *hpx = nullptr, *hpy = nullptr;
     if (p.px != nullptr) {
@@ -276,7 +284,7 @@ torch::Tensor radius_part(torch::Tensor x, torch::Tensor y, std::optional<torch:
   }
 
   // small neighbour caps: one scan that also parks the hits, then a copy (see b200_cluster.h)
-  const size_t ws_bytes = b200c_radius_workspace_bytes(n, m, dim, max_num_neighbors, p.dtype);
+  const size_t ws_bytes = std::max(screen_bytes, b200c_radius_workspace_bytes(n, m, dim, max_num_neighbors, p.dtype));
   auto ws = torch::empty({(int64_t)ws_bytes}, x.options().dtype(torch::kByte));
   void *ws_ptr = ws_bytes ? ws.data_ptr() : nullptr;
   check_status(b200c_radius_count_part(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
@@ -284,7 +292,15 @@ torch::Tensor radius_part(torch::Tensor x, torch::Tensor y, std::optional<torch:
                                        counts.data_ptr<int32_t>(), ws_ptr, ws_bytes, stream.stream()));
   check_status(b200c_exclusive_scan(counts.data_ptr<int32_t>(), m, offsets.data_ptr<int64_t>(),
                                     scan_ws.data_ptr(), scan_bytes, stream.stream()));
-  const int64_t total = offsets[m].item<int64_t>();  // the one host sync: the output size
+  int64_t total;
+  if (screen_bytes > 0) {
+    // the output size and the scan's status word (first 8 bytes of its workspace) travel together
+    auto sizes = torch::stack({offsets[m], ws.narrow(0, 0, 8).view(torch::kLong)[0]}).cpu();
+    TORCH_CHECK(sizes[1].item<int64_t>() == 0, "b200_cluster: a bounded wait of the radius scan ran out");
+    total = sizes[0].item<int64_t>();
+  } else {
+    total = offsets[m].item<int64_t>();  // the one host sync: the output size
+  }
   auto out = torch::empty({2, total}, lopts);
   check_status(b200c_radius_fill_part(p.x.data_ptr(), p.y.data_ptr(), p.px, p.py, p.num_segments, n, m, dim, r,
                                       max_num_neighbors, same, query_index_base, swap, p.dtype,
