@@ -67,11 +67,30 @@ struct KnnSpatial {
   static constexpr int QI_KTH = (DIM + 1 + 1) / 2 * 2;
   static constexpr int QI = (QI_KTH + 2 + 3) / 4 * 4;
   static constexpr int QCAP = KP;
-  static constexpr size_t OFF_BAR = (size_t)KS_STAGES * STAGE_BYTES;
-  static constexpr size_t OFF_REC = OFF_BAR + 2 * KS_STAGES * 8;
-  static constexpr size_t OFF_QI = OFF_REC + (size_t)KS_TILE * REC * 4;
-  static constexpr size_t OFF_KEYS = OFF_QI + (size_t)KS_TILE * QI * 4;
-  static constexpr size_t OFF_CNT = OFF_KEYS + (size_t)KS_TILE * (KP + QCAP) * sizeof(K);
+};
+
+// Stages of the ring and thread blocks per SM of a variant.  Short segments (the rolled variant) spend
+// much of their time outside the scan loop — selection code, instruction fetch — and gain more from a
+// fourth resident thread block than from a deeper ring; up to three features that block fits with two
+// stages (53 KB per block) and 56 registers.  Long segments and more features keep four stages and
+// three blocks.  The 64-wide selection is bound by its key arrays to two blocks.
+__host__ __device__ constexpr bool ks_four_blocks(int dim, int kp, bool rolled) { return kp == 32 && rolled && dim <= 3; }
+__host__ __device__ constexpr int ks_stages(int dim, int kp, bool rolled) {
+  return ks_four_blocks(dim, kp, rolled) ? 2 : KS_STAGES;
+}
+__host__ __device__ constexpr int ks_minblocks(int dim, int kp, bool rolled) {
+  return kp == 32 ? (ks_four_blocks(dim, kp, rolled) ? KS_MINBLOCKS + 1 : KS_MINBLOCKS) : 2;
+}
+
+// Shared memory of a thread block: the ring's stages, its mbarriers, then the per-query state.
+template <int DIM, int KP, int STAGES>
+struct KnnSpatialLayout {
+  using Cfg = KnnSpatial<DIM, KP>;
+  static constexpr size_t OFF_BAR = (size_t)STAGES * Cfg::STAGE_BYTES;
+  static constexpr size_t OFF_REC = OFF_BAR + 2 * STAGES * 8;
+  static constexpr size_t OFF_QI = OFF_REC + (size_t)KS_TILE * Cfg::REC * 4;
+  static constexpr size_t OFF_KEYS = OFF_QI + (size_t)KS_TILE * Cfg::QI * 4;
+  static constexpr size_t OFF_CNT = OFF_KEYS + (size_t)KS_TILE * (KP + Cfg::QCAP) * sizeof(Key<float>);
   static constexpr size_t SMEM_BYTES = OFF_CNT + (size_t)KS_TILE * 2 * 4;  // fill, and fill before the chunk
 };
 
@@ -261,20 +280,22 @@ struct KnnSpatialArgs {
 // in the selection code, and the instruction caches then hold it better next to a small scan loop;
 // long segments live in the scan loop and want it unrolled.
 template <int DIM, int KP, bool ROLLED>
-__global__ void __launch_bounds__(KS_THREADS, KP == 32 ? KS_MINBLOCKS : 2)
+__global__ void __launch_bounds__(KS_THREADS, ks_minblocks(DIM, KP, ROLLED))
 knn_spatial_kernel(const KnnSpatialArgs a) {
   using Cfg = KnnSpatial<DIM, KP>;
   using K = Key<float>;
   constexpr int QW = Cfg::QW, REC = Cfg::REC, QI = Cfg::QI;
+  constexpr int STAGES = ks_stages(DIM, KP, ROLLED);
+  using Lay = KnnSpatialLayout<DIM, KP, STAGES>;
 
   extern __shared__ __align__(128) unsigned char ks_smem_raw[];
   float *stages = reinterpret_cast<float *>(ks_smem_raw);
-  uint64_t *full = reinterpret_cast<uint64_t *>(ks_smem_raw + Cfg::OFF_BAR);
-  uint64_t *empty = full + KS_STAGES;
-  float *recs = reinterpret_cast<float *>(ks_smem_raw + Cfg::OFF_REC);
-  float *qinfos = reinterpret_cast<float *>(ks_smem_raw + Cfg::OFF_QI);
-  K *keys_all = reinterpret_cast<K *>(ks_smem_raw + Cfg::OFF_KEYS);
-  int *cnt_all = reinterpret_cast<int *>(ks_smem_raw + Cfg::OFF_CNT);
+  uint64_t *full = reinterpret_cast<uint64_t *>(ks_smem_raw + Lay::OFF_BAR);
+  uint64_t *empty = full + STAGES;
+  float *recs = reinterpret_cast<float *>(ks_smem_raw + Lay::OFF_REC);
+  float *qinfos = reinterpret_cast<float *>(ks_smem_raw + Lay::OFF_QI);
+  K *keys_all = reinterpret_cast<K *>(ks_smem_raw + Lay::OFF_KEYS);
+  int *cnt_all = reinterpret_cast<int *>(ks_smem_raw + Lay::OFF_CNT);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int segs = a.num_segments;
@@ -375,7 +396,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
 
   // ---- stage ring ----
   if (tid == 0) {
-    for (int s = 0; s < KS_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(ks_smem(full + s)) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ks_smem(empty + s)), "r"(KS_WARPS)
                    : "memory");
@@ -385,7 +406,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
   __syncthreads();
 
   auto issue = [&](int step) {  // thread 0: bulk copies of the chunk of scan step `step`
-    const int slot = step % KS_STAGES;
+    const int slot = step % STAGES;
     const int64_t pos = xs_lo + (int64_t)ks_chunk_at(part + step * parts, seed, nch_all) * SP_CHUNK;
     float *dst = stages + slot * Cfg::STAGE_ELEMS;
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(ks_smem(full + slot)),
@@ -402,7 +423,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
     if (lane == 0) {
       int issued = 0;
       for (int step = 0; step < nch && !failed; ++step) {
-        if (step >= KS_STAGES && !ks_wait(empty + step % KS_STAGES, (unsigned)((step / KS_STAGES - 1) & 1))) {
+        if (step >= STAGES && !ks_wait(empty + step % STAGES, (unsigned)((step / STAGES - 1) & 1))) {
           failed = true;
           break;
         }
@@ -411,8 +432,8 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
       }
       if (failed) {
         // a wait ran out: flag the result as invalid and let the copies already issued land
-        for (int s = issued > KS_STAGES ? issued - KS_STAGES : 0; s < issued; ++s)
-          (void)ks_wait(full + s % KS_STAGES, (unsigned)((s / KS_STAGES) & 1));
+        for (int s = issued > STAGES ? issued - STAGES : 0; s < issued; ++s)
+          (void)ks_wait(full + s % STAGES, (unsigned)((s / STAGES) & 1));
         if (a.graph_out != nullptr)
           atomicAdd(a.graph_irregular, KS_ERROR_IRREGULAR);
         else
@@ -423,8 +444,8 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
   }
 
   for (int step = 0; step < nch; ++step) {
-    const int slot = step % KS_STAGES;
-    if (!ks_wait(full + slot, (unsigned)((step / KS_STAGES) & 1))) {
+    const int slot = step % STAGES;
+    if (!ks_wait(full + slot, (unsigned)((step / STAGES) & 1))) {
       failed = true;
       break;
     }

@@ -6,7 +6,7 @@ namespace b200c {
 
 template <int DIM, int KP, bool ROLLED>
 static int launch_knn_spatial_one(const KnnSpatialArgs &a, int64_t tiles, cudaStream_t stream) {
-  using Cfg = KnnSpatial<DIM, KP>;
+  using Cfg = KnnSpatialLayout<DIM, KP, ks_stages(DIM, KP, ROLLED)>;
   auto kern = knn_spatial_kernel<DIM, KP, ROLLED>;
   static unsigned long long configured = 0ull;  // devices on which the shared-memory opt-in is done
   B200C_CUDA(opt_in_shared_memory(kern, Cfg::SMEM_BYTES, configured));
