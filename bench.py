@@ -564,6 +564,11 @@ def run_only(args):
         x = torch.randn(32768, 64, generator=g).to(dev)
         ptr = torch.arange(0, 32768 + 1, 2048, device=dev)
         fn = lambda: cabi.knn_padded_nosync(x, x, 21, ptr, ptr, args.cosine)
+    elif name == "radius_sparse_small":        # 2 clouds of the large bipartite set, about 15 hits per query: screened scan
+        w = make_knn_bipartite(clouds=2)
+        x, y = w["x"].to(dev), w["y"].to(dev)
+        px, py = seg(w["batch_x"].to(dev), 2), seg(w["batch_y"].to(dev), 2)
+        fn = lambda: cabi.radius(x, y, 3.0, px, py, 32, False, screen=True)
     elif name in ("radius_mixture_small_screen", "radius_mixture_small_screen_large_cap"):
         w = make_radius_mixture(clouds=16)     # 16 of the 64 clouds, the screened scan
         x, ptr = w["x"].to(dev), seg(w["batch"].to(dev), 16)
