@@ -187,6 +187,20 @@ def test_radius_bipartite_full_size(max_nn):
           _reference_radius_per_cloud(x, y, 64, 8192, 2048, 0.05, max_nn, False))
 
 
+@pytest.mark.parametrize("max_nn", [16, 32])
+def test_radius_sparse_hits_full_size(max_nn):
+    """8 clouds of 131072 uniform points, 8192 queries each, about 15 hits per query: segments of at least
+    2048 * max_num_neighbors points, for which the operator takes the screened scan (cap 16 truncates
+    nearly half of the queries, cap 32 almost none)."""
+    g = torch.Generator().manual_seed(3)
+    x = (100 * torch.rand(8 * 131072, 3, generator=g)).to(DEV)
+    y = (100 * torch.rand(8 * 8192, 3, generator=g)).to(DEV)
+    px, py = _ptr(8, 131072), _ptr(8, 8192)
+    ours = _ours_radius(x, y, px, py, 3.0, max_nn, False)
+    _same(ours, refc.radius(x, y, px, py, 3.0, max_nn, False))
+    assert ours.shape[1] > 500_000
+
+
 def test_radius_graph_full_size_truncated():
     """The same 64 clouds with a cap of 64: the surviving hits are the reference's (lowest x rows)."""
     x = _mixture(64, 8192)
