@@ -486,37 +486,42 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
           ks_push<DIM, KP>(s[0].x, s[0].y, s[1].x, s[1].y, s[2].x, s[2].y, s[3].x, s[3].y, buf, rec, my_qi + qi * QI,
                            my_keys + qi * (KP + Cfg::QCAP) + KP, my_cnt + qi);
       };
+      // The loop over the warp's queries only notes — one vote per query — which of them have a point at or
+      // below their threshold in this chunk; those are screened again afterwards with the push attached.  The
+      // loop that does the bulk of the work then holds no call, no convergence bracket and no screen values
+      // that outlive their minimum (long segments: 2.43 -> 2.20 ms on 8 x (131072 points, 8192 queries);
+      // clouds of 4096 / 8192 points: 1.5 % / 5 % faster, of 2048 points 2 % slower).
+      auto note_query = [&](int qi) -> bool {
+        const float *rec = my_recs + qi * REC;
+        float4 rv[REC / 4];
+#pragma unroll
+        for (int i = 0; i < REC / 4; ++i) rv[i] = reinterpret_cast<const float4 *>(rec)[i];
+        const float *f = reinterpret_cast<const float *>(rv);
+        float2 s[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          s[h] = __ffma2_rn(pc[0][h], make_float2(f[0], f[1]), pw[h]);
+#pragma unroll
+          for (int d = 1; d < DIM; ++d) s[h] = __ffma2_rn(pc[d][h], make_float2(f[2 * d], f[2 * d + 1]), s[h]);
+        }
+        const float m0 = fminf(fminf(s[0].x, s[0].y), s[1].x), m1 = fminf(fminf(s[1].y, s[2].x), s[2].y);
+        const float m = fminf(fminf(m0, m1), fminf(s[3].x, s[3].y));
+        return __any_sync(FULL_MASK, m <= f[2 * DIM]) != 0;
+      };
+      unsigned noted = 0u;
       if constexpr (ROLLED) {
 #pragma unroll 1
-        for (int qi = 0; qi < QW; ++qi) screen_query(qi);
+        for (int qi = 0; qi < QW; ++qi)
+          if (note_query(qi)) noted |= 1u << qi;
       } else {
-        // long segments: nearly all (query, chunk) pairs have nothing below the threshold, so the unrolled
-        // loop only notes — one vote per query — which queries have, and those are screened again with
-        // the push attached: no call and no live screen values inside the loop that does the bulk of the work
-        unsigned noted = 0u;
 #pragma unroll
-        for (int qi = 0; qi < QW; ++qi) {
-          const float *rec = my_recs + qi * REC;
-          float4 rv[REC / 4];
-#pragma unroll
-          for (int i = 0; i < REC / 4; ++i) rv[i] = reinterpret_cast<const float4 *>(rec)[i];
-          const float *f = reinterpret_cast<const float *>(rv);
-          float2 s[4];
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            s[h] = __ffma2_rn(pc[0][h], make_float2(f[0], f[1]), pw[h]);
-#pragma unroll
-            for (int d = 1; d < DIM; ++d) s[h] = __ffma2_rn(pc[d][h], make_float2(f[2 * d], f[2 * d + 1]), s[h]);
-          }
-          const float m0 = fminf(fminf(s[0].x, s[0].y), s[1].x), m1 = fminf(fminf(s[1].y, s[2].x), s[2].y);
-          const float m = fminf(fminf(m0, m1), fminf(s[3].x, s[3].y));
-          if (__any_sync(FULL_MASK, m <= f[2 * DIM])) noted |= 1u << qi;
-        }
-        while (noted) {
-          const int qi = __ffs(noted) - 1;
-          noted &= noted - 1u;
-          screen_query(qi);
-        }
+        for (int qi = 0; qi < QW; ++qi)
+          if (note_query(qi)) noted |= 1u << qi;
+      }
+      while (noted) {
+        const int qi = __ffs(noted) - 1;
+        noted &= noted - 1u;
+        screen_query(qi);
       }
       __syncwarp();
       // the queues after this chunk: overflowed ones are rolled back and the chunk offered again by
