@@ -518,6 +518,9 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
         for (int qi = 0; qi < QW; ++qi)
           if (note_query(qi)) noted |= 1u << qi;
       }
+      // no noted query: no queue has changed in this chunk, and long segments (where that is the rule) skip the
+      // look at the queues; on short ones the extra test costs more than it saves (measured: 3 % either way)
+      const bool pushed = ROLLED || noted != 0u;
       while (noted) {
         const int qi = __ffs(noted) - 1;
         noted &= noted - 1u;
@@ -526,10 +529,10 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
       __syncwarp();
       // the queues after this chunk: overflowed ones are rolled back and the chunk offered again by
       // the whole warp; filled ones are merged, which tightens the bound
-      const int fill = lane < QW ? my_cnt[lane] : 0;
+      const int fill = (pushed && lane < QW) ? my_cnt[lane] : 0;
       const int want = step < a.eager_steps ? 1 : a.lazy_fill;
-      unsigned todo = __ballot_sync(FULL_MASK, fill >= want);
-      const unsigned over = __ballot_sync(FULL_MASK, fill > Cfg::QCAP);
+      unsigned todo = pushed ? __ballot_sync(FULL_MASK, fill >= want) : 0u;
+      const unsigned over = pushed ? __ballot_sync(FULL_MASK, fill > Cfg::QCAP) : 0u;
       while (todo) {
         const int qi = __ffs(todo) - 1;
         todo &= todo - 1u;
@@ -544,7 +547,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
           ks_update_bound<DIM, KP>(keys, my_recs + qi * REC, my_qi + qi * QI, wmax, a.k, lane);
         }
       }
-      if (lane < QW) my_mark[lane] = my_cnt[lane];
+      if (pushed && lane < QW) my_mark[lane] = my_cnt[lane];
     } else {
       for (int qi = 0; qi < QW; ++qi)
         if ((valid_mask >> qi) & 1u)
