@@ -581,19 +581,23 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
     }
     return;
   }
+  // A loop, and the last merge through the shared copy of the network: the kernel's code stays small
+  // (with this loop unrolled and the merges inline, eight more copies of the network, the scan of
+  // clouds of 4096 points took 0.544 ms instead of 0.471 ms — instruction fetch).
   int my_valid = 0, my_irregular = 0;
-#pragma unroll
+#pragma unroll 1
   for (int qi = 0; qi < QW; ++qi) {
     const int64_t q = __shfl_sync(FULL_MASK, my_row, qi);
     if (q < 0) continue;  // warp-uniform
     K *keys = my_keys + qi * (KP + Cfg::QCAP);
+    if (my_cnt[qi] > 0) ks_merge<KP>(keys, my_cnt[qi], a.k);
     if (a.graph_out != nullptr) {
-      if (!knn_finish_graph<float, KP>(keys, my_cnt[qi], a.k, q, a.graph_row_stride, a.graph_index_base, a.graph_out,
+      if (!knn_finish_graph<float, KP>(keys, 0, a.k, q, a.graph_row_stride, a.graph_index_base, a.graph_out,
                                        a.graph_s2t != 0, lane))
         ++my_irregular;
       continue;
     }
-    const int valid = knn_finish<float, KP>(keys, my_cnt[qi], a.k, q, a.out_row, a.out_col, lane);
+    const int valid = knn_finish<float, KP>(keys, 0, a.k, q, a.out_row, a.out_col, lane);
     if (lane == 0) {
       a.counts[q] = valid;
       my_valid += valid;
