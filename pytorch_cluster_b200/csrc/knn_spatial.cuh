@@ -276,9 +276,12 @@ struct KnnSpatialArgs {
   Key<float> *part_keys;
 };
 
-// ROLLED: the loop over a warp's eight queries stays a loop.  Short segments spend much of their time
-// in the selection code, and the instruction caches then hold it better next to a small scan loop;
-// long segments live in the scan loop and want it unrolled.
+// ROLLED: the loop over a warp's eight queries stays a loop; up to three features that variant also runs
+// with two ring stages and four thread blocks per SM (ks_four_blocks).  Short segments spend much of their
+// time in the selection code and gain from the extra resident warps; long segments live in the scan loop and
+// want it unrolled.  Instruction fetch is this kernel's largest stall on short segments, so code size matters
+// throughout: the merge network, the push and the chunk offer exist once (noinline), and loops over the
+// warp's queries outside the scan stay rolled.
 template <int DIM, int KP, bool ROLLED>
 __global__ void __launch_bounds__(KS_THREADS, ks_minblocks(DIM, KP, ROLLED))
 knn_spatial_kernel(const KnnSpatialArgs a) {
@@ -367,7 +370,7 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
   }
   const unsigned valid_mask = __ballot_sync(FULL_MASK, lane < QW && my_row >= 0);
   if (!producer) {
-#pragma unroll
+#pragma unroll 1
     for (int qi = 0; qi < QW; ++qi) knn_reset<float, KP>(my_keys + qi * (KP + Cfg::QCAP), lane);
   }
 

@@ -130,10 +130,10 @@ int launch_knn_spatial_f32(const KnnArgs &a, void *workspace, int64_t max_segmen
   s.graph_irregular = a.graph_irregular;
   s.eager_steps = 1;
   s.lazy_fill = a.k <= 32 ? 16 : 32;
-  // segments of up to 64 chunks on average count as short (the kernel variant with the rolled query loop)
-  // rolled variant up to 32 chunks per segment on average (measured on 3-D clouds, k = 21 and 32: 0.705 against
-  // 0.720 ms at 8192 points per cloud, 1.058 against 0.975 ms at 16384)
-  const bool short_segments = a.n / a.num_segments <= 32 * SP_CHUNK;
+  // rolled variant up to 16 chunks per segment on average (measured on 3-D clouds, k = 21: 0.378 against 0.402 ms
+  // at 2048 points per cloud, 0.471 against 0.485 ms at 4096, 0.627 against 0.619 ms at 8192, 0.937 against
+  // 0.898 ms at 16384)
+  const bool short_segments = a.n / a.num_segments <= 16 * SP_CHUNK;
   const int64_t tiles = padded_queries / KS_TILE;  // an upper bound: blocks past the last segment leave at once
   if (g_scan_timing) B200C_CUDA(cudaEventRecord(g_scan_begin, a.stream));
   set_error("Morton-ordered kNN called with dim=%d", a.dim);
