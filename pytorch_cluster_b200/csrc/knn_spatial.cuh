@@ -40,8 +40,8 @@
 namespace b200c {
 
 constexpr int KS_STAGES = 4;
-constexpr int KS_SPIN_LIMIT = 1 << 14;      // polls of a wait; each may sleep up to KS_WAIT_NS
-constexpr unsigned KS_WAIT_NS = 100000u;    // suspend-time hint of one poll (about 1.6 s in all)
+constexpr int KS_SPIN_LIMIT = 1 << 26;      // polls of a wait (about a second: see ks_wait)
+constexpr unsigned KS_WAIT_NS = 20000u;     // suspend-time hint of one poll
 constexpr int KS_WARPS = WARPS_PER_CTA;          // scanning warps per thread block
 constexpr int KS_MINBLOCKS = 3;                  // thread blocks per SM the register budget is set for
 constexpr int KS_TILE = 8 * KS_WARPS;            // queries per thread block
@@ -96,6 +96,12 @@ struct KnnSpatialLayout {
 
 __device__ __forceinline__ unsigned ks_smem(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 
+// Waits for a phase of an mbarrier with a bounded number of polls.  A poll returns within about ten
+// nanoseconds whatever its suspend-time hint (measured: some 14000 polls per thread block of the headline
+// workload, which lives 130 us), so 2^26 polls are about a second.  A bound in cycles (clock64 every 256 polls)
+// made the scans 2 % slower — the wait is inlined in the scan loop — and so did 128 ns of sleep between the
+// polls of the copy warp, which waits nearly all the time (a stage is refilled later; the issue slots its
+// spinning takes cost less).
 __device__ __forceinline__ bool ks_wait(uint64_t *bar, unsigned parity) {
   unsigned done = 0;
   for (int it = 0; it < KS_SPIN_LIMIT && !done; ++it) {
