@@ -217,22 +217,41 @@ __device__ __noinline__ void ks_offer_chunk(const float *buf, float *rec, float 
   const int32_t *idx_plane = reinterpret_cast<const int32_t *>(buf + Cfg::P_IDX * SP_CHUNK);
   uint64_t kth = *reinterpret_cast<const uint64_t *>(qinfo + Cfg::QI_KTH);
   int cnt = *cnt_s;
-  K cand[8];
-  K lane_min = K::empty();
+  // the lane's two runs of four consecutive points: one 16-byte load per array and run
+  float qv[DIM];
 #pragma unroll
-  for (int r = 0; r < 8; ++r) {
-    const int slot = ks_slot(lane, r);
-    const int32_t idx = idx_plane[slot];
-    // d < 1e10 is the reference's admission test (false for NaN, whatever its sign bit)
-    const float d = ks_exact<DIM, KP>(buf, slot, qinfo);
-    cand[r] = (idx >= 0 && d < 1e10f) ? K::make(d, (uint32_t)idx) : K::empty();
-    lane_min = key_min(lane_min, cand[r]);
+  for (int d = 0; d < DIM; ++d) qv[d] = qinfo[d];
+  K cand[8];
+  uint32_t lane_min_word = 0xffffffffu;  // smallest distance word of the lane's candidates
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < DIM; ++d) {
+      const float4 o = *reinterpret_cast<const float4 *>(buf + (Cfg::P_ORG + d) * SP_CHUNK + h * 128 + 4 * lane);
+      const float ov[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float diff = __fsub_rn(ov[j], qv[d]);
+        acc[j] = __fmaf_rn(diff, diff, acc[j]);
+      }
+    }
+    const int4 id4 = *reinterpret_cast<const int4 *>(idx_plane + h * 128 + 4 * lane);
+    const int32_t id[4] = {id4.x, id4.y, id4.z, id4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      // d < 1e10 is the reference's admission test (false for NaN, whatever its sign bit)
+      const K c = (id[j] >= 0 && acc[j] < 1e10f) ? K::make(acc[j], (uint32_t)id[j]) : K::empty();
+      cand[4 * h + j] = c;
+      const uint32_t word = (uint32_t)(c.v >> 32);
+      lane_min_word = word < lane_min_word ? word : lane_min_word;
+    }
   }
   // Nothing known yet and far more candidates than the queue holds: the k-th smallest of the 32
   // lane minima is an upper bound of the k-th smallest key overall, so it filters first.
   if (KP == 32 && kth == ks_no_bound().v) {
     // non-negative floats order like their bit patterns; an empty key's distance word sorts last
-    const uint32_t cap = __shfl_sync(FULL_MASK, warp_sort32_u32((uint32_t)(lane_min.v >> 32), lane), k - 1);
+    const uint32_t cap = __shfl_sync(FULL_MASK, warp_sort32_u32(lane_min_word, lane), k - 1);
     // every key with a distance word <= cap; fewer than k lanes with a candidate give an empty cap
     const uint64_t below = cap == 0xffffffffu ? ~0ull : ((uint64_t)cap + 1u) << 32;
     if (below < kth) kth = below;
