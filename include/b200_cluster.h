@@ -124,7 +124,10 @@ int b200c_exclusive_scan_static(const int32_t *counts, int64_t m, int64_t *offse
  * n and m are taken).  It only limits how many sorting passes the Morton-ordered path enqueues.
  *
  * The Morton-ordered path moves its chunks with bulk asynchronous copies whose waits are
- * bounded; if one ever runs out, 2^62 is added to *num_valid and the output is not valid. */
+ * bounded; if one ever runs out, 2^62 is added to *num_valid and the output is not valid.  The same
+ * happens for segment pointers that overlap (segment sizes that add up to more than the rows): the
+ * sorted copies are sized for a partition of the rows, so the pass leaves them empty and flags the call —
+ * search such inputs without the workspace. */
 size_t b200c_knn_workspace_bytes(int64_t n, int64_t m, int64_t dim, int64_t k,
                                  int dtype, int cosine, int64_t num_segments);
 int b200c_knn(const void *x, const void *y, const int64_t *ptr_x,
@@ -198,7 +201,7 @@ int b200c_knn_graph_tail_write(const int64_t *edge_padded, const int32_t *counts
  *
  * workspace (optional): b200c_knn_graph_workspace_bytes(...) bytes enable the scan over a
  * Morton-ordered copy of x for fp32 (see b200c_knn; max_segment_rows as there).  Should one of
- * that path's bounded waits run out, 2^30 is added to *irregular. */
+ * that path's bounded waits run out, or the segments overlap, 2^30 is added to *irregular. */
 size_t b200c_knn_graph_workspace_bytes(int64_t n, int64_t dim, int64_t k, int dtype,
                                        int64_t num_segments);
 int b200c_knn_graph(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n,
@@ -252,8 +255,9 @@ size_t b200c_radius_workspace_bytes(int64_t n, int64_t m, int64_t dim,
  * (a query keeps at most max_num_neighbors hits), which is the rule torch_cluster::radius applies.
  * Pass 1 parks the hits (up to 64 per query for neighbour caps above 256), pass 2 copies them and scans
  * again only for queries that found more than were parked.  After pass 1 the first 8 bytes of the
- * workspace are a status word (int64): non-zero means that a bounded wait inside the scan ran out and the
- * counts are invalid; read it together with the total of the counts before sizing the output. */
+ * workspace are a status word (int64): non-zero means that a bounded wait inside the scan ran out (1),
+ * or that the segments of x overlap so far that their chunk arrays do not fit (2), and the counts are
+ * invalid; read it together with the total of the counts before sizing the output. */
 size_t b200c_radius_screen_workspace_bytes(int64_t n, int64_t m, int64_t dim,
                                            int64_t max_num_neighbors, int dtype,
                                            int64_t num_segments);

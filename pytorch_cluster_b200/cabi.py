@@ -112,7 +112,7 @@ def radius(x, y, r, ptr_x=None, ptr_y=None, max_num_neighbors=32, ignore_same_in
     counts = radius_counts(x, y, r, ptr_x, ptr_y, max_num_neighbors, ignore_same_index, (ws, nbytes))
     offsets = exclusive_scan(counts)
     if screen and int(ws[:8].view(torch.long).item()) != 0:
-        raise RuntimeError("a bounded wait of the radius scan ran out")
+        raise RuntimeError("the radius scan was abandoned (a bounded wait ran out, or segment pointers that overlap)")
     total = int(offsets[-1].item())
     out = torch.empty(2, total, dtype=torch.long, device=x.device)
     _native.check(lib.b200c_radius_fill(_p(x), _p(y), _p(ptr_x), _p(ptr_y), nseg, n, m, dim, float(r),

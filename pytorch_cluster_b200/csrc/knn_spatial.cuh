@@ -332,6 +332,13 @@ knn_spatial_kernel(const KnnSpatialArgs a) {
   // list for knn_spatial_merge_kernel.
   const int parts = a.parts, part = (int)(blockIdx.x % (unsigned)parts);
   const int64_t pos0 = (int64_t)(blockIdx.x / (unsigned)parts) * KS_TILE;  // first padded query position of this tile
+  if (blockIdx.x == 0 && tid == 0 && (*a.xv.bad != 0 || *a.yv.bad != 0)) {
+    // segment pointers that overlap: the ordering pass left its layout empty; the result is flagged invalid
+    if (a.graph_out != nullptr)
+      atomicAdd(a.graph_irregular, KS_ERROR_IRREGULAR);
+    else
+      atomicAdd(a.num_valid, KS_ERROR_COUNT);
+  }
   if (pos0 >= a.yv.sptr[segs]) return;
   int b;
   {

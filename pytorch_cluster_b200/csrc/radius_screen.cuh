@@ -34,11 +34,12 @@
 namespace b200c {
 
 constexpr int64_t RS_ERROR_WAIT = 1;              // *status when a bounded wait ran out
+constexpr int64_t RS_ERROR_OVERLAP = 2;           // *status when the segment pointers of x overlap
 enum RadiusScreenMode { RS_PASS_COUNT = 0, RS_PASS_FILL = 1 };
 
 // Pieces of the workspace (radius_screen_carve); status comes first so that a caller can read it.
 struct RadiusScreenView {
-  int64_t *status;  // [1] 0, or RS_ERROR_WAIT
+  int64_t *status;  // [1] 0, RS_ERROR_WAIT or RS_ERROR_OVERLAP
   int64_t *sptr;    // [B + 1] first padded position of every segment of x
   uint32_t *stat;   // [B] largest w of the segment (bits of a non-negative float; +inf: no screen)
   float *blob;      // [cap / 256][2 dim + 2][256]
@@ -103,14 +104,17 @@ rs_layout_kernel(const int64_t *__restrict__ ptr_x, int segs, int64_t n, RadiusS
     run[t] += add;
     __syncthreads();
   }
+  // Overlapping segments (pointers that are not a partition of the rows) would not fit the arrays sized for
+  // n rows: their padded sizes then add up to more than the capacity.  The layout is left empty and flagged.
+  const bool overlap = run[1023] > v.cap;
   int64_t at = run[t] - mine;
   for (int b = lo; b < hi; ++b) {
-    v.sptr[b] = at;
+    v.sptr[b] = overlap ? 0 : at;
     at += padded(b);
   }
-  if (t == 1023) v.sptr[segs] = run[t];
+  if (t == 1023) v.sptr[segs] = overlap ? 0 : run[t];
   for (int i = t; i < segs; i += 1024) v.stat[i] = 0u;
-  if (t == 0) *v.status = 0;
+  if (t == 0) *v.status = overlap ? RS_ERROR_OVERLAP : 0;
 }
 
 // One thread block per chunk of the padded layout: the chunk's arrays, and the segment's largest w.

@@ -49,6 +49,7 @@ size_t spatial_view_carve(SpatialView *v, void *workspace, int64_t rows, int dim
   t.table_cap = rows / SP_BUCKET_TARGET + rows / SP_SORT_BLOCK + 2 * large_blocks + 8;
   t.table = (int32_t *)take((size_t)t.table_cap * 4 * 4);
   t.table_count = (int32_t *)take(4);
+  t.bad = (int32_t *)take(4);
   if (v) *v = t;
   return off;
 }
@@ -140,13 +141,14 @@ __global__ void __launch_bounds__(SP_THREADS)
 sp_layout_kernel(const int64_t *__restrict__ ptr, int segs, int64_t rows, int64_t small_cap, int dim,
                  int64_t *__restrict__ sptr, int64_t *__restrict__ pptr, int64_t *__restrict__ lptr,
                  float *__restrict__ box, uint32_t *__restrict__ stat, int reset_box,
-                 int32_t *__restrict__ table_count) {
-  __shared__ int64_t run[3][SP_THREADS];
+                 int32_t *__restrict__ table_count, int32_t *__restrict__ bad) {
+  __shared__ int64_t run[4][SP_THREADS];
   const int t = threadIdx.x;
   if (t == 0) *table_count = 0;
   const int per = (segs + SP_THREADS - 1) / SP_THREADS;
   const int lo = t * per < segs ? t * per : segs;
   const int hi = lo + per < segs ? lo + per : segs;
+  int64_t s3 = 0;  // rows of this thread's segments: the sizes of segments that do not overlap add up to <= rows
   auto sizes = [&](int b, int64_t &padded, int64_t &small, int64_t &large) {
     int64_t a, e;
     seg_rows_clamped(ptr, rows, b, a, e);
@@ -163,23 +165,42 @@ sp_layout_kernel(const int64_t *__restrict__ ptr, int segs, int64_t rows, int64_
     s0 += p;
     s1 += s;
     s2 += l;
+    int64_t a, e;
+    seg_rows_clamped(ptr, rows, b, a, e);
+    s3 += e - a;
   }
   run[0][t] = s0;
   run[1][t] = s1;
   run[2][t] = s2;
+  run[3][t] = s3;
   __syncthreads();
   for (int o = 1; o < SP_THREADS; o <<= 1) {
-    int64_t a0 = 0, a1 = 0, a2 = 0;
+    int64_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
     if (t >= o) {
       a0 = run[0][t - o];
       a1 = run[1][t - o];
       a2 = run[2][t - o];
+      a3 = run[3][t - o];
     }
     __syncthreads();
     run[0][t] += a0;
     run[1][t] += a1;
     run[2][t] += a2;
+    run[3][t] += a3;
     __syncthreads();
+  }
+  // Overlapping segments (pointers that are not a partition of the rows) would not fit the arrays sized for
+  // `rows` rows: the layout is left empty — every kernel after this one finds nothing to do — and flagged.
+  const bool overlap = run[3][SP_THREADS - 1] > rows;
+  if (t == 0) *bad = overlap ? 1 : 0;
+  if (overlap) {
+    for (int b = t; b <= segs; b += SP_THREADS) {
+      sptr[b] = 0;
+      pptr[b] = 0;
+      lptr[b] = 0;
+    }
+    for (int i = t; i < segs * 2; i += SP_THREADS) stat[i] = 0u;
+    return;
   }
   int64_t r0 = run[0][t] - s0, r1 = run[1][t] - s1, r2 = run[2][t] - s2;
   for (int b = lo; b < hi; ++b) {
@@ -381,6 +402,7 @@ template <int DIM>
 __global__ void __launch_bounds__(SP_THREADS)
 sp_small_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, int segs, int64_t rows,
                 const float *__restrict__ box_from, int points, SpatialView v) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   extern __shared__ __align__(16) unsigned char sp_smem[];
   uint64_t *pairs = reinterpret_cast<uint64_t *>(sp_smem);
   __shared__ float red[2 * SP_MAX_DIM][32];
@@ -474,6 +496,7 @@ __device__ __forceinline__ bool large_segment(const SpatialView &v, int b) { ret
 template <int DIM>
 __global__ void __launch_bounds__(SP_THREADS)
 sp_box_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   __shared__ float red[2 * SP_MAX_DIM][32];
   const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (!large_segment(v, b)) return;
@@ -521,6 +544,7 @@ template <int DIM>
 __global__ void __launch_bounds__(SP_THREADS)
 sp_keys_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, int64_t rows,
                const float *__restrict__ box, SpatialView v) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   const int b = blockIdx.y;
   if (!large_segment(v, b)) return;
   int64_t x_lo, x_hi;
@@ -558,6 +582,7 @@ __device__ __forceinline__ int segment_of_block(const int64_t *__restrict__ lptr
 // size > SP_SORT_BLOCK: the block-local tail (strides below SP_SORT_BLOCK) of the merge of that size.
 __global__ void __launch_bounds__(SP_THREADS)
 sp_sort_block_kernel(SpatialView v, int segs, int64_t size) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   extern __shared__ __align__(16) unsigned char sp_smem[];
   uint64_t *a = reinterpret_cast<uint64_t *>(sp_smem);
   const int64_t j = blockIdx.x;
@@ -581,6 +606,7 @@ sp_sort_block_kernel(SpatialView v, int segs, int64_t size) {
 
 // One exchange step (stride >= SP_SORT_BLOCK) of the merge of `size` over all large segments.
 __global__ void sp_sort_global_kernel(SpatialView v, int segs, int64_t size, int64_t stride) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // exchange number over the large region
   const int64_t total = v.lptr[segs] * (SP_SORT_BLOCK / 2);
   if (t >= total) return;
@@ -602,6 +628,7 @@ template <int DIM>
 __global__ void __launch_bounds__(SP_THREADS)
 sp_emit_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, int64_t rows,
                const float *__restrict__ box, int points, SpatialView v) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   __shared__ float red[32];
   const int b = blockIdx.y;
   if (!large_segment(v, b)) return;
@@ -652,6 +679,7 @@ __device__ __forceinline__ int bucket_of(const uint64_t *split_s, int nsplit, ui
 
 __global__ void __launch_bounds__(SP_THREADS)
 sp_sample_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   extern __shared__ __align__(16) unsigned char sp_smem[];
   uint64_t *a = reinterpret_cast<uint64_t *>(sp_smem);
   const int b = blockIdx.x, tid = threadIdx.x;
@@ -681,6 +709,7 @@ sp_sample_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
 
 __global__ void __launch_bounds__(SP_THREADS)
 sp_count_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   __shared__ uint64_t split_s[SP_MAX_BUCKETS];
   __shared__ int hist[SP_MAX_BUCKETS];
   const int b = blockIdx.y, tid = threadIdx.x;
@@ -705,6 +734,7 @@ sp_count_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
 // One block per segment: bucket offsets, scatter cursors, and the segment's entries of the bucket table.
 __global__ void __launch_bounds__(SP_MAX_BUCKETS)
 sp_offsets_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   __shared__ int scan[SP_MAX_BUCKETS], entries[SP_MAX_BUCKETS];
   __shared__ int table_base;
   const int b = blockIdx.x, t = threadIdx.x;
@@ -749,6 +779,7 @@ sp_offsets_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) 
 // them within their buckets in shared memory, reserves a range of every bucket, then writes.
 __global__ void __launch_bounds__(SP_THREADS)
 sp_scatter_kernel(const int64_t *__restrict__ ptr, int64_t rows, SpatialView v) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   __shared__ uint64_t split_s[SP_MAX_BUCKETS];
   __shared__ int hist[SP_MAX_BUCKETS], base[SP_MAX_BUCKETS];
   constexpr int PER = 4;
@@ -792,6 +823,7 @@ template <int DIM>
 __global__ void __launch_bounds__(SP_THREADS)
 sp_bucket_sort_kernel(const float *__restrict__ pts, const int64_t *__restrict__ ptr, int64_t rows,
                       const float *__restrict__ box, int points, SpatialView v) {
+  if (*v.bad) return;  // overlapping segments: see sp_layout_kernel
   extern __shared__ __align__(16) unsigned char sp_smem[];
   uint64_t *a = reinterpret_cast<uint64_t *>(sp_smem);
   __shared__ float red[32];
@@ -839,7 +871,7 @@ static int spatial_sort_dim(const float *pts, const int64_t *ptr, int64_t segs, 
   static unsigned long long done_small = 0ull, done_block = 0ull;
   B200C_CUDA(opt_in_shared_memory(sp_small_kernel<DIM>, sort_smem, done_small));
   sp_layout_kernel<<<1, SP_THREADS, 0, stream>>>(ptr, (int)segs, rows, pairs_small_cap(rows), DIM, v->sptr, v->pptr,
-                                                 v->lptr, v->box, v->stat, box_from == nullptr ? 1 : 0, v->table_count);
+                                                 v->lptr, v->box, v->stat, box_from == nullptr ? 1 : 0, v->table_count, v->bad);
   B200C_LAUNCH_CHECK("sp_layout_kernel");
   sp_small_kernel<DIM><<<(unsigned)segs, SP_THREADS, sort_smem, stream>>>(pts, ptr, (int)segs, rows, box_from,
                                                                            points ? 1 : 0, *v);

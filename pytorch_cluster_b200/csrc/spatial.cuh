@@ -55,6 +55,8 @@ struct SpatialView {
   int32_t *bcursor;     // [large_blocks][SP_MAX_BUCKETS]
   int32_t *table;       // [table_cap][4]: segment, first position in the segment, size, last-of-segment flag
   int32_t *table_count; // [1]
+  int32_t *bad;         // [1] non-zero: the segment pointers overlap (their sizes add up to more than the rows);
+                        //     the layout is then empty and the scan flags its result
   int64_t table_cap;
 };
 

@@ -135,7 +135,7 @@ torch::Tensor knn_hinted(torch::Tensor x, torch::Tensor y, std::optional<torch::
                          num_valid.data_ptr<int64_t>(), max_segment_rows, ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
                          stream.stream()));
   const int64_t total = num_valid.item<int64_t>();  // the one host sync: the output size
-  TORCH_CHECK(total < kKnnWaitError, "b200_cluster: a bounded wait of the kNN scan ran out");
+  TORCH_CHECK(total < kKnnWaitError, "b200_cluster: the kNN scan was abandoned (a bounded wait ran out, or segment pointers that overlap)");
   if (total == m * k) return padded;
 
   // some query had fewer than k admissible points: drop the -1 slots
@@ -189,7 +189,7 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
                                  out.data_ptr<int64_t>(), irregular.data_ptr<int32_t>(), max_segment_rows,
                                  gws_bytes ? gws.data_ptr() : nullptr, gws_bytes, stream.stream()));
     const int32_t odd = irregular.item<int32_t>();  // the one host sync
-    TORCH_CHECK(odd < kGraphWaitError, "b200_cluster: a bounded wait of the kNN scan ran out");
+    TORCH_CHECK(odd < kGraphWaitError, "b200_cluster: the kNN scan was abandoned (a bounded wait ran out, or segment pointers that overlap)");
     if (odd == 0) return out;
   }
 
@@ -213,7 +213,7 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
   // the output size and the search's own count travel together: one host sync
   auto sizes = torch::stack({offsets[n], num_valid[0]}).cpu();
   const int64_t total = sizes[0].item<int64_t>();
-  TORCH_CHECK(sizes[1].item<int64_t>() < kKnnWaitError, "b200_cluster: a bounded wait of the kNN scan ran out");
+  TORCH_CHECK(sizes[1].item<int64_t>() < kKnnWaitError, "b200_cluster: the kNN scan was abandoned (a bounded wait ran out, or segment pointers that overlap)");
   auto out = torch::empty({2, total}, lopts);
   check_status(b200c_knn_graph_tail_write(padded.data_ptr<int64_t>(), counts.data_ptr<int32_t>(),
                                           offsets.data_ptr<int64_t>(), n, k1, loop ? 0 : 1,
@@ -296,7 +296,7 @@ torch::Tensor radius_part(torch::Tensor x, torch::Tensor y, std::optional<torch:
   if (screen_bytes > 0) {
     // the output size and the scan's status word (first 8 bytes of its workspace) travel together
     auto sizes = torch::stack({offsets[m], ws.narrow(0, 0, 8).view(torch::kLong)[0]}).cpu();
-    TORCH_CHECK(sizes[1].item<int64_t>() == 0, "b200_cluster: a bounded wait of the radius scan ran out");
+    TORCH_CHECK(sizes[1].item<int64_t>() == 0, "b200_cluster: the radius scan was abandoned (a bounded wait ran out, or segment pointers that overlap)");
     total = sizes[0].item<int64_t>();
   } else {
     total = offsets[m].item<int64_t>();  // the one host sync: the output size
@@ -603,7 +603,7 @@ int64_t knn_graph_host(torch::Tensor x, torch::Tensor ptr, int64_t k, bool sourc
   for (auto &s : streams) s.synchronize();
   int64_t irregular = 0;
   for (int64_t g = 0; g < groups; ++g) irregular += flags_host[g];
-  TORCH_CHECK(irregular < kGraphWaitError, "b200_cluster: a bounded wait of the kNN scan ran out");
+  TORCH_CHECK(irregular < kGraphWaitError, "b200_cluster: the kNN scan was abandoned (a bounded wait ran out, or segment pointers that overlap)");
   return irregular;
 }
 

@@ -132,3 +132,18 @@ def test_through_the_operators():
     want = whole[:, keep].flip(0).clone()
     want[1] -= 2000
     assert torch.equal(part, want)
+
+
+def test_overlapping_segments_are_refused_not_overrun():
+    """Segments of x that overlap so far that their chunk arrays would not fit the workspace: the layout is left empty
+    and the status word says so; nothing is written out of bounds."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.rand(6000, 3, generator=g).to(DEV)
+    y = torch.rand(300, 3, generator=g).to(DEV)
+    px = torch.tensor([0, 6000, 0, 6000], device=DEV)  # the whole set twice
+    py = torch.tensor([0, 100, 200, 300], device=DEV)
+    with pytest.raises(RuntimeError, match="overlap"):
+        _cabi().radius(x, y, 0.1, px, py, 16, False, screen=True)
+    plain = _cabi().radius(x, y, 0.1, px, py, 16, False, one_pass=False)  # the plain scan takes them as the reference does
+    assert plain.shape[1] > 0
+    _both(x, y, 0.1, max_nn=16)

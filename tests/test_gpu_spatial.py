@@ -187,3 +187,22 @@ def test_large_segments_with_duplicates_and_outliers():
     _both(x, y, 16)
     ptr_x, ptr_y = _ptr([70000, 50000]), _ptr([700, y.shape[0] - 700])
     _both(x, y, 8, ptr_x, ptr_y, hint=70000)
+
+
+def test_overlapping_segments_are_refused_not_overrun():
+    """Segment pointers that are no partition of the rows (sizes adding up to more than the rows) do not fit the
+    sorted copies: the ordering pass leaves its layout empty and the call is flagged, as a bounded wait that ran
+    out would be — nothing is written out of bounds, and the operator raises."""
+    g = torch.Generator().manual_seed(29)
+    x = torch.rand(6000, 3, generator=g).to(DEV)
+    y = torch.rand(300, 3, generator=g).to(DEV)
+    px = torch.tensor([0, 3000, 2000, 6000], device=DEV)  # the third segment starts inside the first
+    py = torch.tensor([0, 100, 200, 300], device=DEV)
+    with pytest.raises(RuntimeError, match="overlap"):
+        torch.ops.torch_cluster.knn(x, y, px, py, 8, False, 1)
+    with pytest.raises(RuntimeError, match="overlap"):
+        torch.ops.torch_cluster.knn_graph_edges(x, px, 8, False, True, False, 0)
+    # the plain kernels take such pointers as the reference does
+    _cabi().knn_padded(x, y, 8, px, py, workspace=False)
+    # and the next regular call is unaffected
+    _both(x, y, 8)
