@@ -61,6 +61,15 @@ int b200c_segment_ptr(const int64_t *batch, int64_t n, int64_t num_segments,
  * torch_cluster/knn.py:62-69; the second is the max_segment_rows hint of b200c_knn. */
 int b200c_batch_info(const int64_t *batch, int64_t n, int64_t *info, b200c_stream_t stream);
 
+/* The two device-side checks of torch_cluster/nearest.py:60-87, one kernel each instead of a dozen tensor
+ * operations.  b200c_batch_check: info (int64 [3], device) = b200c_batch_info's two values and info[2] = 1
+ * if the batch vector is not sorted ("'batch_x' is not sorted", nearest.py:60-66).  b200c_segment_mismatch:
+ * *flag (int32, device) = 1 if some segment is empty on one side and not on the other ("Some batch indices
+ * occur in 'batch_x' that do not occur in 'batch_y'", nearest.py:81-87), else 0. */
+int b200c_batch_check(const int64_t *batch, int64_t n, int64_t *info, b200c_stream_t stream);
+int b200c_segment_mismatch(const int64_t *ptr_x, const int64_t *ptr_y, int64_t num_segments,
+                           int32_t *flag, b200c_stream_t stream);
+
 /* Exclusive prefix sum of per-query edge counts:
  *   offsets[0] = 0, offsets[i + 1] = offsets[i] + counts[i];  offsets[m] = E.
  * Replaces the mask + masked_select compaction of csrc/cuda/radius_cuda.cu:94-95

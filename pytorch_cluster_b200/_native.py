@@ -50,6 +50,10 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_segment_ptr.argtypes = [p, i64, i64, p, p]
     lib.b200c_batch_info.argtypes = [p, i64, p, p]
     lib.b200c_batch_info.restype = i32
+    lib.b200c_batch_check.argtypes = [p, i64, p, p]
+    lib.b200c_batch_check.restype = i32
+    lib.b200c_segment_mismatch.argtypes = [p, p, i64, p, p]
+    lib.b200c_segment_mismatch.restype = i32
     lib.b200c_scan_workspace_bytes.argtypes = [i64]
     lib.b200c_scan_workspace_bytes.restype = sz
     lib.b200c_exclusive_scan.argtypes = [p, i64, p, p, sz, p]

@@ -28,11 +28,15 @@ __global__ void segment_ptr_kernel(const int64_t *__restrict__ batch, int64_t n,
 
 // info[0] = batch[n - 1] + 1 (the ids are sorted, so the last is the largest), info[1] = rows of the
 // longest run of equal ids.  The thread at the last row of a run bisects for the run's first row.
-__global__ void batch_info_kernel(const int64_t *__restrict__ batch, int64_t n, unsigned long long *__restrict__ info) {
+// With `unsorted` != nullptr also *unsorted = 1 if some entry is smaller than the one before it (the other two
+// values mean nothing then).
+__global__ void batch_info_kernel(const int64_t *__restrict__ batch, int64_t n, unsigned long long *__restrict__ info,
+                                  unsigned long long *__restrict__ unsorted) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   unsigned long long best = 0;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     const int64_t id = batch[i];
+    if (unsorted != nullptr && i + 1 < n && batch[i + 1] < id) *unsorted = 1ull;
     if (i + 1 < n && batch[i + 1] == id) continue;
     int64_t lo = 0, hi = i;
     while (lo < hi) {
@@ -330,8 +334,39 @@ extern "C" int b200c_batch_info(const int64_t *batch, int64_t n, int64_t *info, 
   if (n == 0) return B200C_OK;
   const int64_t want = (n + 255) / 256;
   batch_info_kernel<<<(unsigned)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(batch, n,
-                                                                                  (unsigned long long *)info);
+                                                                                  (unsigned long long *)info, nullptr);
   B200C_LAUNCH_CHECK("batch_info_kernel");
+  return B200C_OK;
+}
+
+extern "C" int b200c_batch_check(const int64_t *batch, int64_t n, int64_t *info, b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  B200C_CHECK_ARG(n >= 0 && info != nullptr && (batch != nullptr || n == 0), "Input mismatch");
+  B200C_CUDA(cudaMemsetAsync(info, 0, 3 * sizeof(int64_t), stream));
+  if (n == 0) return B200C_OK;
+  const int64_t want = (n + 255) / 256;
+  batch_info_kernel<<<(unsigned)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(
+      batch, n, (unsigned long long *)info, (unsigned long long *)info + 2);
+  B200C_LAUNCH_CHECK("batch_info_kernel");
+  return B200C_OK;
+}
+
+__global__ void segment_mismatch_kernel(const int64_t *__restrict__ ptr_x, const int64_t *__restrict__ ptr_y,
+                                        int64_t num_segments, int32_t *__restrict__ flag) {
+  const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= num_segments) return;
+  if ((ptr_x[b + 1] > ptr_x[b]) != (ptr_y[b + 1] > ptr_y[b])) *flag = 1;
+}
+
+extern "C" int b200c_segment_mismatch(const int64_t *ptr_x, const int64_t *ptr_y, int64_t num_segments,
+                                      int32_t *flag, b200c_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  B200C_CHECK_ARG(num_segments >= 0 && flag != nullptr && ((ptr_x != nullptr && ptr_y != nullptr) || num_segments == 0),
+                  "Input mismatch");
+  B200C_CUDA(cudaMemsetAsync(flag, 0, sizeof(int32_t), stream));
+  if (num_segments == 0) return B200C_OK;
+  segment_mismatch_kernel<<<(unsigned)((num_segments + 255) / 256), 256, 0, stream>>>(ptr_x, ptr_y, num_segments, flag);
+  B200C_LAUNCH_CHECK("segment_mismatch_kernel");
   return B200C_OK;
 }
 

@@ -384,6 +384,61 @@ torch::Tensor nearest(torch::Tensor x, torch::Tensor y, torch::Tensor ptr_x, tor
   return out;
 }
 
+namespace {
+
+// `nearest` of torch_cluster/nearest.py:44-87 with its checks in one operator: both batch vectors sorted
+// (ValueError otherwise), equally many examples on both sides, and every example that has rows in x has rows
+// in y.  One host read before the search (segments and sortedness of both vectors, one kernel each) and one
+// after it (the emptiness comparison, which the search does not depend on: rows of an example without a row
+// in y are assigned 0).
+torch::Tensor nearest_batched(torch::Tensor x, torch::Tensor y, std::optional<torch::Tensor> batch_x,
+                              std::optional<torch::Tensor> batch_y) {
+  CHECK_CUDA(x);
+  CHECK_CUDA(y);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const auto lopts = x.options().dtype(torch::kLong);
+  const int64_t n = x.size(0), m = y.size(0);
+  auto info = torch::zeros({6}, lopts);
+  torch::Tensor bx, by;
+  if (batch_x.has_value()) {
+    bx = batch_x.value().contiguous();
+    CHECK_CUDA(bx);
+    TORCH_CHECK(bx.scalar_type() == at::kLong && bx.dim() == 1, "batch_x must be a 1-D int64 tensor");
+    TORCH_CHECK(bx.numel() == n || bx.numel() == 0, "x.size(0) == batch_x.numel()");
+    check_status(b200c_batch_check(bx.data_ptr<int64_t>(), bx.numel(), info.data_ptr<int64_t>(), stream.stream()));
+  }
+  if (batch_y.has_value()) {
+    by = batch_y.value().contiguous();
+    CHECK_CUDA(by);
+    TORCH_CHECK(by.scalar_type() == at::kLong && by.dim() == 1, "batch_y must be a 1-D int64 tensor");
+    TORCH_CHECK(by.numel() == m || by.numel() == 0, "y.size(0) == batch_y.numel()");
+    check_status(b200c_batch_check(by.data_ptr<int64_t>(), by.numel(), info.data_ptr<int64_t>() + 3, stream.stream()));
+  }
+  const auto seen = info.cpu();
+  const int64_t *h = seen.data_ptr<int64_t>();
+  TORCH_CHECK_VALUE(h[2] == 0, "'batch_x' is not sorted");
+  TORCH_CHECK_VALUE(h[5] == 0, "'batch_y' is not sorted");
+  auto whole = [&](int64_t rows) {
+    auto ptr = torch::zeros({2}, lopts);
+    ptr[1].fill_(rows);
+    return ptr;
+  };
+  const int64_t segs_x = batch_x.has_value() ? std::max<int64_t>(h[0], 1) : 1;
+  const int64_t segs_y = batch_y.has_value() ? std::max<int64_t>(h[3], 1) : 1;
+  auto ptr_x = batch_x.has_value() ? segment_ptr(bx, segs_x) : whole(n);
+  auto ptr_y = batch_y.has_value() ? segment_ptr(by, segs_y) : whole(m);
+  TORCH_CHECK_VALUE(segs_x == segs_y, "Some batch indices occur in 'batch_x' that do not occur in 'batch_y'");
+  auto flag = torch::empty({1}, x.options().dtype(torch::kInt));
+  check_status(b200c_segment_mismatch(ptr_x.data_ptr<int64_t>(), ptr_y.data_ptr<int64_t>(), segs_x,
+                                      flag.data_ptr<int32_t>(), stream.stream()));
+  auto out = nearest(x, y, ptr_x, ptr_y);
+  TORCH_CHECK_VALUE(flag.item<int32_t>() == 0, "Some batch indices occur in 'batch_x' that do not occur in 'batch_y'");
+  return out;
+}
+
+}  // namespace
+
 // Which segments of an fps call go where: `large` (more than per_cta points, at most multi_cap, at least
 // one sample) are sampled by many SMs together, `oversize` (more than multi_cap) by one thread block from
 // global memory in a call of their own; every other segment runs in the common call.
@@ -613,6 +668,7 @@ static auto registry = torch::RegisterOperators()
                            .op("torch_cluster::knn", &knn)
                            .op("torch_cluster::knn_hinted", &knn_hinted)
                            .op("torch_cluster::batch_info", &batch_info)
+                           .op("torch_cluster::nearest_batched", &nearest_batched)
                            .op("torch_cluster::radius", &radius)
                            .op("torch_cluster::radius_part", &radius_part)
                            .op("torch_cluster::fps_ptr_list", &fps_ptr_list)

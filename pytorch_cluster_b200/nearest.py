@@ -24,26 +24,6 @@ def nearest(
     if not x.is_cuda:
         raise RuntimeError("x must be CUDA tensor")
 
-    if batch_x is not None and bool((batch_x[1:] - batch_x[:-1] < 0).any()):
-        raise ValueError("'batch_x' is not sorted")
-    if batch_y is not None and bool((batch_y[1:] - batch_y[:-1] < 0).any()):
-        raise ValueError("'batch_y' is not sorted")
-
-    if batch_x is not None:
-        assert x.size(0) == batch_x.numel()
-        ptr_x = torch.ops.torch_cluster.segment_ptr(batch_x, int(batch_x[-1]) + 1 if batch_x.numel() > 0 else 1)
-    else:
-        ptr_x = torch.tensor([0, x.size(0)], device=x.device)
-    if batch_y is not None:
-        assert y.size(0) == batch_y.numel()
-        ptr_y = torch.ops.torch_cluster.segment_ptr(batch_y, int(batch_y[-1]) + 1 if batch_y.numel() > 0 else 1)
-    else:
-        ptr_y = torch.tensor([0, y.size(0)], device=y.device)
-
-    # If an instance in `batch_x` is non-empty, it must be non-empty in `batch_y` as well
-    nonempty_ptr_x = (ptr_x[1:] - ptr_x[:-1]) > 0
-    nonempty_ptr_y = (ptr_y[1:] - ptr_y[:-1]) > 0
-    if not torch.equal(nonempty_ptr_x, nonempty_ptr_y):
-        raise ValueError("Some batch indices occur in 'batch_x' that do not occur in 'batch_y'")
-
-    return torch.ops.torch_cluster.nearest(x, y, ptr_x, ptr_y)
+    # checks, segment pointers and search in one operator (two host reads: the batch vectors' summaries
+    # before the search, the emptiness comparison after it)
+    return torch.ops.torch_cluster.nearest_batched(x, y, batch_x, batch_y)
