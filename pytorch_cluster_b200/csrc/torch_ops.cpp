@@ -337,6 +337,23 @@ std::vector<int64_t> batch_info(torch::Tensor batch) {
   return {host[0].item<int64_t>(), host[1].item<int64_t>()};
 }
 
+// [last id + 1, rows of the longest run of equal ids, 1 if some entry is smaller than the one before it]
+// (one kernel, one host sync): for callers that must not assume a sorted vector (torch_cluster/fps.py:95-104
+// counts members instead of bisecting) but want the cheap route when it is.
+std::vector<int64_t> batch_check(torch::Tensor batch) {
+  CHECK_CUDA(batch);
+  CHECK_INPUT(batch.dim() == 1);
+  TORCH_CHECK(batch.scalar_type() == at::kLong, "batch must be an int64 tensor");
+  if (batch.numel() == 0) return {0, 0, 0};
+  batch = batch.contiguous();
+  c10::cuda::CUDAGuard guard(batch.device());
+  auto info = torch::empty({3}, batch.options());
+  check_status(b200c_batch_check(batch.data_ptr<int64_t>(), batch.numel(), info.data_ptr<int64_t>(),
+                                 at::cuda::getCurrentCUDAStream().stream()));
+  auto host = info.cpu();
+  return {host[0].item<int64_t>(), host[1].item<int64_t>(), host[2].item<int64_t>()};
+}
+
 // Device-side construction of the segment pointers from a sorted batch vector
 // (what torch_cluster/knn.py:77-79 does with torch.bucketize).
 torch::Tensor segment_ptr(torch::Tensor batch, int64_t num_segments) {
@@ -668,6 +685,7 @@ static auto registry = torch::RegisterOperators()
                            .op("torch_cluster::knn", &knn)
                            .op("torch_cluster::knn_hinted", &knn_hinted)
                            .op("torch_cluster::batch_info", &batch_info)
+                           .op("torch_cluster::batch_check", &batch_check)
                            .op("torch_cluster::nearest_batched", &nearest_batched)
                            .op("torch_cluster::radius", &radius)
                            .op("torch_cluster::radius_part", &radius_part)

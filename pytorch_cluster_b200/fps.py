@@ -62,6 +62,12 @@ def fps(  # noqa
         return torch.ops.torch_cluster.fps_ptr_list(src, [0, src.size(0)], r, random_start)
 
     assert src.size(0) == batch.numel()
+    # A sorted vector (the usual case) gives its boundaries by bisection, one small kernel; the summary that
+    # says so is one kernel and one host read.
+    seen: List[int] = torch.ops.torch_cluster.batch_check(batch)
+    if seen[2] == 0:
+        examples = batch_size if batch_size is not None else seen[0]
+        return torch.ops.torch_cluster.fps(src, torch.ops.torch_cluster.segment_ptr(batch, examples), r, random_start)
     num_examples = batch_size if batch_size is not None else int(batch.max()) + 1
     # The example ids need not be sorted for this operator (torch_cluster/fps.py:98-103 counts
     # members instead of bisecting), so the boundaries are the running sum of a histogram.
