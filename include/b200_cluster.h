@@ -196,7 +196,7 @@ int b200c_knn_graph_tail_write(const int64_t *edge_padded, const int32_t *counts
                                int64_t m, int64_t k, int drop_self, int source_to_target,
                                int64_t num_edges, int64_t *edge_index, b200c_stream_t stream);
 
-/* knn_graph with loop = False in one kernel, for fp32 / fp64 points of up to 8 features — the
+/* knn_graph with loop = False in one call, for fp32 / fp64 points of up to 8 features (one kernel) — the
  * search for k + 1 neighbours of every row of x in x, the `row != col` mask and the flow swap of
  * torch_cluster/knn.py:131-144 without the padded intermediate.
  *
@@ -206,10 +206,13 @@ int b200c_knn_graph_tail_write(const int64_t *edge_padded, const int32_t *counts
  * number of queries that do not have that shape (segments of fewer than k + 1 points; rows
  * pushed out of their own list by k + 1 exact duplicates); their slots are left unwritten.  When
  * it is 0 the result is final, otherwise run b200c_knn and the tail entry points instead.
- * Returns B200C_ERR_UNSUPPORTED for more than 8 features and for the 16-bit types.
+ * Returns B200C_ERR_UNSUPPORTED for the 16-bit types and for more than 8 features, except fp32
+ * feature vectors for which b200c_knn_graph_workspace_bytes answers non-zero (32 to 128 features, a
+ * multiple of 8, k + 1 <= 32, 16-byte aligned x) when that workspace is given: the exact re-rank of the
+ * tensor-core candidates (see b200c_knn) then writes the edge rows itself.
  *
- * workspace (optional): b200c_knn_graph_workspace_bytes(...) bytes enable the scan over a
- * Morton-ordered copy of x for fp32 (see b200c_knn; max_segment_rows as there).  Should one of
+ * workspace (optional for up to 8 features): b200c_knn_graph_workspace_bytes(...) bytes enable the scan
+ * over a Morton-ordered copy of x for fp32 (see b200c_knn; max_segment_rows as there).  Should one of
  * that path's bounded waits run out, or the segments overlap, 2^30 is added to *irregular. */
 size_t b200c_knn_graph_workspace_bytes(int64_t n, int64_t dim, int64_t k, int dtype,
                                        int64_t num_segments);

@@ -179,8 +179,13 @@ extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t n
   B200C_CHECK_ARG(k + 1 <= B200C_MAX_K, "`k` needs to smaller than or equal to 100");
   B200C_CHECK_ARG(irregular != nullptr && (edge_row0 != nullptr || n == 0), "null output pointer");
   B200C_CHECK_ARG(index_base >= 0 && row_stride >= n * k, "Input mismatch");
-  if (dim > 8 || is16(dtype)) {
-    set_error("b200c_knn_graph covers fp32 / fp64 points of up to 8 features; use b200c_knn and the tail entry points");
+  // feature vectors: the tensor-core candidate path with the re-rank writing the edge rows (fp32, workspace given)
+  const bool features = dtype == B200C_F32 && dim > 8 && workspace != nullptr &&
+                        knn_tensor_applicable(n, n, (int)dim, (int)(k + 1), num_segments, x, x) &&
+                        workspace_bytes >= knn_tensor_workspace_bytes(n, n, (int)dim, 0);
+  if ((dim > 8 && !features) || is16(dtype)) {
+    set_error("b200c_knn_graph covers fp32 / fp64 points of up to 8 features, and fp32 feature vectors where the "
+              "tensor-core path applies and its workspace is given; use b200c_knn and the tail entry points");
     return B200C_ERR_UNSUPPORTED;
   }
   if ((st = check_device()) != B200C_OK) return st;
@@ -193,6 +198,7 @@ extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t n
   a.graph_index_base = index_base;
   a.graph_s2t = source_to_target;
   a.graph_irregular = (int *)irregular;
+  if (features) return launch_knn_tensor_f32(a, workspace);
   if (dtype == B200C_F32 && workspace != nullptr && knn_spatial_applicable(n, n, (int)dim, (int)(k + 1), num_segments) &&
       workspace_bytes >= knn_spatial_workspace_bytes(n, n, (int)dim, num_segments, true))
     return launch_knn_spatial_f32(a, workspace, max_segment_rows);
@@ -202,6 +208,9 @@ extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t n
 extern "C" size_t b200c_knn_graph_workspace_bytes(int64_t n, int64_t dim, int64_t k, int dtype, int64_t num_segments) {
   if (dtype == B200C_F32 && knn_spatial_applicable(n, n, (int)dim, (int)(k + 1), num_segments))
     return knn_spatial_workspace_bytes(n, n, (int)dim, num_segments, true);
+  if (dtype == B200C_F32 && dim > 8 && num_segments >= 1 &&
+      knn_tensor_applicable(n, n, (int)dim, (int)(k + 1), num_segments, nullptr, nullptr))
+    return knn_tensor_workspace_bytes(n, n, (int)dim, 0);
   return 0;
 }
 

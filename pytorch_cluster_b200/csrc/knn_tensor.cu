@@ -432,7 +432,12 @@ knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, cons
                   const float *__restrict__ norms_x, const float *__restrict__ norms_y,
                   const int32_t *__restrict__ cand, const int32_t *__restrict__ cand_count,
                   const int *__restrict__ error_flag, int64_t *__restrict__ out_row, int64_t *__restrict__ out_col,
-                  int32_t *__restrict__ counts, unsigned long long *__restrict__ num_valid) {
+                  int32_t *__restrict__ counts, unsigned long long *__restrict__ num_valid,
+                  int64_t *__restrict__ graph_out, int64_t graph_row_stride, int64_t graph_index_base, int graph_s2t,
+                  int *__restrict__ graph_irregular) {
+  // graph_out != nullptr: knn_graph output (see knn_finish_graph in select.cuh) instead of the padded rows:
+  // the k - 1 neighbours other than the query itself straight into the final edge rows; queries that do not
+  // have that shape are counted in *graph_irregular and write nothing.
   using K = Key<float>;
   constexpr int KP = 32;
   extern __shared__ __align__(16) unsigned char smem_rerank[];
@@ -533,6 +538,24 @@ knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, cons
       k0 = warp_bitonic_merge32(k0, lane);
     }
     const bool okk = lane < k && !k0.is_empty();
+    if (graph_out != nullptr) {
+      // lane e holds the e-th best: all k present and the query itself among them, else irregular
+      const unsigned present = __ballot_sync(FULL_MASK, okk);
+      const unsigned self = __ballot_sync(FULL_MASK, okk && (int64_t)k0.index() == q);
+      if (__popc(present) != k || self == 0u) {
+        if (lane == 0) atomicAdd(graph_irregular, 1);
+        return;
+      }
+      const int selfpos = __ffs(self) - 1;
+      if (lane < k && lane != selfpos) {
+        const int64_t slot = q * (k - 1) + lane - (lane > selfpos ? 1 : 0);
+        int64_t *row_nb = graph_s2t ? graph_out : graph_out + graph_row_stride;
+        int64_t *row_q = graph_s2t ? graph_out + graph_row_stride : graph_out;
+        row_nb[slot] = graph_index_base + (int64_t)k0.index();
+        row_q[slot] = graph_index_base + q;
+      }
+      return;
+    }
     if (lane < k) {
       out_row[q * k + lane] = q;
       out_col[q * k + lane] = okk ? (int64_t)k0.index() : (int64_t)-1;
@@ -573,6 +596,13 @@ knn_rerank_kernel(const float *__restrict__ x, const float *__restrict__ y, cons
       if (lane == 0) *my_cnt = cnt;
       __syncwarp();
     }
+  }
+  if (graph_out != nullptr) {
+    if (!knn_finish_graph<float, KP>(my_keys, *my_cnt, k, q, graph_row_stride, graph_index_base, graph_out,
+                                     graph_s2t != 0, lane) &&
+        lane == 0)
+      atomicAdd(graph_irregular, 1);
+    return;
   }
   const int valid = knn_finish<float, KP>(my_keys, *my_cnt, k, q, out_row, out_col, lane);
   if (lane == 0) {
@@ -629,11 +659,13 @@ int launch_knn_rerank_f32(const KnnArgs &a, const int32_t *cand, const int32_t *
   if (a.cosine)
     knn_rerank_kernel<true><<<rr_ctas, RR_WARPS * 32, rr_smem, a.stream>>>(
         (const float *)a.x, (const float *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, norms_x,
-        norms_y, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid);
+        norms_y, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid, a.graph_out,
+        a.graph_row_stride, a.graph_index_base, a.graph_s2t, a.graph_irregular);
   else
     knn_rerank_kernel<false><<<rr_ctas, RR_WARPS * 32, rr_smem, a.stream>>>(
         (const float *)a.x, (const float *)a.y, a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, nullptr,
-        nullptr, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid);
+        nullptr, cand, cand_count, error_flag, a.out_row, a.out_col, a.counts, a.num_valid, a.graph_out,
+        a.graph_row_stride, a.graph_index_base, a.graph_s2t, a.graph_irregular);
   B200C_LAUNCH_CHECK("knn_rerank_kernel");
   return B200C_OK;
 }
@@ -683,11 +715,14 @@ int launch_knn_tensor_f32(const KnnArgs &a, void *workspace) {
                a.ptr_x, a.ptr_y, a.num_segments, a.n, a.m, a.dim, a.k, cand, cand_count, error_flag};
   const size_t smem = knn_tensor_smem_bytes(a.dim, TC_RING);
   const unsigned ctas = (unsigned)((a.m + TC_M - 1) / TC_M);
+  // the opt-in covers the largest tile set (128 features) once per device and kernel
+  const size_t smem_most = knn_tensor_smem_bytes(128, TC_RING);
+  static unsigned long long configured_cosine = 0ull, configured_l2 = 0ull;
   if (a.cosine) {
-    B200C_CUDA(cudaFuncSetAttribute(knn_tensor_candidates_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200C_CUDA(opt_in_shared_memory(knn_tensor_candidates_kernel<true>, smem_most, configured_cosine));
     knn_tensor_candidates_kernel<true><<<ctas, TC_THREADS, smem, a.stream>>>(t);
   } else {
-    B200C_CUDA(cudaFuncSetAttribute(knn_tensor_candidates_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200C_CUDA(opt_in_shared_memory(knn_tensor_candidates_kernel<false>, smem_most, configured_l2));
     knn_tensor_candidates_kernel<false><<<ctas, TC_THREADS, smem, a.stream>>>(t);
   }
   B200C_LAUNCH_CHECK("knn_tensor_candidates_kernel");

@@ -178,12 +178,14 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
   const int64_t n = p.x.size(0), dim = p.x.size(1);
   if (n == 0) return torch::empty({2, 0}, lopts);
 
-  if (!loop && !cosine && dim <= 8 && (p.dtype == B200C_F32 || p.dtype == B200C_F64)) {
-    // the usual shape (every row finds itself and k others) comes out of one kernel; anything
-    // else is detected there and takes the general route below
+  const size_t gws_bytes = (!loop && !cosine) ? b200c_knn_graph_workspace_bytes(n, dim, k, p.dtype, p.num_segments) : 0;
+  const bool aligned = (reinterpret_cast<uintptr_t>(p.x.data_ptr()) & 15) == 0;  // the tensor-core path's operand copies
+  if (!loop && !cosine && (p.dtype == B200C_F32 || p.dtype == B200C_F64) && (dim <= 8 || (gws_bytes > 0 && aligned))) {
+    // the usual shape (every row finds itself and k others) comes out of one kernel (low-dimensional points)
+    // or of the re-rank of the tensor-core candidates (feature vectors); anything else is detected there and
+    // takes the general route below
     auto out = torch::empty({2, n * k}, lopts);
     auto irregular = torch::empty({1}, iopts);
-    const size_t gws_bytes = b200c_knn_graph_workspace_bytes(n, dim, k, p.dtype, p.num_segments);
     auto gws = torch::empty({(int64_t)gws_bytes}, x.options().dtype(torch::kByte));
     check_status(b200c_knn_graph(p.x.data_ptr(), p.px, p.num_segments, n, dim, k, p.dtype, source_to_target ? 1 : 0,
                                  out.data_ptr<int64_t>(), irregular.data_ptr<int32_t>(), max_segment_rows,

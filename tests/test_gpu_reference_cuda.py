@@ -96,6 +96,35 @@ def test_knn_feature_space_tensor_path(cosine, dim):
     _same(_ours_knn(x, x, p, p, 21, cosine), refc.knn(x, x, p, p, 21, cosine))
 
 
+@pytest.mark.parametrize("dim", [32, 64, 128])
+def test_knn_graph_feature_space_in_one_call(dim):
+    """knn_graph on feature vectors: the re-rank of the tensor-core candidates writes the final edge rows; equal
+    to the reference's composition (k + 1 neighbours by its CUDA kernel, self matches dropped, rows by flow) —
+    also where exact duplicates push a row out of its own list, which takes the general route."""
+    import pytorch_cluster_b200 as pc
+
+    g = torch.Generator().manual_seed(40 + dim)
+    x = torch.randn(8 * 2048, dim, generator=g).to(DEV)
+    batch = torch.arange(8, device=DEV).repeat_interleave(2048)
+    p = _ptr(8, 2048)
+
+    def composed(xx, flow):
+        e = refc.knn(xx, xx, p, p, 21, False)           # row 0 = query, row 1 = neighbour
+        e = e[:, e[0] != e[1]]
+        return e.flip(0) if flow == "source_to_target" else e
+
+    for flow in ("source_to_target", "target_to_source"):
+        _same(pc.knn_graph(x, 20, batch, flow=flow), composed(x, flow))
+    dup = x.clone()
+    dup[:30] = dup[0]  # 30 copies of one row: some are pushed out of their own lists
+    _same(pc.knn_graph(dup, 20, batch), composed(dup, "source_to_target"))
+    from pytorch_cluster_b200 import cabi
+
+    fast, odd = cabi.knn_graph(x, 20, p, True, workspace=True)
+    assert odd == 0
+    _same(fast, composed(x, "source_to_target"))
+
+
 @pytest.mark.parametrize("cosine", [False, True])
 def test_knn_general_dim(cosine):
     g = torch.Generator().manual_seed(14)
