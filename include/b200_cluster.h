@@ -233,6 +233,19 @@ int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t num_segments
                          int32_t *irregular, int64_t max_segment_rows, void *workspace,
                          size_t workspace_bytes, b200c_stream_t stream);
 
+/* The same for the cosine distance of the reference (csrc/cuda/knn_cuda.cu:9-28, 55-59) on fp32 feature
+ * vectors: tensor-core candidates over the normalised rows, the exact re-rank — which evaluates
+ * 1 - dot / (|x| |y|) as the reference does — writing the edge rows.  The workspace is required
+ * (b200c_knn_graph_cosine_workspace_bytes; 0: not applicable, use b200c_knn with cosine = 1 and the tail
+ * entry points).  The reference composes this case from `knn(..., cosine=True)` and the mask of
+ * torch_cluster/knn.py:131-144. */
+size_t b200c_knn_graph_cosine_workspace_bytes(int64_t n, int64_t dim, int64_t k,
+                                              int64_t num_segments);
+int b200c_knn_graph_cosine(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n,
+                           int64_t dim, int64_t k, int source_to_target, int64_t *edge_index,
+                           int32_t *irregular, void *workspace, size_t workspace_bytes,
+                           b200c_stream_t stream);
+
 /* Fixed-radius search — replaces radius_kernel and its -1 padded output
  * (csrc/cuda/radius_cuda.cu:9-42, 75-95) by count -> exclusive scan -> fill.
  *

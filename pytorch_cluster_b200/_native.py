@@ -98,6 +98,10 @@ def cabi() -> ctypes.CDLL:
     lib.b200c_knn_graph.restype = i32
     lib.b200c_knn_graph_part.argtypes = [p, p, i64, i64, i64, i64, i32, i32, i64, p, i64, p, i64, p, sz, p]
     lib.b200c_knn_graph_part.restype = i32
+    lib.b200c_knn_graph_cosine_workspace_bytes.argtypes = [i64, i64, i64, i64]
+    lib.b200c_knn_graph_cosine_workspace_bytes.restype = sz
+    lib.b200c_knn_graph_cosine.argtypes = [p, p, i64, i64, i64, i64, i32, p, p, p, sz, p]
+    lib.b200c_knn_graph_cosine.restype = i32
     lib.b200c_radius_mask_workspace_bytes.argtypes = [p, p, i64, i64, i64, i64, i32]
     lib.b200c_radius_mask_workspace_bytes.restype = sz
     lib.b200c_radius_count_masks.argtypes = [p, p, p, p, p, p, i64, i64, i64, i64, dbl, i64, i32, i32, p, p, sz, p]

@@ -167,12 +167,10 @@ extern "C" int b200c_knn(const void *x, const void *y, const int64_t *ptr_x, con
 }
 
 // knn_graph of low-dimensional points in one kernel: see b200_cluster.h
-extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
-                                    int64_t k, int dtype, int source_to_target, int64_t index_base,
-                                    int64_t *edge_row0, int64_t row_stride, int32_t *irregular,
-                                    int64_t max_segment_rows, void *workspace, size_t workspace_bytes,
-                                    b200c_stream_t stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
+static int knn_graph_common(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
+                            int64_t k, int dtype, int cosine, int source_to_target, int64_t index_base,
+                            int64_t *edge_row0, int64_t row_stride, int32_t *irregular, int64_t max_segment_rows,
+                            void *workspace, size_t workspace_bytes, cudaStream_t stream) {
   int st = check_common(x, x, ptr, ptr, num_segments, n, n, dim, dtype);
   if (st != B200C_OK) return st;
   B200C_CHECK_ARG(k >= 1, "`k` needs to be positive");
@@ -182,8 +180,8 @@ extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t n
   // feature vectors: the tensor-core candidate path with the re-rank writing the edge rows (fp32, workspace given)
   const bool features = dtype == B200C_F32 && dim > 8 && workspace != nullptr &&
                         knn_tensor_applicable(n, n, (int)dim, (int)(k + 1), num_segments, x, x) &&
-                        workspace_bytes >= knn_tensor_workspace_bytes(n, n, (int)dim, 0);
-  if ((dim > 8 && !features) || is16(dtype)) {
+                        workspace_bytes >= knn_tensor_workspace_bytes(n, n, (int)dim, cosine);
+  if ((dim > 8 && !features) || (cosine && !features) || is16(dtype)) {
     set_error("b200c_knn_graph covers fp32 / fp64 points of up to 8 features, and fp32 feature vectors where the "
               "tensor-core path applies and its workspace is given; use b200c_knn and the tail entry points");
     return B200C_ERR_UNSUPPORTED;
@@ -191,7 +189,7 @@ extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t n
   if ((st = check_device()) != B200C_OK) return st;
   B200C_CUDA(cudaMemsetAsync(irregular, 0, sizeof(int32_t), stream));
   if (n == 0) return B200C_OK;
-  KnnArgs a{x, x, ptr, ptr, (int)num_segments, n, n, (int)dim, (int)(k + 1), 0, nullptr, nullptr,
+  KnnArgs a{x, x, ptr, ptr, (int)num_segments, n, n, (int)dim, (int)(k + 1), cosine, nullptr, nullptr,
             nullptr, nullptr, nullptr, nullptr, stream};
   a.graph_out = edge_row0;
   a.graph_row_stride = row_stride;
@@ -203,6 +201,29 @@ extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t n
       workspace_bytes >= knn_spatial_workspace_bytes(n, n, (int)dim, num_segments, true))
     return launch_knn_spatial_f32(a, workspace, max_segment_rows);
   return dtype == B200C_F32 ? launch_knn_lowd_f32(a) : launch_knn_lowd_f64(a);
+}
+
+extern "C" int b200c_knn_graph_part(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
+                                    int64_t k, int dtype, int source_to_target, int64_t index_base,
+                                    int64_t *edge_row0, int64_t row_stride, int32_t *irregular,
+                                    int64_t max_segment_rows, void *workspace, size_t workspace_bytes,
+                                    b200c_stream_t stream) {
+  return knn_graph_common(x, ptr, num_segments, n, dim, k, dtype, 0, source_to_target, index_base, edge_row0, row_stride,
+                          irregular, max_segment_rows, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" size_t b200c_knn_graph_cosine_workspace_bytes(int64_t n, int64_t dim, int64_t k, int64_t num_segments) {
+  if (n >= 1 && dim > 8 && num_segments >= 1 &&
+      knn_tensor_applicable(n, n, (int)dim, (int)(k + 1), num_segments, nullptr, nullptr))
+    return knn_tensor_workspace_bytes(n, n, (int)dim, 1);
+  return 0;
+}
+
+extern "C" int b200c_knn_graph_cosine(const void *x, const int64_t *ptr, int64_t num_segments, int64_t n, int64_t dim,
+                                      int64_t k, int source_to_target, int64_t *edge_index, int32_t *irregular,
+                                      void *workspace, size_t workspace_bytes, b200c_stream_t stream) {
+  return knn_graph_common(x, ptr, num_segments, n, dim, k, B200C_F32, 1, source_to_target, 0, edge_index, n * k,
+                          irregular, 0, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 extern "C" size_t b200c_knn_graph_workspace_bytes(int64_t n, int64_t dim, int64_t k, int dtype, int64_t num_segments) {

@@ -178,18 +178,28 @@ torch::Tensor knn_graph_edges(torch::Tensor x, std::optional<torch::Tensor> ptr,
   const int64_t n = p.x.size(0), dim = p.x.size(1);
   if (n == 0) return torch::empty({2, 0}, lopts);
 
-  const size_t gws_bytes = (!loop && !cosine) ? b200c_knn_graph_workspace_bytes(n, dim, k, p.dtype, p.num_segments) : 0;
+  size_t gws_bytes = 0;
+  if (!loop && cosine && p.dtype == B200C_F32)
+    gws_bytes = b200c_knn_graph_cosine_workspace_bytes(n, dim, k, p.num_segments);
+  else if (!loop && !cosine)
+    gws_bytes = b200c_knn_graph_workspace_bytes(n, dim, k, p.dtype, p.num_segments);
   const bool aligned = (reinterpret_cast<uintptr_t>(p.x.data_ptr()) & 15) == 0;  // the tensor-core path's operand copies
-  if (!loop && !cosine && (p.dtype == B200C_F32 || p.dtype == B200C_F64) && (dim <= 8 || (gws_bytes > 0 && aligned))) {
+  const bool features = dim > 8 && gws_bytes > 0 && aligned;
+  if (!loop && (p.dtype == B200C_F32 || p.dtype == B200C_F64) && ((!cosine && dim <= 8) || features)) {
     // the usual shape (every row finds itself and k others) comes out of one kernel (low-dimensional points)
     // or of the re-rank of the tensor-core candidates (feature vectors); anything else is detected there and
     // takes the general route below
     auto out = torch::empty({2, n * k}, lopts);
     auto irregular = torch::empty({1}, iopts);
     auto gws = torch::empty({(int64_t)gws_bytes}, x.options().dtype(torch::kByte));
-    check_status(b200c_knn_graph(p.x.data_ptr(), p.px, p.num_segments, n, dim, k, p.dtype, source_to_target ? 1 : 0,
-                                 out.data_ptr<int64_t>(), irregular.data_ptr<int32_t>(), max_segment_rows,
-                                 gws_bytes ? gws.data_ptr() : nullptr, gws_bytes, stream.stream()));
+    if (cosine)
+      check_status(b200c_knn_graph_cosine(p.x.data_ptr(), p.px, p.num_segments, n, dim, k, source_to_target ? 1 : 0,
+                                          out.data_ptr<int64_t>(), irregular.data_ptr<int32_t>(), gws.data_ptr(),
+                                          gws_bytes, stream.stream()));
+    else
+      check_status(b200c_knn_graph(p.x.data_ptr(), p.px, p.num_segments, n, dim, k, p.dtype, source_to_target ? 1 : 0,
+                                   out.data_ptr<int64_t>(), irregular.data_ptr<int32_t>(), max_segment_rows,
+                                   gws_bytes ? gws.data_ptr() : nullptr, gws_bytes, stream.stream()));
     const int32_t odd = irregular.item<int32_t>();  // the one host sync
     TORCH_CHECK(odd < kGraphWaitError, "b200_cluster: the kNN scan was abandoned (a bounded wait ran out, or segment pointers that overlap)");
     if (odd == 0) return out;

@@ -108,13 +108,14 @@ def test_knn_graph_feature_space_in_one_call(dim):
     batch = torch.arange(8, device=DEV).repeat_interleave(2048)
     p = _ptr(8, 2048)
 
-    def composed(xx, flow):
-        e = refc.knn(xx, xx, p, p, 21, False)           # row 0 = query, row 1 = neighbour
+    def composed(xx, flow, cosine=False):
+        e = refc.knn(xx, xx, p, p, 21, cosine)          # row 0 = query, row 1 = neighbour
         e = e[:, e[0] != e[1]]
         return e.flip(0) if flow == "source_to_target" else e
 
     for flow in ("source_to_target", "target_to_source"):
         _same(pc.knn_graph(x, 20, batch, flow=flow), composed(x, flow))
+        _same(pc.knn_graph(x, 20, batch, flow=flow, cosine=True), composed(x, flow, True))
     dup = x.clone()
     dup[:30] = dup[0]  # 30 copies of one row: some are pushed out of their own lists
     _same(pc.knn_graph(dup, 20, batch), composed(dup, "source_to_target"))
