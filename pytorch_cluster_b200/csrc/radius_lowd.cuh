@@ -244,6 +244,10 @@ static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask
   const int64_t row_words = (nx + chunk_points - 1) / chunk_points * chunk_words;
   const uint32_t *row = mask_words + mask_base[b] + (q - y_lo) * row_words;
   const int64_t o = offsets[q];
+  // the query's own row number, count times: consecutive lanes, consecutive places (the bit loops below then
+  // only place the point indices)
+  for (int e = lane; e < count; e += 32) out_row[o + e] = q;
+  int64_t *col = out_col + o;
   int run = 0;
   // 128 words (4096 points) per step: lane l takes words 4 l .. 4 l + 3 in one 16-byte load (a row holds a
   // whole number of chunks, i.e. a multiple of four words, and starts at such a multiple: the load is aligned
@@ -266,15 +270,13 @@ static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask
     while (lo != 0ull && pos < count) {
       const int bit = __ffsll((long long)lo) - 1;
       lo &= lo - 1ull;
-      out_row[o + pos] = q;
-      out_col[o + pos] = idx0 + bit;
+      col[pos] = idx0 + bit;
       ++pos;
     }
     while (hi != 0ull && pos < count) {
       const int bit = __ffsll((long long)hi) - 1;
       hi &= hi - 1ull;
-      out_row[o + pos] = q;
-      out_col[o + pos] = idx0 + 64 + bit;
+      col[pos] = idx0 + 64 + bit;
       ++pos;
     }
     run += __shfl_sync(FULL_MASK, incl, 31);
