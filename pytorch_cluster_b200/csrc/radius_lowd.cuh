@@ -220,9 +220,12 @@ radius_lowd_kernel(const T *__restrict__ x, const T *__restrict__ y,
 }
 
 // Edges from the bit matrix a COUNT_MASK pass left: one warp per query walks the query's row in
-// blocks of 32 words (one coalesced load), places every set bit at offsets[q] + (bits before it)
-// and stops after counts[q] of them (the truncation rule of csrc/cuda/radius_cuda.cu:33-40; words
-// of chunks the scan skipped after the query reached its quota are never needed).
+// blocks of 128 words (lane l: words 4 l .. 4 l + 3 in one 16-byte load), places every set bit at
+// offsets[q] + (bits before it) and stops after counts[q] of them (the truncation rule of
+// csrc/cuda/radius_cuda.cu:33-40; words of chunks the scan skipped after the query reached its quota are
+// never needed).  The pass is bound by its instruction count, not by bytes in flight, so the loop over a
+// lane's bits is kept to the minimum: 32-bit words, one store per bit (the point index); the query's own
+// row number goes out separately, count times, by consecutive lanes.
 static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask_words,
                                                const int64_t *__restrict__ mask_base,
                                                const int64_t *__restrict__ ptr_x, const int64_t *__restrict__ ptr_y,
@@ -266,18 +269,17 @@ static __global__ void radius_mask_fill_kernel(const uint32_t *__restrict__ mask
     }
     int pos = run + incl - mine;
     const int64_t idx0 = x_lo + w * 32;
-    uint64_t lo = ((uint64_t)quad.y << 32) | quad.x, hi = ((uint64_t)quad.w << 32) | quad.z;
-    while (lo != 0ull && pos < count) {
-      const int bit = __ffsll((long long)lo) - 1;
-      lo &= lo - 1ull;
-      col[pos] = idx0 + bit;
-      ++pos;
-    }
-    while (hi != 0ull && pos < count) {
-      const int bit = __ffsll((long long)hi) - 1;
-      hi &= hi - 1ull;
-      col[pos] = idx0 + 64 + bit;
-      ++pos;
+    uint32_t words[4] = {quad.x, quad.y, quad.z, quad.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t word = words[j];
+      const int64_t first = idx0 + 32 * j;
+      while (word != 0u && pos < count) {
+        const int bit = __ffs((int)word) - 1;
+        word &= word - 1u;
+        col[pos] = first + bit;
+        ++pos;
+      }
     }
     run += __shfl_sync(FULL_MASK, incl, 31);
   }
